@@ -1,0 +1,118 @@
+/*
+ * cs2d - 2D-CrossScan selective scan for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of the drop-in replacement for the two operators that
+ * longlong-yu/official-cross-scan exposes from its CUDA extension
+ * `selective_nd_scan_cuda_oflex` (kernels/selective_nd_scan).  A host binding
+ * (the Python module of the same name shipped in this repository, or any FFI)
+ * validates tensors, allocates outputs and calls these entry points with raw
+ * device pointers.  Nothing here takes or returns a framework type, allocates
+ * device memory, or synchronises the stream.
+ *
+ * All functions return 0 on success and a negative cs2d_status otherwise;
+ * cs2d_last_error() gives the message for the calling thread.
+ */
+#ifndef CS2D_H_
+#define CS2D_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CS2D_ABI_VERSION 1
+#define CS2D_MAX_DSTATE 16 /* reference: MAX_DSTATE, include/selective_scan_common.h:13 */
+
+typedef enum {
+    CS2D_OK = 0,
+    CS2D_ERR_INVALID = -1,     /* bad shape / dtype / pointer / stride           */
+    CS2D_ERR_UNSUPPORTED = -2, /* valid for the reference, not implemented here  */
+    CS2D_ERR_CUDA = -3         /* a CUDA runtime call or the launch failed       */
+} cs2d_status;
+
+typedef enum { CS2D_F32 = 0, CS2D_F16 = 1, CS2D_BF16 = 2 } cs2d_dtype;
+
+/*
+ * Problem description shared by forward and backward.  It replaces the
+ * reference's launch-parameter struct SSMParamsBase
+ * (include/cusoflex/selective_scan_oflex.h:4-51), filled there by
+ * set_ssm_params_fwd (src/cusoflex/selective_scan_oflex.cpp:37-112).
+ *
+ * Tensor meaning and layout are the reference's: u (batch, dim, nrows, ncols),
+ * delta (batch, delta_dim, nrows, ncols), A (dim, dstate) fp32,
+ * B and C (batch, n_groups, dstate, nrows, ncols), D (dim) fp32 or NULL,
+ * delta_bias (delta_dim) fp32 or NULL, A_decay (1) fp32 or NULL.
+ * Strides are in ELEMENTS (64-bit, the reference uses 32-bit); the innermost
+ * (ncols) stride of u, delta, B, C, out/dout must be 1 as the reference
+ * requires (selective_scan_oflex.cpp:203-204,227,229,318).
+ */
+typedef struct {
+    int32_t batch, dim, nrows, ncols, dstate, n_groups, delta_dim;
+    int32_t io_dtype;       /* cs2d_dtype of u, delta, B, C (and du, ddelta)          */
+    int32_t out_dtype;      /* cs2d_dtype of out (fwd) / dout (bwd): io_dtype or F32  */
+    int32_t delta_softplus; /* nonzero: delta = softplus(delta + bias), threshold 20  */
+    const void *u;      int64_t u_bs, u_ds, u_hs;
+    const void *delta;  int64_t delta_bs, delta_ds, delta_hs;
+    const float *A;     int64_t A_ds, A_ns;
+    const void *B;      int64_t B_bs, B_gs, B_ns, B_hs;
+    const void *C;      int64_t C_bs, C_gs, C_ns, C_hs;
+    const float *D;          /* may be NULL */
+    const float *delta_bias; /* may be NULL */
+    const float *A_decay;    /* may be NULL (then 1.0); must be > 0 when given */
+} cs2d_problem;
+
+/*
+ * Bytes of the saved-state buffer the forward writes and the backward reads
+ * (row checkpoints of the state h).  It takes the place of the reference's
+ * three side tensors x, x_v, x_sd (selective_scan_oflex.cpp:251-258); unlike
+ * them it is NOT modified by the backward, so backward may run twice on it.
+ * Returns 0 for an invalid problem.
+ */
+size_t cs2d_saved_bytes(const cs2d_problem *p);
+
+/*
+ * Forward.  Replaces selective_scan_fwd_cuda<input_t, float, output_t>
+ * (include/cusoflex/selective_scan_fwd_kernel_oflex.cuh:376-392) as called by
+ * selective_scan_fwd (src/cusoflex/selective_scan_oflex.cpp:275-281).
+ *   out   (batch, dim, nrows, ncols) of out_dtype, strides out_bs/ds/hs, inner 1
+ *   saved device buffer of cs2d_saved_bytes(p) bytes, 16-byte aligned
+ * Launches on `stream` (a cudaStream_t) of the current device; asynchronous.
+ */
+int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, int64_t out_hs,
+             void *saved, void *stream);
+
+/*
+ * Backward.  Replaces selective_scan_bwd_cuda<input_t, float, output_t>
+ * (include/cusoflex/selective_scan_bwd_kernel_oflex.cuh:922-938) as called by
+ * selective_scan_bwd (src/cusoflex/selective_scan_oflex.cpp:424-430).
+ *   dout   (batch, dim, nrows, ncols) of p->out_dtype
+ *   du     (batch, dim, nrows, ncols) of io_dtype
+ *   ddelta (batch, dim, nrows, ncols) of io_dtype - at full channel resolution
+ *          like the reference kernel; the host reduces it to delta_dim
+ *          (selective_scan_oflex.cpp:433-438)
+ *   dA (dim, dstate), dB, dC (batch, n_groups, dstate, nrows, ncols): fp32,
+ *          contiguous, ACCUMULATED into - the caller zero-fills them, exactly as
+ *          the reference host does (selective_scan_oflex.cpp:395,398-399)
+ *   dD (dim), ddelta_bias (dim), dA_decay (1): fp32, accumulated into, or NULL
+ *   du, ddelta: contiguous.
+ * dA_decay reproduces the reference's value (it omits the row-scan term).
+ */
+int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t dout_ds, int64_t dout_hs,
+             const void *saved, void *du, void *ddelta, float *dA, float *dB, float *dC,
+             float *dD, float *ddelta_bias, float *dA_decay, void *stream);
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char *cs2d_last_error(void);
+
+/* CS2D_ABI_VERSION the library was built with. */
+int cs2d_abi_version(void);
+
+/* Number of kernels this library has launched in this process (for benchmarks). */
+int64_t cs2d_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CS2D_H_ */

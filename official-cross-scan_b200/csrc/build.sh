@@ -1,0 +1,11 @@
+#!/usr/bin/env bash
+# Builds the cs2d shared library in-tree for sm_100a.
+#   official-cross-scan_b200/csrc/build.sh [extra nvcc flags]
+set -euo pipefail
+here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+out="$here/../cs2d/libcs2d.so"
+NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
+"$NVCC" -gencode arch=compute_100a,code=sm_100a -lineinfo -O3 -std=c++17 \
+  -Xcompiler -fPIC -shared -cudart static --threads 3 "$@" \
+  -o "$out" "$here/cs2d_api.cu" "$here/cs2d_fwd.cu" "$here/cs2d_bwd.cu"
+echo "built $out"

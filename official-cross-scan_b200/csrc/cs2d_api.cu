@@ -1,0 +1,149 @@
+// extern "C" boundary of the cs2d library: validation, launch geometry, errors.
+// Mirrors the checks of the reference host binding
+// (src/cusoflex/selective_scan_oflex.cpp:188-245 and :298-391) on raw pointers.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "cs2d_common.cuh"
+
+namespace cs2d {
+cudaError_t launch_fwd(const Dev &P, int L, int grid, int threads, cudaStream_t st);
+cudaError_t launch_bwd(const Dev &P, int L, int grid, int threads, cudaStream_t st);
+size_t fwd_smem_bytes(int L, int DC, int NP);
+size_t bwd_smem_bytes(int L, int DC, int NP);
+
+static thread_local char g_err[512] = "";
+static std::atomic<int64_t> g_launches{0};
+
+static int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+static int gcd(int a, int b) { return b ? gcd(b, a % b) : a; }
+
+struct Geometry { int L, NP, DC, threads, ntiles, grid, nck; };
+
+static const size_t kMaxSmem = 227 * 1024;
+
+// Lanes per row, channels per CTA and grid for a problem.  threads is always a
+// multiple of 32 and of NP*L so that a warp holds whole (channel, pair) groups.
+static int plan(const cs2d_problem *p, bool backward, Geometry *g) {
+    const int strips = (p->ncols + STRIP - 1) / STRIP;
+    int L = 1;
+    while (L < strips) L <<= 1;
+    if (L > 32) return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d: rows wider than %d columns are not supported yet",
+                            p->ncols, 32 * STRIP);
+    const int NP = (p->dstate + 1) / 2;
+    const int tpc = NP * L;
+    const int unit = 32 / gcd(32, tpc);  // channels needed to fill whole warps
+    const int dpg = p->dim / p->n_groups;
+    int DC = unit * (256 / (unit * tpc) > 0 ? 256 / (unit * tpc) : 1);
+    while (DC - unit >= dpg && DC > unit) DC -= unit;  // do not carry idle channels
+    if (backward) {
+        while (DC > unit && bwd_smem_bytes(L, DC, NP) > kMaxSmem) DC -= unit;
+        if (bwd_smem_bytes(L, DC, NP) > kMaxSmem)
+            return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d with dstate=%d needs more shared memory than one SM has",
+                        p->ncols, p->dstate);
+    }
+    g->L = L; g->NP = NP; g->DC = DC; g->threads = DC * tpc;
+    g->ntiles = (dpg + DC - 1) / DC;
+    g->grid = p->batch * p->n_groups * g->ntiles;
+    g->nck = (p->nrows + RB - 1) / RB;
+    return CS2D_OK;
+}
+
+static int validate(const cs2d_problem *p) {
+    if (!p) return fail(CS2D_ERR_INVALID, "problem is NULL");
+    if (p->batch <= 0 || p->dim <= 0 || p->nrows <= 0 || p->ncols <= 0 || p->dstate <= 0 || p->n_groups <= 0 ||
+        p->delta_dim <= 0)
+        return fail(CS2D_ERR_INVALID, "all sizes must be positive");
+    if (p->io_dtype < CS2D_F32 || p->io_dtype > CS2D_BF16)
+        return fail(CS2D_ERR_INVALID, "input type must be float32, float16 or bfloat16");
+    if (p->out_dtype != p->io_dtype && p->out_dtype != CS2D_F32)
+        return fail(CS2D_ERR_INVALID, "out/dout type must equal the input type or be float32");
+    if (p->dim % p->n_groups) return fail(CS2D_ERR_INVALID, "dims should be dividable by n_groups");
+    if (p->dim % p->delta_dim) return fail(CS2D_ERR_INVALID, "dims should be dividable by delta_dim");
+    if (p->dstate > CS2D_MAX_DSTATE)
+        return fail(CS2D_ERR_INVALID, "selective_scan only supports state dimension <= %d", CS2D_MAX_DSTATE);
+    if (!p->u || !p->delta || !p->A || !p->B || !p->C) return fail(CS2D_ERR_INVALID, "u, delta, A, B, C must be given");
+    return CS2D_OK;
+}
+
+static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
+    d.batch = p->batch; d.dim = p->dim; d.H = p->nrows; d.W = p->ncols; d.N = p->dstate; d.G = p->n_groups;
+    d.ddim = p->delta_dim; d.io_dt = p->io_dtype; d.out_dt = p->out_dtype; d.softplus = p->delta_softplus;
+    d.dpg = p->dim / p->n_groups; d.drep = p->dim / p->delta_dim; d.NP = g.NP; d.DC = g.DC; d.ntiles = g.ntiles;
+    d.nck = g.nck;
+    d.u = p->u; d.delta = p->delta; d.B = p->B; d.C = p->C; d.A = p->A; d.D = p->D; d.bias = p->delta_bias;
+    d.decay = p->A_decay;
+    d.u_bs = p->u_bs; d.u_ds = p->u_ds; d.u_hs = p->u_hs;
+    d.dl_bs = p->delta_bs; d.dl_ds = p->delta_ds; d.dl_hs = p->delta_hs;
+    d.A_ds = p->A_ds; d.A_ns = p->A_ns;
+    d.B_bs = p->B_bs; d.B_gs = p->B_gs; d.B_ns = p->B_ns; d.B_hs = p->B_hs;
+    d.C_bs = p->C_bs; d.C_gs = p->C_gs; d.C_ns = p->C_ns; d.C_hs = p->C_hs;
+    d.du = d.ddelta = nullptr; d.dA = d.dB = d.dC = d.dD = d.dbias = d.ddecay = nullptr;
+}
+}  // namespace cs2d
+
+using namespace cs2d;
+
+extern "C" {
+
+size_t cs2d_saved_bytes(const cs2d_problem *p) {
+    Geometry g;
+    if (validate(p) != CS2D_OK || plan(p, false, &g) != CS2D_OK) return 0;
+    return (size_t)p->batch * p->dim * g.nck * g.NP * (g.L * STRIP) * sizeof(float2);
+}
+
+int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, int64_t out_hs, void *saved,
+             void *stream) {
+    int rc = validate(p);
+    if (rc) return rc;
+    if (!out || !saved) return fail(CS2D_ERR_INVALID, "out and saved must be given");
+    if (reinterpret_cast<uintptr_t>(saved) & 15) return fail(CS2D_ERR_INVALID, "saved must be 16-byte aligned");
+    Geometry g;
+    if ((rc = plan(p, false, &g))) return rc;
+    Dev d;
+    fill(d, p, g);
+    d.out = out; d.o_bs = out_bs; d.o_ds = out_ds; d.o_hs = out_hs;
+    d.saved = reinterpret_cast<float2 *>(saved);
+    cudaError_t e = launch_fwd(d, g.L, g.grid, g.threads, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
+    g_launches.fetch_add(1);
+    return CS2D_OK;
+}
+
+int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t dout_ds, int64_t dout_hs,
+             const void *saved, void *du, void *ddelta, float *dA, float *dB, float *dC, float *dD,
+             float *ddelta_bias, float *dA_decay, void *stream) {
+    int rc = validate(p);
+    if (rc) return rc;
+    if (!dout || !saved || !du || !ddelta || !dA || !dB || !dC)
+        return fail(CS2D_ERR_INVALID, "dout, saved, du, ddelta, dA, dB, dC must be given");
+    if (dA_decay && !p->A_decay) return fail(CS2D_ERR_INVALID, "dA_decay requested without A_decay");
+    Geometry g, gf;
+    if ((rc = plan(p, true, &g))) return rc;
+    if ((rc = plan(p, false, &gf))) return rc;
+    Dev d;
+    fill(d, p, g);
+    d.NP = g.NP;
+    d.out = const_cast<void *>(dout); d.o_bs = dout_bs; d.o_ds = dout_ds; d.o_hs = dout_hs;
+    d.saved = reinterpret_cast<float2 *>(const_cast<void *>(saved));
+    d.du = du; d.ddelta = ddelta; d.dA = dA; d.dB = dB; d.dC = dC; d.dD = dD; d.dbias = ddelta_bias;
+    d.ddecay = dA_decay;
+    cudaError_t e = launch_bwd(d, g.L, g.grid, g.threads, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
+    g_launches.fetch_add(1);
+    return CS2D_OK;
+}
+
+const char *cs2d_last_error(void) { return g_err; }
+int cs2d_abi_version(void) { return CS2D_ABI_VERSION; }
+int64_t cs2d_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"
