@@ -73,6 +73,15 @@ typedef struct {
 size_t cs2d_saved_bytes(const cs2d_problem *p);
 
 /*
+ * Bytes of the scratch buffer the backward needs (one adjoint row per channel
+ * and state pair, carried between row blocks).  Contents are undefined before
+ * and after a call.  The reference keeps the equivalent state in the x / x_sd
+ * tensors it overwrites (selective_scan_bwd_kernel_oflex.cuh:490,726).
+ * Returns 0 for an invalid or unsupported problem.
+ */
+size_t cs2d_bwd_scratch_bytes(const cs2d_problem *p);
+
+/*
  * Forward.  Replaces selective_scan_fwd_cuda<input_t, float, output_t>
  * (include/cusoflex/selective_scan_fwd_kernel_oflex.cuh:376-392) as called by
  * selective_scan_fwd (src/cusoflex/selective_scan_oflex.cpp:275-281).
@@ -88,6 +97,8 @@ int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, i
  * (include/cusoflex/selective_scan_bwd_kernel_oflex.cuh:922-938) as called by
  * selective_scan_bwd (src/cusoflex/selective_scan_oflex.cpp:424-430).
  *   dout   (batch, dim, nrows, ncols) of p->out_dtype
+ *   scratch device buffer of cs2d_bwd_scratch_bytes(p) bytes, 16-byte aligned;
+ *          concurrent calls must not share it
  *   du     (batch, dim, nrows, ncols) of io_dtype
  *   ddelta (batch, dim, nrows, ncols) of io_dtype - at full channel resolution
  *          like the reference kernel; the host reduces it to delta_dim
@@ -100,7 +111,7 @@ int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, i
  * dA_decay reproduces the reference's value (it omits the row-scan term).
  */
 int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t dout_ds, int64_t dout_hs,
-             const void *saved, void *du, void *ddelta, float *dA, float *dB, float *dC,
+             const void *saved, void *scratch, void *du, void *ddelta, float *dA, float *dB, float *dC,
              float *dD, float *ddelta_bias, float *dA_decay, void *stream);
 
 /* Message of the last failure on the calling thread ("" if none). */

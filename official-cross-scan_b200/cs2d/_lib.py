@@ -49,10 +49,12 @@ def lib():
         vp, i64 = ctypes.c_void_p, ctypes.c_int64
         L.cs2d_saved_bytes.restype = ctypes.c_size_t
         L.cs2d_saved_bytes.argtypes = [ctypes.POINTER(Problem)]
+        L.cs2d_bwd_scratch_bytes.restype = ctypes.c_size_t
+        L.cs2d_bwd_scratch_bytes.argtypes = [ctypes.POINTER(Problem)]
         L.cs2d_fwd.restype = ctypes.c_int
         L.cs2d_fwd.argtypes = [ctypes.POINTER(Problem), vp, i64, i64, i64, vp, vp]
         L.cs2d_bwd.restype = ctypes.c_int
-        L.cs2d_bwd.argtypes = [ctypes.POINTER(Problem), vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+        L.cs2d_bwd.argtypes = [ctypes.POINTER(Problem), vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
         L.cs2d_last_error.restype = ctypes.c_char_p
         L.cs2d_abi_version.restype = ctypes.c_int
         L.cs2d_launch_count.restype = ctypes.c_int64

@@ -145,9 +145,10 @@ def bwd(u, delta, A, B, C, D_, delta_bias_, dout, x_, x_v_, delta_softplus, A_de
         dD = torch.zeros(dim, dtype=torch.float32, device=dev) if D_ is not None else None
         ddelta_bias = torch.zeros(dim, dtype=torch.float32, device=dev) if delta_bias_ is not None else None
         dA_decay = torch.zeros(1, dtype=torch.float32, device=dev) if A_decay_ is not None else None
+        scratch = torch.empty(L.cs2d_bwd_scratch_bytes(ctypes.byref(p)) // 4, dtype=torch.float32, device=dev)
         stream = torch.cuda.current_stream(dev).cuda_stream
         rc = L.cs2d_bwd(ctypes.byref(p), _ptr(dout), dout.stride(0), dout.stride(1), dout.stride(2), _ptr(x_v_),
-                        _ptr(du), _ptr(ddelta), _ptr(dA), _ptr(dB), _ptr(dC), _ptr(dD), _ptr(ddelta_bias),
+                        _ptr(scratch), _ptr(du), _ptr(ddelta), _ptr(dA), _ptr(dB), _ptr(dC), _ptr(dD), _ptr(ddelta_bias),
                         _ptr(dA_decay), ctypes.c_void_p(stream))
     _raise_on(rc, "backward")
     if dim != delta_dim:

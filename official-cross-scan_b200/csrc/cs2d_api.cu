@@ -4,14 +4,15 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <initializer_list>
 
 #include "cs2d_common.cuh"
 
 namespace cs2d {
-cudaError_t launch_fwd(const Dev &P, int L, int grid, int threads, cudaStream_t st);
-cudaError_t launch_bwd(const Dev &P, int L, int grid, int threads, cudaStream_t st);
-size_t fwd_smem_bytes(int L, int DC, int NP);
-size_t bwd_smem_bytes(int L, int DC, int NP);
+cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st);
+cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st);
+size_t fwd_smem_bytes(int L, int CG, int NPp);
+size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc);
 
 static thread_local char g_err[512] = "";
 static std::atomic<int64_t> g_launches{0};
@@ -24,14 +25,12 @@ static int fail(int code, const char *fmt, ...) {
     return code;
 }
 
-static int gcd(int a, int b) { return b ? gcd(b, a % b) : a; }
-
-struct Geometry { int L, NP, DC, threads, ntiles, grid, nck; };
+struct Geometry { int L, NPp, CG, CP, CT, npass, ntiles, grid, nck, acc; };
 
 static const size_t kMaxSmem = 227 * 1024;
+static const int kSMs = 148;
 
-// Lanes per row, channels per CTA and grid for a problem.  threads is always a
-// multiple of 32 and of NP*L so that a warp holds whole (channel, pair) groups.
+// Lanes per row, state-pair slots, channels per pass and per CTA, and the grid.
 static int plan(const cs2d_problem *p, bool backward, Geometry *g) {
     const int strips = (p->ncols + STRIP - 1) / STRIP;
     int L = 1;
@@ -39,19 +38,35 @@ static int plan(const cs2d_problem *p, bool backward, Geometry *g) {
     if (L > 32) return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d: rows wider than %d columns are not supported yet",
                             p->ncols, 32 * STRIP);
     const int NP = (p->dstate + 1) / 2;
-    const int tpc = NP * L;
-    const int unit = 32 / gcd(32, tpc);  // channels needed to fill whole warps
+    int NPp = 1;
+    while (NPp < NP) NPp <<= 1;
     const int dpg = p->dim / p->n_groups;
-    int DC = unit * (256 / (unit * tpc) > 0 ? 256 / (unit * tpc) : 1);
-    while (DC - unit >= dpg && DC > unit) DC -= unit;  // do not carry idle channels
+    // Channel groups per pass: fill the CTA up to 8 warps, but keep the staged
+    // per-channel tiles small enough that the shared memory fits.
+    int CG = MAX_WARPS / NPp;
+    while (CG > 1 && (backward ? bwd_smem_bytes(L, CG, NPp, CG * (32 / L), false) : 2 * fwd_smem_bytes(L, CG, NPp)) > kMaxSmem)
+        CG >>= 1;
+    const int CP = CG * (32 / L);
+    const int pmax = (dpg + CP - 1) / CP;  // passes that cover a whole group
+    // Channels per CTA: as many as possible (B/C staging and the dB/dC atomics are
+    // paid once per CTA) while the grid still fills the machine a few times over.
+    const int slots = kSMs * (backward ? 1 : 2);
+    int npass = pmax < 8 ? pmax : 8;
+    while (npass > 1 && (int64_t)p->batch * p->n_groups * ((dpg + npass * CP - 1) / (npass * CP)) < 3LL * slots)
+        npass = (npass + 1) / 2;
+    g->acc = 1;
     if (backward) {
-        while (DC > unit && bwd_smem_bytes(L, DC, NP) > kMaxSmem) DC -= unit;
-        if (bwd_smem_bytes(L, DC, NP) > kMaxSmem)
+        if (bwd_smem_bytes(L, CG, NPp, npass * CP, true) > kMaxSmem) g->acc = 0;
+        while (npass > 1 && bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc) > kMaxSmem) --npass;
+        if (bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc) > kMaxSmem)
             return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d with dstate=%d needs more shared memory than one SM has",
                         p->ncols, p->dstate);
+    } else if (fwd_smem_bytes(L, CG, NPp) > kMaxSmem) {
+        return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d with dstate=%d needs more shared memory than one SM has",
+                    p->ncols, p->dstate);
     }
-    g->L = L; g->NP = NP; g->DC = DC; g->threads = DC * tpc;
-    g->ntiles = (dpg + DC - 1) / DC;
+    g->L = L; g->NPp = NPp; g->CG = CG; g->CP = CP; g->npass = npass; g->CT = npass * CP;
+    g->ntiles = (dpg + g->CT - 1) / g->CT;
     g->grid = p->batch * p->n_groups * g->ntiles;
     g->nck = (p->nrows + RB - 1) / RB;
     return CS2D_OK;
@@ -74,11 +89,23 @@ static int validate(const cs2d_problem *p) {
     return CS2D_OK;
 }
 
+// A tensor may be accessed four elements at a time when its base address is
+// aligned to four elements and every stride that separates rows is a multiple
+// of four (rows then start aligned whenever ncols is a multiple of four).
+static bool vec_ok(const void *ptr, int esize, int ncols, std::initializer_list<int64_t> strides) {
+    if (ncols % 4) return false;
+    if (reinterpret_cast<uintptr_t>(ptr) % (4 * esize)) return false;
+    for (int64_t s : strides)
+        if (s % 4) return false;
+    return true;
+}
+static int esize(int dt) { return dt == CS2D_F32 ? 4 : 2; }
+
 static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     d.batch = p->batch; d.dim = p->dim; d.H = p->nrows; d.W = p->ncols; d.N = p->dstate; d.G = p->n_groups;
     d.ddim = p->delta_dim; d.io_dt = p->io_dtype; d.out_dt = p->out_dtype; d.softplus = p->delta_softplus;
-    d.dpg = p->dim / p->n_groups; d.drep = p->dim / p->delta_dim; d.NP = g.NP; d.DC = g.DC; d.ntiles = g.ntiles;
-    d.nck = g.nck;
+    d.dpg = p->dim / p->n_groups; d.drep = p->dim / p->delta_dim;
+    d.acc_dbc = g.acc; d.NPp = g.NPp; d.CG = g.CG; d.CT = g.CT; d.npass = g.npass; d.ntiles = g.ntiles; d.nck = g.nck;
     d.u = p->u; d.delta = p->delta; d.B = p->B; d.C = p->C; d.A = p->A; d.D = p->D; d.bias = p->delta_bias;
     d.decay = p->A_decay;
     d.u_bs = p->u_bs; d.u_ds = p->u_ds; d.u_hs = p->u_hs;
@@ -86,6 +113,13 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     d.A_ds = p->A_ds; d.A_ns = p->A_ns;
     d.B_bs = p->B_bs; d.B_gs = p->B_gs; d.B_ns = p->B_ns; d.B_hs = p->B_hs;
     d.C_bs = p->C_bs; d.C_gs = p->C_gs; d.C_ns = p->C_ns; d.C_hs = p->C_hs;
+    const int es = esize(p->io_dtype);
+    d.vec = 0;
+    if (vec_ok(p->u, es, p->ncols, {p->u_bs, p->u_ds, p->u_hs})) d.vec |= VEC_U;
+    if (vec_ok(p->delta, es, p->ncols, {p->delta_bs, p->delta_ds, p->delta_hs})) d.vec |= VEC_DELTA;
+    if (vec_ok(p->B, es, p->ncols, {p->B_bs, p->B_gs, p->B_ns, p->B_hs})) d.vec |= VEC_B;
+    if (vec_ok(p->C, es, p->ncols, {p->C_bs, p->C_gs, p->C_ns, p->C_hs})) d.vec |= VEC_C;
+    d.adj = nullptr;
     d.du = d.ddelta = nullptr; d.dA = d.dB = d.dC = d.dD = d.dbias = d.ddecay = nullptr;
 }
 }  // namespace cs2d
@@ -97,7 +131,13 @@ extern "C" {
 size_t cs2d_saved_bytes(const cs2d_problem *p) {
     Geometry g;
     if (validate(p) != CS2D_OK || plan(p, false, &g) != CS2D_OK) return 0;
-    return (size_t)p->batch * p->dim * g.nck * g.NP * (g.L * STRIP) * sizeof(float2);
+    return (size_t)p->batch * p->dim * g.nck * g.NPp * (g.L * STRIP) * sizeof(float2);
+}
+
+size_t cs2d_bwd_scratch_bytes(const cs2d_problem *p) {
+    Geometry g;
+    if (validate(p) != CS2D_OK || plan(p, true, &g) != CS2D_OK) return 0;
+    return (size_t)p->batch * p->dim * g.NPp * (g.L * STRIP) * sizeof(float2);
 }
 
 int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, int64_t out_hs, void *saved,
@@ -111,32 +151,37 @@ int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, i
     Dev d;
     fill(d, p, g);
     d.out = out; d.o_bs = out_bs; d.o_ds = out_ds; d.o_hs = out_hs;
+    if (vec_ok(out, esize(p->out_dtype), p->ncols, {out_bs, out_ds, out_hs})) d.vec |= VEC_OUT;
     d.saved = reinterpret_cast<float2 *>(saved);
-    cudaError_t e = launch_fwd(d, g.L, g.grid, g.threads, reinterpret_cast<cudaStream_t>(stream));
+    cudaError_t e = launch_fwd(d, g.L, g.grid, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
     g_launches.fetch_add(1);
     return CS2D_OK;
 }
 
 int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t dout_ds, int64_t dout_hs,
-             const void *saved, void *du, void *ddelta, float *dA, float *dB, float *dC, float *dD,
-             float *ddelta_bias, float *dA_decay, void *stream) {
+             const void *saved, void *scratch, void *du, void *ddelta, float *dA, float *dB, float *dC,
+             float *dD, float *ddelta_bias, float *dA_decay, void *stream) {
     int rc = validate(p);
     if (rc) return rc;
-    if (!dout || !saved || !du || !ddelta || !dA || !dB || !dC)
-        return fail(CS2D_ERR_INVALID, "dout, saved, du, ddelta, dA, dB, dC must be given");
+    if (!dout || !saved || !scratch || !du || !ddelta || !dA || !dB || !dC)
+        return fail(CS2D_ERR_INVALID, "dout, saved, scratch, du, ddelta, dA, dB, dC must be given");
+    if ((reinterpret_cast<uintptr_t>(saved) | reinterpret_cast<uintptr_t>(scratch)) & 15)
+        return fail(CS2D_ERR_INVALID, "saved and scratch must be 16-byte aligned");
     if (dA_decay && !p->A_decay) return fail(CS2D_ERR_INVALID, "dA_decay requested without A_decay");
-    Geometry g, gf;
+    Geometry g;
     if ((rc = plan(p, true, &g))) return rc;
-    if ((rc = plan(p, false, &gf))) return rc;
     Dev d;
     fill(d, p, g);
-    d.NP = g.NP;
     d.out = const_cast<void *>(dout); d.o_bs = dout_bs; d.o_ds = dout_ds; d.o_hs = dout_hs;
+    if (vec_ok(dout, esize(p->out_dtype), p->ncols, {dout_bs, dout_ds, dout_hs})) d.vec |= VEC_OUT;
+    if (vec_ok(du, esize(p->io_dtype), p->ncols, {}) && vec_ok(ddelta, esize(p->io_dtype), p->ncols, {}))
+        d.vec |= VEC_DU;
     d.saved = reinterpret_cast<float2 *>(const_cast<void *>(saved));
+    d.adj = reinterpret_cast<float2 *>(scratch);
     d.du = du; d.ddelta = ddelta; d.dA = dA; d.dB = dB; d.dC = dC; d.dD = dD; d.dbias = ddelta_bias;
     d.ddecay = dA_decay;
-    cudaError_t e = launch_bwd(d, g.L, g.grid, g.threads, reinterpret_cast<cudaStream_t>(stream));
+    cudaError_t e = launch_bwd(d, g.L, g.grid, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
     g_launches.fetch_add(1);
     return CS2D_OK;

@@ -15,368 +15,498 @@
 // cross-pixel terms (:544-587) regrouped by the pixel whose delta they touch.
 // ddelta = ddl * sigmoid(delta+bias) under softplus (:785-806).
 //
-// Rows are processed in blocks of RB from the bottom up.  For each block the
-// state h is recomputed from the checkpoint row the forward saved, kept in
-// registers, and consumed by the reverse sweep; the plain row scan s is
-// recomputed per row.  Sums over states (du, ddl) and over channels (dB, dC)
-// are formed in shared memory; dB/dC then go to global memory with one atomic
-// add per element and CTA.
+// Row blocks are processed from the bottom up; inside a block the CTA walks its
+// channels in passes.  For each (pass, block) h is recomputed from the
+// checkpoint row the forward saved, kept in registers, and consumed by the
+// reverse sweep; the plain row scan s is recomputed per row.  The adjoint row m
+// that crosses the block boundary is parked in a global scratch buffer.
+// dB/dC are summed over the warp's channels through a per-warp transposition
+// buffer and accumulated over passes in shared memory, then added to global
+// memory once per block and CTA.
 #include "cs2d_common.cuh"
 
 namespace cs2d {
 
 template <int L>
-__global__ void __launch_bounds__(256) bwd_kernel(const Dev P) {
-    constexpr int Wp = L * STRIP;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int DC = P.DC, NP = P.NP;
-    const int n_in = DC * RB * Wp;
-    const int n_bc = NP * RB * Wp;
-    float *su = reinterpret_cast<float *>(smem_raw);  // [DC][RB][Wp]
-    float *sg = su + n_in;                            // [DC][RB][Wp]  dout
-    float *ssig = sg + n_in;                          // [DC][RB][Wp]  d softplus / dx
-    float *sdu = ssig + n_in;                         // [DC][RB][Wp]  sum over states
-    float *sddl = sdu + n_in;                         // [DC][RB][Wp]
-    float *sdl = sddl + n_in;                         // [DC][RB+1][Wp] row 0 = row above block
-    float2 *sB = reinterpret_cast<float2 *>(sdl + DC * (RB + 1) * Wp);  // [NP][RB][Wp]
-    float2 *sC = sB + n_bc;
-    float2 *sdB = sC + n_bc;                          // sums over the CTA's channels
-    float2 *sdC = sdB + n_bc;
-    float *sred = reinterpret_cast<float *>(sdC + n_bc);  // [DC][2]: dD, ddelta_bias
+struct BwdSmem {
+    static constexpr int Wp = L * STRIP, CW = 32 / L;
+    static constexpr int CS4 = chan_stride<L>(RB), CS6 = chan_stride<L>(RB + 2);
+    // float offsets
+    static __host__ __device__ constexpr int u(int) { return 0; }
+    static __host__ __device__ constexpr int g(int CP) { return CP * CS4; }
+    static __host__ __device__ constexpr int sig(int CP) { return 2 * CP * CS4; }
+    static __host__ __device__ constexpr int dl(int CP) { return 3 * CP * CS4; }                 // RB+2 rows
+    static __host__ __device__ constexpr int pdu(int CP) { return dl(CP) + CP * CS6; }           // [warps][CW][CS4]
+    static __host__ __device__ constexpr int pdd(int CP, int nw) { return pdu(CP) + nw * CW * CS4; }
+    static __host__ __device__ constexpr int tr(int CP, int nw) { return pdd(CP, nw) + nw * CW * CS4; }   // [warps][2][256] float2
+    static __host__ __device__ constexpr int aB(int CP, int nw) { return tr(CP, nw) + nw * 1024; }        // [warps][RB][Wp] float2
+    static __host__ __device__ constexpr int aC(int CP, int nw, bool acc) { return aB(CP, nw) + (acc ? nw * RB * Wp * 2 : 0); }
+    static __host__ __device__ constexpr int B(int CP, int nw, bool acc) { return aC(CP, nw, acc) + (acc ? nw * RB * Wp * 2 : 0); }  // [NPp][RB][Wp] float2
+    static __host__ __device__ constexpr int C(int CP, int NPp, int nw, bool acc) { return B(CP, nw, acc) + NPp * RB * Wp * 2; }
+    static __host__ __device__ constexpr int dA(int CP, int NPp, int nw, bool acc) { return C(CP, NPp, nw, acc) + NPp * RB * Wp * 2; }
+    // dA: [CT][2*NPp], red: [CT][2], decay: [warps]
+    static __host__ __device__ constexpr int total(int CP, int NPp, int CT, int nw, bool acc) {
+        return dA(CP, NPp, nw, acc) + CT * 2 * NPp + CT * 2 + nw;
+    }
+};
 
-    const int tid = threadIdx.x;
-    const int j = tid & (L - 1);
-    const int q = tid / L;
-    const int pp = q % NP;
-    const int dc = q / NP;
-    const int tile = blockIdx.x % P.ntiles;
-    const int bg = blockIdx.x / P.ntiles;
-    const int g_ = bg % P.G;
-    const int b = bg / P.G;
-    const int d0 = g_ * P.dpg + tile * DC;
-    const int dvalid = min(DC, (g_ + 1) * P.dpg - d0);
-    const int d = d0 + min(dc, dvalid - 1);
-    const bool ch_ok = dc < dvalid;
+template <int L>
+__global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
+    using S = BwdSmem<L>;
+    constexpr int Wp = S::Wp, CW = S::CW, T4 = Wp / 4, CS4 = S::CS4, CS6 = S::CS6, L4 = 4 * L, L2 = 2 * L;
+    constexpr int NU = CW >= 8 ? 1 : 8 / CW;  // columns of a strip owned by a lane after the channel sum
+    extern __shared__ __align__(16) float smem[];
+    const int NPp = P.NPp, CG = P.CG, CP = CG * CW, CT = P.CT;
+    const int nthr = blockDim.x, nw = nthr >> 5;  // NPp * CG warps
+    float *su = smem + S::u(CP), *sg = smem + S::g(CP), *ssig = smem + S::sig(CP), *sdl = smem + S::dl(CP);
+    float *spdu = smem + S::pdu(CP), *spdd = smem + S::pdd(CP, nw);
+    float2 *str = reinterpret_cast<float2 *>(smem + S::tr(CP, nw));
+    float2 *saB = reinterpret_cast<float2 *>(smem + S::aB(CP, nw));
+    const bool acc_on = P.acc_dbc != 0;  // dB/dC accumulated over passes in shared memory
+    float2 *saC = reinterpret_cast<float2 *>(smem + S::aC(CP, nw, acc_on));
+    float2 *sB = reinterpret_cast<float2 *>(smem + S::B(CP, nw, acc_on));
+    float2 *sC = reinterpret_cast<float2 *>(smem + S::C(CP, NPp, nw, acc_on));
+    float *sdA = smem + S::dA(CP, NPp, nw, acc_on);
+    float *sred = sdA + CT * 2 * NPp;
+    float *sdecay = sred + CT * 2;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int j = lane & (L - 1), cl = lane / L;
+    const int pp = warp % NPp, cg = warp / NPp;
+    const int cp = cg * CW + cl;
+    const int tile = blockIdx.x % P.ntiles, bg = blockIdx.x / P.ntiles;
+    const int g_ = bg % P.G, b = bg / P.G;
+    const int dbase = g_ * P.dpg + tile * CT;
+    const int nch = min(CT, (g_ + 1) * P.dpg - dbase);
     const int H = P.H, W = P.W, N = P.N;
-    const int c0 = j * STRIP;
-    const int n0 = 2 * pp, n1 = 2 * pp + 1;
-
+    const int n0 = 2 * pp, n1 = n0 + 1;
+    const bool pair_on = n0 < N;
     const float decay = P.decay ? __ldg(P.decay) : 1.f;
     const float2 lgd = bc(P.decay ? log2f(decay) : 0.f);
-    const float2 Araw = f2(__ldg(P.A + d * P.A_ds + n0 * P.A_ns), n1 < N ? __ldg(P.A + d * P.A_ds + n1 * P.A_ns) : 0.f);
-    const float2 A2 = mul2(Araw, bc(LOG2E));
     const bool want_decay = P.ddecay != nullptr;
 
-    if (tid < DC * 2) sred[tid] = 0.f;
+    for (int i = tid; i < nw * CW * CS4; i += nthr) { spdu[i] = 0.f; spdd[i] = 0.f; }
+    if (acc_on)
+        for (int i = tid; i < nw * RB * Wp; i += nthr) { saB[i] = bc(0.f); saC[i] = bc(0.f); }
+    for (int i = tid; i < CT * 2 * NPp + CT * 2 + nw; i += nthr) sdA[i] = 0.f;
+    float2 ddecay_acc = bc(0.f);
 
-    float2 m_dn[STRIP], a_dn[STRIP];
+    const int nblk = P.nck, npass = P.npass;
+    const int steps = nblk * npass;
+    for (int step = 0; step <= steps; ++step) {
+        const int blk = nblk - 1 - step / npass, pass = step % npass;  // bottom-up
+        const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
+        const int ch0 = pass * CP;
+        const int pstep = step - 1;
+        const int pblk = nblk - 1 - pstep / npass, ppass = pstep % npass;
+        const int pr0 = pblk * RB, pnr = step > 0 ? min(RB, H - pr0) : 0, pch0 = ppass * CP;
+        // ---- phase A: write out the previous step, stage this one -------------------
+        {
+            const int items = CP * RB * T4;
+            for (int it = tid; it < items; it += nthr) {
+                const int t = it % T4, rr = (it / T4) % RB, sc = it / (T4 * RB);
+                const int c = 4 * t, o4 = sc * CS4 + rr * Wp + pos4<L>(t);
+                if (pnr > 0) {  // uniform
+                    float dDp = 0.f, dbp = 0.f;
+                    if (rr < pnr && pch0 + sc < nch) {
+                        const int sd = dbase + pch0 + sc;
+                        const int scg = sc / CW, scl = sc % CW;
+                        float4 a1 = make_float4(0.f, 0.f, 0.f, 0.f), a2 = a1;
+                        for (int q = 0; q < NPp; ++q) {
+                            const int o = ((scg * NPp + q) * CW + scl) * CS4 + rr * Wp + pos4<L>(t);
+                            const float4 v1 = *reinterpret_cast<const float4 *>(spdu + o);
+                            const float4 v2 = *reinterpret_cast<const float4 *>(spdd + o);
+                            a1.x += v1.x; a1.y += v1.y; a1.z += v1.z; a1.w += v1.w;
+                            a2.x += v2.x; a2.y += v2.y; a2.z += v2.z; a2.w += v2.w;
+                        }
+                        const float4 gv = *reinterpret_cast<const float4 *>(sg + o4);
+                        const float4 uv = *reinterpret_cast<const float4 *>(su + o4);
+                        const float4 sv = *reinterpret_cast<const float4 *>(ssig + o4);
+                        const float Dv = P.D ? __ldg(P.D + sd) : 0.f;
+                        a1.x = fmaf(Dv, gv.x, a1.x); a1.y = fmaf(Dv, gv.y, a1.y);
+                        a1.z = fmaf(Dv, gv.z, a1.z); a1.w = fmaf(Dv, gv.w, a1.w);
+                        a2.x *= sv.x; a2.y *= sv.y; a2.z *= sv.z; a2.w *= sv.w;
+                        const int64_t o = (((int64_t)b * P.dim + sd) * H + (pr0 + rr)) * W + c;
+                        st4(P.du, o, P.io_dt, P.vec & VEC_DU, W - c, a1);
+                        st4(P.ddelta, o, P.io_dt, P.vec & VEC_DU, W - c, a2);
+                        // columns past the image carry g = 0 and ddl = 0
+                        dDp = gv.x * uv.x + gv.y * uv.y + gv.z * uv.z + gv.w * uv.w;
+                        dbp = a2.x + a2.y + a2.z + a2.w;
+                    }
+                    // the RB*T4 items of a channel are consecutive: segmented warp sum
+                    constexpr int SEG = RB * T4 < 32 ? RB * T4 : 32;
 #pragma unroll
-    for (int i = 0; i < STRIP; ++i) { m_dn[i] = bc(0.f); a_dn[i] = bc(0.f); }
-    float2 dAacc = bc(0.f), ddecay_acc = bc(0.f);
-
-    const int r_last = ((H - 1) / RB) * RB;
-    for (int r0 = r_last; r0 >= -RB; r0 -= RB) {
-        const int nr = r0 >= 0 ? min(RB, H - r0) : 0;
-        // ---- write out the block processed before (r0+RB), stage block r0 ----
-        const int rp = r0 + RB;
-        const int nrp = rp <= r_last ? min(RB, H - rp) : 0;
-        for (int idx = tid; idx < n_in; idx += blockDim.x) {
-            const int c = idx % Wp, rr = (idx / Wp) % RB, sdc = idx / (Wp * RB);
-            const int sd = d0 + sdc;
-            const bool okc = sdc < dvalid && c < W;
-            if (nrp > 0) {
-                float dDp = 0.f, dbp = 0.f;
-                if (okc && rr < nrp) {
-                    const float gv = sg[idx];
-                    const float dux = (P.D ? __ldg(P.D + sd) * gv : 0.f) + sdu[idx];
-                    const float dd = sddl[idx] * ssig[idx];
-                    const int64_t o = (((int64_t)b * P.dim + sd) * H + (rp + rr)) * W + c;
-                    st_elem(P.du, o, P.io_dt, dux);
-                    st_elem(P.ddelta, o, P.io_dt, dd);
-                    dDp = gv * su[idx];
-                    dbp = dd;
+                    for (int off = SEG / 2; off; off >>= 1) {
+                        dDp += __shfl_xor_sync(0xffffffffu, dDp, off);
+                        dbp += __shfl_xor_sync(0xffffffffu, dbp, off);
+                    }
+                    if ((lane & (SEG - 1)) == 0 && pch0 + sc < nch) {
+                        atomicAdd(sred + 2 * (pch0 + sc), dDp);
+                        atomicAdd(sred + 2 * (pch0 + sc) + 1, dbp);
+                    }
                 }
-                // RB*Wp is a multiple of 32, so a warp never straddles two channels
+                float4 uv = make_float4(0.f, 0.f, 0.f, 0.f), gv = uv;
+                if (rr < nr && ch0 + sc < nch) {
+                    const int sd = dbase + ch0 + sc, r = r0 + rr;
+                    uv = ld4(P.u, (int64_t)b * P.u_bs + (int64_t)sd * P.u_ds + (int64_t)r * P.u_hs + c, P.io_dt,
+                             P.vec & VEC_U, W - c);
+                    gv = ld4(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + (int64_t)r * P.o_hs + c, P.out_dt,
+                             P.vec & VEC_OUT, W - c);
+                }
+                *reinterpret_cast<float4 *>(su + o4) = uv;
+                *reinterpret_cast<float4 *>(sg + o4) = gv;
+            }
+            __syncthreads();  // the write-out above read ssig; the loop below refills it item by item
+            if (nr > 0) {
+                const int items6 = CP * (RB + 2) * T4;
+                for (int it = tid; it < items6; it += nthr) {
+                    const int t = it % T4, rr = (it / T4) % (RB + 2), sc = it / (T4 * (RB + 2));
+                    const int c = 4 * t, r = r0 + rr - 1;
+                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), sg4 = x;
+                    // rows r0-1 .. r0+nr (the row below the block only if it exists)
+                    if (r >= 0 && r < H && rr - 1 <= nr && ch0 + sc < nch) {
+                        const int sdd = (dbase + ch0 + sc) / P.drep;
+                        x = ld4(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)r * P.dl_hs + c,
+                                P.io_dt, P.vec & VEC_DELTA, W - c);
+                        const float bv = P.bias ? __ldg(P.bias + sdd) : 0.f;
+                        float xs[4] = {x.x + bv, x.y + bv, x.z + bv, x.w + bv}, sgs[4];
 #pragma unroll
-                for (int off = 16; off; off >>= 1) {
-                    dDp += __shfl_xor_sync(0xffffffffu, dDp, off);
-                    dbp += __shfl_xor_sync(0xffffffffu, dbp, off);
-                }
-                if ((tid & 31) == 0) {
-                    atomicAdd(sred + 2 * sdc, dDp);
-                    atomicAdd(sred + 2 * sdc + 1, dbp);
-                }
-            }
-            float uv = 0.f, dlv = 0.f, gv = 0.f, sig = 0.f;
-            if (okc && rr < nr) {
-                const int r = r0 + rr;
-                uv = ld_elem(P.u, (int64_t)b * P.u_bs + (int64_t)sd * P.u_ds + (int64_t)r * P.u_hs + c, P.io_dt);
-                gv = ld_elem(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + (int64_t)r * P.o_hs + c, P.out_dt);
-                const int sdd = sd / P.drep;
-                float x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)r * P.dl_hs + c,
-                                  P.io_dt);
-                if (P.bias) x += __ldg(P.bias + sdd);
-                dlv = x; sig = 1.f;
-                if (P.softplus && x <= 20.f) { dlv = log1pf(__expf(x)); sig = 1.f / (1.f + __expf(-x)); }
-            }
-            su[idx] = uv; sg[idx] = gv; ssig[idx] = sig; sdu[idx] = 0.f; sddl[idx] = 0.f;
-            sdl[(sdc * (RB + 1) + rr + 1) * Wp + c] = dlv;
-        }
-        if (nr > 0) {
-            // delta of the row above the block (for a of the checkpoint row)
-            for (int idx = tid; idx < DC * Wp; idx += blockDim.x) {
-                const int c = idx % Wp, sdc = idx / Wp;
-                const int sd = d0 + sdc;
-                float dlv = 0.f;
-                if (sdc < dvalid && c < W && r0 > 0) {
-                    const int sdd = sd / P.drep;
-                    float x = ld_elem(P.delta,
-                                      (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)(r0 - 1) * P.dl_hs + c,
-                                      P.io_dt);
-                    if (P.bias) x += __ldg(P.bias + sdd);
-                    dlv = P.softplus ? softplus20(x) : x;
-                }
-                sdl[(sdc * (RB + 1)) * Wp + c] = dlv;
-            }
-        }
-        for (int idx = tid; idx < n_bc; idx += blockDim.x) {
-            const int c = idx % Wp, rr = (idx / Wp) % RB, sp = idx / (Wp * RB);
-            if (nrp > 0 && c < W && rr < nrp) {
-                const float2 vb = sdB[idx], vc = sdC[idx];
-                const int64_t o = ((((int64_t)b * P.G + g_) * N + 2 * sp) * H + (rp + rr)) * W + c;
-                atomicAdd(P.dB + o, vb.x);
-                atomicAdd(P.dC + o, vc.x);
-                if (2 * sp + 1 < N) {
-                    atomicAdd(P.dB + o + (int64_t)H * W, vb.y);
-                    atomicAdd(P.dC + o + (int64_t)H * W, vc.y);
+                        for (int e = 0; e < 4; ++e) {
+                            sgs[e] = 1.f;
+                            if (P.softplus && xs[e] <= 20.f) {
+                                sgs[e] = 1.f / (1.f + __expf(-xs[e]));
+                                xs[e] = log1pf(__expf(xs[e]));
+                            }
+                            if (c + e >= W) { xs[e] = 0.f; sgs[e] = 0.f; }
+                        }
+                        x = make_float4(xs[0], xs[1], xs[2], xs[3]);
+                        sg4 = make_float4(sgs[0], sgs[1], sgs[2], sgs[3]);
+                    }
+                    *reinterpret_cast<float4 *>(sdl + sc * CS6 + rr * Wp + pos4<L>(t)) = x;
+                    if (rr >= 1 && rr <= RB)
+                        *reinterpret_cast<float4 *>(ssig + sc * CS4 + (rr - 1) * Wp + pos4<L>(t)) = sg4;
                 }
             }
-            float2 bv = bc(0.f), cv = bc(0.f);
-            if (c < W && rr < nr) {
-                const int r = r0 + rr;
-                const int64_t ob = (int64_t)b * P.B_bs + (int64_t)g_ * P.B_gs + (int64_t)r * P.B_hs + c;
-                const int64_t oc = (int64_t)b * P.C_bs + (int64_t)g_ * P.C_gs + (int64_t)r * P.C_hs + c;
-                bv.x = ld_elem(P.B, ob + (int64_t)(2 * sp) * P.B_ns, P.io_dt);
-                cv.x = ld_elem(P.C, oc + (int64_t)(2 * sp) * P.C_ns, P.io_dt);
-                if (2 * sp + 1 < N) {
-                    bv.y = ld_elem(P.B, ob + (int64_t)(2 * sp + 1) * P.B_ns, P.io_dt);
-                    cv.y = ld_elem(P.C, oc + (int64_t)(2 * sp + 1) * P.C_ns, P.io_dt);
+            // a row block is complete when its last pass has been written out
+            if (acc_on && pnr > 0 && ppass == npass - 1) {
+                const int itemsB = nw * RB * Wp;  // one float2 (two states) per item
+                for (int it = tid; it < itemsB; it += nthr) {
+                    const int c = it % Wp, rr = (it / Wp) % RB, w = it / (Wp * RB);
+                    const int spp = w % NPp, scg = w / NPp;
+                    const int o = (w * RB + rr) * Wp + pos2<L>(c);
+                    const float2 vb = saB[o], vc = saC[o];
+                    saB[o] = bc(0.f); saC[o] = bc(0.f);
+                    (void)scg;
+                    if (c < W && rr < pnr && 2 * spp < N) {
+                        const int64_t og = ((((int64_t)b * P.G + g_) * N + 2 * spp) * H + (pr0 + rr)) * W + c;
+                        atomicAdd(P.dB + og, vb.x);
+                        atomicAdd(P.dC + og, vc.x);
+                        if (2 * spp + 1 < N) {
+                            atomicAdd(P.dB + og + (int64_t)H * W, vb.y);
+                            atomicAdd(P.dC + og + (int64_t)H * W, vc.y);
+                        }
+                    }
                 }
             }
-            sB[idx] = bv; sC[idx] = cv; sdB[idx] = bc(0.f); sdC[idx] = bc(0.f);
+            if (nr > 0 && pass == 0) stage_BC<L>(P, b, g_, r0, nr, sB, sC);
         }
         __syncthreads();
         if (nr == 0) break;
 
-        // ---- recompute h for the block from the checkpoint row ---------------
-        float2 hs[RB + 1][STRIP];  // hs[0] = row above the block
-        float2 a_up[STRIP];
-        {
-            const float4 *pd = reinterpret_cast<const float4 *>(sdl + (dc * (RB + 1)) * Wp + c0);
-            const float4 e0 = pd[0], e1 = pd[1];
-            const float dlt[STRIP] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
-            if (r0 > 0 && ch_ok) {
-                const float4 *ck = reinterpret_cast<const float4 *>(
-                    P.saved + ((((int64_t)b * P.dim + d) * P.nck + (r0 / RB - 1)) * NP + pp) * Wp + c0);
-#pragma unroll
-                for (int k = 0; k < STRIP / 2; ++k) {
-                    const float4 v = __ldg(ck + k);
-                    hs[0][2 * k] = f2(v.x, v.y); hs[0][2 * k + 1] = f2(v.z, v.w);
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < STRIP; ++i) hs[0][i] = bc(0.f);
-            }
-#pragma unroll
-            for (int i = 0; i < STRIP; ++i) a_up[i] = r0 > 0 ? ex2_2(fma2(bc(dlt[i]), A2, lgd)) : bc(0.f);
-        }
-#pragma unroll
-        for (int rr = 0; rr < RB; ++rr) {
-            if (rr < nr) {
-                float dl[STRIP], dlu[STRIP];
-                float2 Bv[STRIP];
-                const float4 *pu = reinterpret_cast<const float4 *>(su + (dc * RB + rr) * Wp + c0);
-                const float4 *pd = reinterpret_cast<const float4 *>(sdl + (dc * (RB + 1) + rr + 1) * Wp + c0);
-                const float4 u0 = pu[0], u1 = pu[1], e0 = pd[0], e1 = pd[1];
-                dl[0] = e0.x; dl[1] = e0.y; dl[2] = e0.z; dl[3] = e0.w;
-                dl[4] = e1.x; dl[5] = e1.y; dl[6] = e1.z; dl[7] = e1.w;
-                dlu[0] = e0.x * u0.x; dlu[1] = e0.y * u0.y; dlu[2] = e0.z * u0.z; dlu[3] = e0.w * u0.w;
-                dlu[4] = e1.x * u1.x; dlu[5] = e1.y * u1.y; dlu[6] = e1.z * u1.z; dlu[7] = e1.w * u1.w;
-                const float4 *pb = reinterpret_cast<const float4 *>(sB + (pp * RB + rr) * Wp + c0);
-#pragma unroll
-                for (int k = 0; k < STRIP / 2; ++k) {
-                    const float4 bq = pb[k];
-                    Bv[2 * k] = f2(bq.x, bq.y); Bv[2 * k + 1] = f2(bq.z, bq.w);
-                }
-                float2 a[STRIP], p[STRIP], sdummy[STRIP];
-                row_forward<L, false>(j, dl, dlu, Bv, A2, lgd, hs[rr], a_up, a, p, hs[rr + 1], sdummy);
-#pragma unroll
-                for (int i = 0; i < STRIP; ++i) a_up[i] = a[i];
-            }
-        }
-
-        // ---- reverse sweep over the block --------------------------------------
-#pragma unroll
-        for (int rr = RB - 1; rr >= 0; --rr) {
-            if (rr < nr) {
-                float dl[STRIP], uu[STRIP], gg[STRIP];
-                float2 Bv[STRIP], Cv[STRIP];
-                {
-                    const float4 *pu = reinterpret_cast<const float4 *>(su + (dc * RB + rr) * Wp + c0);
-                    const float4 *pg = reinterpret_cast<const float4 *>(sg + (dc * RB + rr) * Wp + c0);
-                    const float4 *pd = reinterpret_cast<const float4 *>(sdl + (dc * (RB + 1) + rr + 1) * Wp + c0);
-                    const float4 u0 = pu[0], u1 = pu[1], e0 = pd[0], e1 = pd[1], g0 = pg[0], g1 = pg[1];
-                    dl[0] = e0.x; dl[1] = e0.y; dl[2] = e0.z; dl[3] = e0.w;
-                    dl[4] = e1.x; dl[5] = e1.y; dl[6] = e1.z; dl[7] = e1.w;
-                    uu[0] = u0.x; uu[1] = u0.y; uu[2] = u0.z; uu[3] = u0.w;
-                    uu[4] = u1.x; uu[5] = u1.y; uu[6] = u1.z; uu[7] = u1.w;
-                    gg[0] = g0.x; gg[1] = g0.y; gg[2] = g0.z; gg[3] = g0.w;
-                    gg[4] = g1.x; gg[5] = g1.y; gg[6] = g1.z; gg[7] = g1.w;
-                    const float4 *pb = reinterpret_cast<const float4 *>(sB + (pp * RB + rr) * Wp + c0);
-                    const float4 *pc = reinterpret_cast<const float4 *>(sC + (pp * RB + rr) * Wp + c0);
+        // ---- compute ---------------------------------------------------------------------
+        if (pair_on) {
+            const bool ch_ok = ch0 + cp < nch;
+            const int d = dbase + min(ch0 + cp, nch - 1);
+            const float2 Araw = f2(__ldg(P.A + d * P.A_ds + n0 * P.A_ns),
+                                   n1 < N ? __ldg(P.A + d * P.A_ds + n1 * P.A_ns) : 0.f);
+            const float2 A2 = mul2(Araw, bc(LOG2E));
+            const float *dlc = sdl + cp * CS6;
+            float2 hs[RB + 1][STRIP];  // hs[0] = row above the block
+            // -- recompute h for the block from the checkpoint row --
+            {
+                float2 a_up[STRIP];
+                if (r0 > 0) {
+                    float dlt[STRIP];
+                    unpack8(dlc, L4, j, dlt);
+                    const float4 *pk = reinterpret_cast<const float4 *>(
+                        P.saved + ((((int64_t)b * P.dim + d) * P.nck + (blk - 1)) * NPp + pp) * Wp + j * STRIP);
 #pragma unroll
                     for (int k = 0; k < STRIP / 2; ++k) {
-                        const float4 bq = pb[k], cq = pc[k];
-                        Bv[2 * k] = f2(bq.x, bq.y); Bv[2 * k + 1] = f2(bq.z, bq.w);
-                        Cv[2 * k] = f2(cq.x, cq.y); Cv[2 * k + 1] = f2(cq.z, cq.w);
+                        const float4 v = ch_ok ? __ldg(pk + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        hs[0][2 * k] = f2(v.x, v.y); hs[0][2 * k + 1] = f2(v.z, v.w);
+                    }
+#pragma unroll
+                    for (int i = 0; i < STRIP; ++i) a_up[i] = ex2_2(fma2(bc(dlt[i]), A2, lgd));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < STRIP; ++i) { hs[0][i] = bc(0.f); a_up[i] = bc(0.f); }
+                }
+#pragma unroll
+                for (int rr = 0; rr < RB; ++rr) {
+                    if (rr < nr) {
+                        float dl[STRIP], uu[STRIP], dlu[STRIP];
+                        float2 Bv[STRIP];
+                        unpack8(su + cp * CS4 + rr * Wp, L4, j, uu);
+                        unpack8(dlc + (rr + 1) * Wp, L4, j, dl);
+#pragma unroll
+                        for (int i = 0; i < STRIP; ++i) dlu[i] = dl[i] * uu[i];
+                        unpack8x2(sB + (pp * RB + rr) * Wp, L2, j, Bv);
+                        float2 a[STRIP], p[STRIP], sdummy[STRIP];
+                        row_forward<L, false>(j, dl, dlu, Bv, A2, lgd, hs[rr], a_up, a, p, hs[rr + 1], sdummy);
+#pragma unroll
+                        for (int i = 0; i < STRIP; ++i) a_up[i] = a[i];
                     }
                 }
-                const float2 (&hrow)[STRIP] = hs[rr + 1];
-                const float2 (&hup)[STRIP] = hs[rr];
-                float2 a[STRIP], p[STRIP], s[STRIP], gC[STRIP];
-                // a, p and the plain row scan s (recomputed)
-                {
-                    float2 Pm = bc(1.f), St = bc(0.f);
+            }
+            // -- adjoint row below the block --
+            float2 m_dn[STRIP], a_dn[STRIP];
+            float2 *adj = P.adj + (((int64_t)b * P.dim + d) * NPp + pp) * Wp + j * STRIP;
+            if (r0 + RB < H) {
+                float dlt[STRIP];
+                unpack8(dlc + (RB + 1) * Wp, L4, j, dlt);
+                const float4 *pk = reinterpret_cast<const float4 *>(adj);
+#pragma unroll
+                for (int k = 0; k < STRIP / 2; ++k) {
+                    const float4 v = ch_ok ? pk[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    m_dn[2 * k] = f2(v.x, v.y); m_dn[2 * k + 1] = f2(v.z, v.w);
+                }
+#pragma unroll
+                for (int i = 0; i < STRIP; ++i) a_dn[i] = ex2_2(fma2(bc(dlt[i]), A2, lgd));
+            } else {
+#pragma unroll
+                for (int i = 0; i < STRIP; ++i) { m_dn[i] = bc(0.f); a_dn[i] = bc(0.f); }
+            }
+            float2 dAacc = bc(0.f);
+            // -- reverse sweep over the block --
+#pragma unroll
+            for (int rr = RB - 1; rr >= 0; --rr) {
+                if (rr < nr) {
+                    float dl[STRIP], uu[STRIP], gg[STRIP];
+                    float2 Bv[STRIP], Cv[STRIP];
+                    unpack8(su + cp * CS4 + rr * Wp, L4, j, uu);
+                    unpack8(sg + cp * CS4 + rr * Wp, L4, j, gg);
+                    unpack8(dlc + (rr + 1) * Wp, L4, j, dl);
+                    unpack8x2(sB + (pp * RB + rr) * Wp, L2, j, Bv);
+                    unpack8x2(sC + (pp * RB + rr) * Wp, L2, j, Cv);
+                    const float2 (&hrow)[STRIP] = hs[rr + 1];
+                    const float2 (&hup)[STRIP] = hs[rr];
+                    float2 a[STRIP], p[STRIP], s[STRIP], gC[STRIP];
+                    {   // a, p and the plain row scan s (recomputed)
+                        float2 Pm = bc(1.f), St = bc(0.f);
+#pragma unroll
+                        for (int i = 0; i < STRIP; ++i) {
+                            a[i] = ex2_2(fma2(bc(dl[i]), A2, lgd));
+                            p[i] = mul2(Bv[i], bc(dl[i] * uu[i]));
+                            gC[i] = mul2(Cv[i], bc(gg[i]));
+                            St = fma2(a[i], St, p[i]);
+                            Pm = mul2(Pm, a[i]);
+                        }
+                        float2 cs, unused;
+                        carry_fwd<L, false>(j, Pm, St, bc(0.f), cs, unused);
+#pragma unroll
+                        for (int i = 0; i < STRIP; ++i) { cs = fma2(a[i], cs, p[i]); s[i] = cs; }
+                    }
+                    float2 a_r7 = bc(0.f), mdr7 = bc(0.f);  // next lane's first column
+                    if constexpr (L > 1) {
+                        a_r7 = shfl_down2<L>(a[0], 1);
+                        mdr7 = shfl_down2<L>(m_dn[0], 1);
+                        if (j == L - 1) { a_r7 = bc(0.f); mdr7 = bc(0.f); }
+                    }
+                    float2 bt[STRIP], dh[STRIP], ds[STRIP];
+                    {   // reverse scans for dh and ds (shared multipliers a(r,c+1))
+                        float2 Pm = bc(1.f), Dh = bc(0.f), Ds = bc(0.f);
+#pragma unroll
+                        for (int i = STRIP - 1; i >= 0; --i) {
+                            const float2 ar = i < STRIP - 1 ? a[i + 1] : a_r7;
+                            const float2 mdr = i < STRIP - 1 ? m_dn[i + 1] : mdr7;
+                            bt[i] = fma2(mul2(add2(ar, a_dn[i]), mdr), bc(-0.5f), add2(gC[i], m_dn[i]));
+                            Dh = fma2(ar, Dh, bt[i]);
+                            Ds = fma2(ar, Ds, neg2(gC[i]));
+                            Pm = mul2(Pm, ar);
+                        }
+                        float2 cdh, cds;
+                        carry_rev<L, true>(j, Pm, Dh, Ds, cdh, cds);
+#pragma unroll
+                        for (int i = STRIP - 1; i >= 0; --i) {
+                            const float2 ar = i < STRIP - 1 ? a[i + 1] : a_r7;
+                            cdh = fma2(ar, cdh, bt[i]); dh[i] = cdh;
+                            cds = fma2(ar, cds, neg2(gC[i])); ds[i] = cds;
+                        }
+                    }
+                    float2 m[STRIP];
+#pragma unroll
+                    for (int i = 0; i < STRIP; ++i) m[i] = mul2(a[i], dh[i]);
+                    float2 m_r7 = bc(0.f), h_l0 = bc(0.f);
+                    if constexpr (L > 1) {
+                        m_r7 = shfl_down2<L>(m[0], 1);
+                        h_l0 = shfl_up2<L>(hrow[STRIP - 1], 1);
+                        if (j == L - 1) m_r7 = bc(0.f);
+                        if (j == 0) h_l0 = bc(0.f);
+                    }
+                    float duv[STRIP], ddv[STRIP];
+                    // dB/dC are summed over the warp's CW channels by transposing through
+                    // shared memory (each lane then adds up NU columns) and accumulated over
+                    // passes in the warp's private tile.  Column i is rotated by its owner
+                    // so that the owners' reads hit distinct banks.
+                    float2 *trB = str + warp * 512, *trC = trB + 256;
+                    float2 *accB = saB + (warp * RB + rr) * Wp, *accC = saC + (warp * RB + rr) * Wp;
 #pragma unroll
                     for (int i = 0; i < STRIP; ++i) {
-                        a[i] = ex2_2(fma2(bc(dl[i]), A2, lgd));
-                        p[i] = mul2(Bv[i], bc(dl[i] * uu[i]));
-                        gC[i] = mul2(Cv[i], bc(gg[i]));
-                        St = fma2(a[i], St, p[i]);
-                        Pm = mul2(Pm, a[i]);
+                        const float2 hl = i ? hrow[i - 1] : h_l0;
+                        const float2 mr = i < STRIP - 1 ? m[i + 1] : m_r7;
+                        const float2 X = fma2(m_dn[i], hl, mul2(mr, hup[i]));
+                        const float2 hm = sub2(hrow[i], p[i]);
+                        const float2 sm = sub2(s[i], p[i]);
+                        const float2 Gh = fma2(dh[i], hm, mul2(mul2(a[i], X), bc(-0.5f)));
+                        const float2 G = fma2(ds[i], sm, Gh);
+                        const float2 eps = fma2(gC[i], bc(0.25f), add2(dh[i], ds[i]));
+                        const float2 t1 = mul2(Bv[i], eps);
+                        const float2 t2 = mul2(Araw, G);
+                        const float S1 = t1.x + t1.y;
+                        duv[i] = dl[i] * S1;
+                        ddv[i] = fmaf(uu[i], S1, t2.x + t2.y);
+                        dAacc = fma2(bc(dl[i]), G, dAacc);
+                        if (want_decay) ddecay_acc = add2(ddecay_acc, Gh);
+                        const float2 dBv = mul2(bc(dl[i] * uu[i]), eps);
+                        const float2 dCv = mul2(bc(gg[i]), fma2(p[i], bc(0.25f), sub2(hrow[i], s[i])));
+                        if constexpr (CW == 1) {
+                            if (acc_on) {
+                                float2 *qb = accB + pos2<L>(j * STRIP + i), *qc = accC + pos2<L>(j * STRIP + i);
+                                *qb = add2(*qb, dBv);
+                                *qc = add2(*qc, dCv);
+                            } else if (ch_ok && j * STRIP + i < W) {
+                                const int64_t og = ((((int64_t)b * P.G + g_) * N + n0) * H + (r0 + rr)) * W + j * STRIP + i;
+                                atomicAdd(P.dB + og, dBv.x);
+                                atomicAdd(P.dC + og, dCv.x);
+                                if (n1 < N) {
+                                    atomicAdd(P.dB + og + (int64_t)H * W, dBv.y);
+                                    atomicAdd(P.dC + og + (int64_t)H * W, dCv.y);
+                                }
+                            }
+                        } else {
+                            const int o = i * 32 + ((lane + L * (i / NU)) & 31);
+                            trB[o] = dBv;
+                            trC[o] = dCv;
+                        }
                     }
-                    float2 cs, unused;
-                    carry_fwd<L, false>(j, Pm, St, bc(0.f), cs, unused);
+                    // sums over the state pairs: per-warp partial tiles, added up at write-out
+                    pack8(spdu + (warp * CW + cl) * CS4 + rr * Wp, L4, j, duv);
+                    pack8(spdd + (warp * CW + cl) * CS4 + rr * Wp, L4, j, ddv);
+                    if constexpr (CW > 1) {
+                        __syncwarp();
+                        if (cl < 8) {
+                            const int my = CW >= 8 ? cl : cl * NU;  // first owned column
 #pragma unroll
-                    for (int i = 0; i < STRIP; ++i) { cs = fma2(a[i], cs, p[i]); s[i] = cs; }
-                }
-                // neighbours to the right (next lane's first column)
-                float2 a_r7 = bc(0.f), mdr7 = bc(0.f);
-                if constexpr (L > 1) {
-                    a_r7 = shfl_down2<L>(a[0], 1);
-                    mdr7 = shfl_down2<L>(m_dn[0], 1);
-                    if (j == L - 1) { a_r7 = bc(0.f); mdr7 = bc(0.f); }
-                }
-                // reverse scans for dh and ds (shared multipliers a(r,c+1))
-                float2 bt[STRIP], dh[STRIP], ds[STRIP];
-                {
-                    float2 Pm = bc(1.f), Dh = bc(0.f), Ds = bc(0.f);
+                            for (int t = 0; t < NU; ++t) {
+                                const int col = my + t;
+                                float2 sb = bc(0.f), sc2 = bc(0.f);
 #pragma unroll
-                    for (int i = STRIP - 1; i >= 0; --i) {
-                        const float2 ar = i < STRIP - 1 ? a[i + 1] : a_r7;
-                        const float2 mdr = i < STRIP - 1 ? m_dn[i + 1] : mdr7;
-                        bt[i] = fma2(mul2(add2(ar, a_dn[i]), mdr), bc(-0.5f), add2(gC[i], m_dn[i]));
-                        Dh = fma2(ar, Dh, bt[i]);
-                        Ds = fma2(ar, Ds, neg2(gC[i]));
-                        Pm = mul2(Pm, ar);
+                                for (int c2 = 0; c2 < CW; ++c2) {
+                                    const int o = col * 32 + ((c2 * L + j + L * (col / NU)) & 31);
+                                    sb = add2(sb, trB[o]);
+                                    sc2 = add2(sc2, trC[o]);
+                                }
+                                if (acc_on) {
+                                    float2 *qb = accB + pos2<L>(j * STRIP + col), *qc = accC + pos2<L>(j * STRIP + col);
+                                    *qb = add2(*qb, sb);
+                                    *qc = add2(*qc, sc2);
+                                } else if (j * STRIP + col < W) {
+                                    const int64_t og =
+                                        ((((int64_t)b * P.G + g_) * N + n0) * H + (r0 + rr)) * W + j * STRIP + col;
+                                    atomicAdd(P.dB + og, sb.x);
+                                    atomicAdd(P.dC + og, sc2.x);
+                                    if (n1 < N) {
+                                        atomicAdd(P.dB + og + (int64_t)H * W, sb.y);
+                                        atomicAdd(P.dC + og + (int64_t)H * W, sc2.y);
+                                    }
+                                }
+                            }
+                        }
+                        __syncwarp();
                     }
-                    float2 cdh, cds;
-                    carry_rev<L, true>(j, Pm, Dh, Ds, cdh, cds);
 #pragma unroll
-                    for (int i = STRIP - 1; i >= 0; --i) {
-                        const float2 ar = i < STRIP - 1 ? a[i + 1] : a_r7;
-                        cdh = fma2(ar, cdh, bt[i]); dh[i] = cdh;
-                        cds = fma2(ar, cds, neg2(gC[i])); ds[i] = cds;
-                    }
+                    for (int i = 0; i < STRIP; ++i) { m_dn[i] = m[i]; a_dn[i] = a[i]; }
                 }
-                float2 m[STRIP];
+            }
+            if (r0 > 0 && ch_ok) {  // park the adjoint row for the block above
+                float4 *pk = reinterpret_cast<float4 *>(adj);
 #pragma unroll
-                for (int i = 0; i < STRIP; ++i) m[i] = mul2(a[i], dh[i]);
-                float2 m_r7 = bc(0.f), h_l0 = bc(0.f);
-                if constexpr (L > 1) {
-                    m_r7 = shfl_down2<L>(m[0], 1);
-                    h_l0 = shfl_up2<L>(hrow[STRIP - 1], 1);
-                    if (j == L - 1) m_r7 = bc(0.f);
-                    if (j == 0) h_l0 = bc(0.f);
-                }
-                float *durow = sdu + (dc * RB + rr) * Wp + c0;
-                float *ddrow = sddl + (dc * RB + rr) * Wp + c0;
-                float2 *dBrow = sdB + (pp * RB + rr) * Wp + c0;
-                float2 *dCrow = sdC + (pp * RB + rr) * Wp + c0;
+                for (int k = 0; k < STRIP / 2; ++k)
+                    pk[k] = make_float4(m_dn[2 * k].x, m_dn[2 * k].y, m_dn[2 * k + 1].x, m_dn[2 * k + 1].y);
+            }
+            if constexpr (L > 1) {
 #pragma unroll
-                for (int i = 0; i < STRIP; ++i) {
-                    const float2 hl = i ? hrow[i - 1] : h_l0;
-                    const float2 mr = i < STRIP - 1 ? m[i + 1] : m_r7;
-                    const float2 X = fma2(m_dn[i], hl, mul2(mr, hup[i]));
-                    const float2 hm = sub2(hrow[i], p[i]);
-                    const float2 sm = sub2(s[i], p[i]);
-                    const float2 Gh = fma2(dh[i], hm, mul2(mul2(a[i], X), bc(-0.5f)));
-                    const float2 G = fma2(ds[i], sm, Gh);
-                    const float2 eps = fma2(gC[i], bc(0.25f), add2(dh[i], ds[i]));
-                    const float2 t1 = mul2(Bv[i], eps);
-                    const float2 t2 = mul2(Araw, G);
-                    const float S1 = t1.x + t1.y;
-                    atomicAdd(durow + i, dl[i] * S1);
-                    atomicAdd(ddrow + i, fmaf(uu[i], S1, t2.x + t2.y));
-                    dAacc = fma2(bc(dl[i]), G, dAacc);
-                    if (want_decay) ddecay_acc = add2(ddecay_acc, Gh);
-                    const float2 dBv = mul2(bc(dl[i] * uu[i]), eps);
-                    const float2 dCv = mul2(bc(gg[i]), fma2(p[i], bc(0.25f), sub2(hrow[i], s[i])));
-                    atomicAdd(&dBrow[i].x, dBv.x); atomicAdd(&dBrow[i].y, dBv.y);
-                    atomicAdd(&dCrow[i].x, dCv.x); atomicAdd(&dCrow[i].y, dCv.y);
-                }
-#pragma unroll
-                for (int i = 0; i < STRIP; ++i) { m_dn[i] = m[i]; a_dn[i] = a[i]; }
+                for (int off = L / 2; off; off >>= 1) dAacc = add2(dAacc, shfl_xor2<L>(dAacc, off));
+            }
+            if (j == 0 && ch_ok) {  // one owner per (channel, pair): no atomics needed
+                float *q = sdA + (ch0 + cp) * 2 * NPp + 2 * pp;
+                q[0] += dAacc.x; q[1] += dAacc.y;
             }
         }
         __syncthreads();
     }
 
     // ---- per-channel parameter gradients ---------------------------------------
-    if constexpr (L > 1) {
+    if (want_decay) {
+        float v = ddecay_acc.x + (n1 < N ? ddecay_acc.y : 0.f);
+        if (!pair_on) v = 0.f;
 #pragma unroll
-        for (int off = L / 2; off; off >>= 1) {
-            dAacc = add2(dAacc, shfl_xor2<L>(dAacc, off));
-            ddecay_acc = add2(ddecay_acc, shfl_xor2<L>(ddecay_acc, off));
-        }
-    }
-    if (j == 0 && ch_ok) {
-        atomicAdd(P.dA + (int64_t)d * N + n0, dAacc.x);
-        if (n1 < N) atomicAdd(P.dA + (int64_t)d * N + n1, dAacc.y);
-        if (want_decay) atomicAdd(P.ddecay, (ddecay_acc.x + (n1 < N ? ddecay_acc.y : 0.f)) / decay);
+        for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == 0) sdecay[warp] = v;
     }
     __syncthreads();
-    if (tid < dvalid * 2) {
-        const int sd = d0 + tid / 2;
-        if ((tid & 1) == 0) { if (P.dD) atomicAdd(P.dD + sd, sred[tid]); }
-        else if (P.dbias) atomicAdd(P.dbias + sd, sred[tid]);
+    for (int i = tid; i < nch * 2 * NPp; i += nthr) {
+        const int sc = i / (2 * NPp), n = i % (2 * NPp);
+        if (n < N) atomicAdd(P.dA + (int64_t)(dbase + sc) * N + n, sdA[i]);
+    }
+    for (int i = tid; i < nch * 2; i += nthr) {
+        const int sd = dbase + i / 2;
+        if ((i & 1) == 0) { if (P.dD) atomicAdd(P.dD + sd, sred[i]); }
+        else if (P.dbias) atomicAdd(P.dbias + sd, sred[i]);
+    }
+    if (want_decay && tid == 0) {
+        float v = 0.f;
+        for (int w = 0; w < nw; ++w) v += sdecay[w];
+        atomicAdd(P.ddecay, v / decay);
     }
 }
 
-size_t bwd_smem_bytes(int L, int DC, int NP) {
-    const int Wp = L * STRIP;
-    return (size_t)(5 * DC * RB * Wp + DC * (RB + 1) * Wp + 2 * DC) * 4 + (size_t)(4 * NP * RB * Wp) * 8;
+size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc) {
+    const int nw = CG * NPp;
+    const int CP = CG * (32 / L);
+    switch (L) {
+        case 1: return (size_t)BwdSmem<1>::total(CP, NPp, CT, nw, acc) * 4;
+        case 2: return (size_t)BwdSmem<2>::total(CP, NPp, CT, nw, acc) * 4;
+        case 4: return (size_t)BwdSmem<4>::total(CP, NPp, CT, nw, acc) * 4;
+        case 8: return (size_t)BwdSmem<8>::total(CP, NPp, CT, nw, acc) * 4;
+        case 16: return (size_t)BwdSmem<16>::total(CP, NPp, CT, nw, acc) * 4;
+        default: return (size_t)BwdSmem<32>::total(CP, NPp, CT, nw, acc) * 4;
+    }
 }
 
 template <int L>
-static cudaError_t launch(const Dev &P, int grid, int threads, size_t smem, cudaStream_t st) {
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(bwd_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) {
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(bwd_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    bwd_kernel<L><<<grid, threads, smem, st>>>(P);
+    bwd_kernel<L><<<grid, 32 * P.CG * P.NPp, smem, st>>>(P);
     return cudaGetLastError();
 }
 
-cudaError_t launch_bwd(const Dev &P, int L, int grid, int threads, cudaStream_t st) {
-    const size_t smem = bwd_smem_bytes(L, P.DC, P.NP);
+cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st) {
+    const size_t smem = bwd_smem_bytes(L, P.CG, P.NPp, P.CT, P.acc_dbc != 0);
     switch (L) {
-        case 1: return launch<1>(P, grid, threads, smem, st);
-        case 2: return launch<2>(P, grid, threads, smem, st);
-        case 4: return launch<4>(P, grid, threads, smem, st);
-        case 8: return launch<8>(P, grid, threads, smem, st);
-        case 16: return launch<16>(P, grid, threads, smem, st);
-        case 32: return launch<32>(P, grid, threads, smem, st);
+        case 1: return launch<1>(P, grid, smem, st);
+        case 2: return launch<2>(P, grid, smem, st);
+        case 4: return launch<4>(P, grid, smem, st);
+        case 8: return launch<8>(P, grid, smem, st);
+        case 16: return launch<16>(P, grid, smem, st);
+        case 32: return launch<32>(P, grid, smem, st);
     }
     return cudaErrorInvalidValue;
 }

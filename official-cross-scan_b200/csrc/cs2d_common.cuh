@@ -5,13 +5,23 @@
 // There are batch*dim*dstate independent 2-D linear recurrences.  A thread owns
 // a strip of STRIP (=8) consecutive columns of ONE row at a time, for a PAIR of
 // states (n, n+1) of one channel; the pair is processed with packed fp32x2
-// arithmetic (FFMA2/FMUL2/FADD2 of sm_100).  L = 2^k lanes of a warp cover one
-// image row (L*8 >= ncols) and rows are walked sequentially, so the previous
-// row lives in registers.  The recurrence along a row is a first-order linear
-// scan: each lane folds its 8 columns, a log2(L)-step warp-shuffle scan
-// combines the lane aggregates, and a second local pass applies the carry.
-// Inputs are staged once per CTA (all channels of the tile and all states
-// share them) in shared memory, 4 rows at a time.
+// arithmetic (FFMA2/FMUL2/FADD2 of sm_100).  L = 2^k lanes cover one image row
+// (L*8 >= ncols) and rows are walked sequentially, so the previous row lives in
+// registers.  The recurrence along a row is a first-order linear scan: each
+// lane folds its 8 columns, a log2(L)-step warp-shuffle scan combines the lane
+// aggregates, and a second local pass applies the carry.
+//
+// A warp holds CW = 32/L channels of the SAME state pair, so B and C are read
+// from shared memory as broadcasts and the sums over channels (dB, dC) are
+// formed inside the warp.  A CTA has NPp state pairs x CG channel groups
+// (at most 8 warps) and walks its CT channels in passes of CP = CG*CW channels; sums over
+// state pairs (y, du, ddelta) go through per-warp partial tiles.  No shared
+// memory atomics are used anywhere (fp32 shared atomics are CAS loops).
+//
+// Rows are processed in blocks of RB = 4.  The state that crosses a block
+// boundary lives in global memory: the last h row of each block is the
+// checkpoint the backward needs anyway, and the backward keeps its adjoint row
+// in a scratch buffer.  Both are read back by the thread that wrote them.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -24,7 +34,9 @@
 namespace cs2d {
 
 constexpr int STRIP = 8;     // columns per thread
-constexpr int RB = 4;        // rows per staged block == checkpoint cadence
+constexpr int RB = 4;        // rows per block == checkpoint cadence
+constexpr int MAX_WARPS = 8;  // warps per CTA: state-pair slots x channel groups, at most 8
+constexpr int MAX_THREADS = MAX_WARPS * 32;
 constexpr float LOG2E = 1.4426950408889634f;
 
 // Device-side problem description (passed by value to the kernels).
@@ -33,21 +45,27 @@ struct Dev {
     int io_dt, out_dt, softplus;
     int dpg;    // channels per B/C group
     int drep;   // channels per delta channel
-    int NP;     // state pairs: ceil(N/2)
-    int DC;     // channels per CTA
+    int NPp;    // state-pair slots per channel: power of two >= ceil(N/2)
+    int CG;     // channel groups per pass; the CTA has NPp * CG warps
+    int CT;     // channels per CTA
+    int npass;  // passes per row block = CT / (CG * 32/L)
     int ntiles; // channel tiles per group
-    int nck;    // checkpoint rows per image: ceil(H/RB)
+    int nck;    // row blocks per image: ceil(H/RB)
+    int acc_dbc; // backward: 1 = dB/dC accumulated over the CTA's passes in shared memory,
+                 //           0 = added to global memory row by row (wide rows: tiles do not fit)
+    int vec;    // bit i set: tensor i may be accessed 4 elements at a time
     const void *u, *delta, *B, *C;
     const float *A, *D, *bias, *decay;
     int64_t u_bs, u_ds, u_hs, dl_bs, dl_ds, dl_hs, A_ds, A_ns;
     int64_t B_bs, B_gs, B_ns, B_hs, C_bs, C_gs, C_ns, C_hs;
-    // forward: out; backward: dout
-    void *out; int64_t o_bs, o_ds, o_hs;
-    float2 *saved;
+    void *out; int64_t o_bs, o_ds, o_hs;  // forward: out; backward: dout
+    float2 *saved;                         // [batch][dim][nck][NPp][L*8] checkpoints of h
     // backward only
+    float2 *adj;                           // [batch][dim][NPp][L*8] adjoint row between blocks
     void *du, *ddelta;
     float *dA, *dB, *dC, *dD, *dbias, *ddecay;
 };
+enum { VEC_U = 1, VEC_DELTA = 2, VEC_B = 4, VEC_C = 8, VEC_OUT = 16, VEC_DU = 32 };
 
 // ---- packed fp32x2 helpers -------------------------------------------------
 __device__ __forceinline__ float2 f2(float x, float y) { return make_float2(x, y); }
@@ -79,7 +97,7 @@ __device__ __forceinline__ float2 shfl_xor2(float2 v, int off) {
     return make_float2(__shfl_xor_sync(0xffffffffu, v.x, off, WIDTH), __shfl_xor_sync(0xffffffffu, v.y, off, WIDTH));
 }
 
-// ---- dtype-generic element access (staging only; uniform branch) -----------
+// ---- dtype-generic global access (staging / write-out only) -------------------
 __device__ __forceinline__ float ld_elem(const void *p, int64_t i, int dt) {
     if (dt == CS2D_F32) return __ldg(reinterpret_cast<const float *>(p) + i);
     if (dt == CS2D_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i]);
@@ -90,9 +108,90 @@ __device__ __forceinline__ void st_elem(void *p, int64_t i, int dt, float v) {
     else if (dt == CS2D_BF16) reinterpret_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16(v);
     else reinterpret_cast<__half *>(p)[i] = __float2half(v);
 }
+// 4 consecutive elements starting at i; `nvalid` (<=4) of them exist, the rest read as 0.
+__device__ __forceinline__ float4 ld4(const void *p, int64_t i, int dt, bool vec, int nvalid) {
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (nvalid <= 0) return r;
+    if (vec && nvalid >= 4) {
+        if (dt == CS2D_F32) return __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p) + i));
+        const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(p) + i));
+        if (dt == CS2D_BF16) {
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+            const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+            return make_float4(a.x, a.y, b.x, b.y);
+        }
+        const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    r.x = ld_elem(p, i, dt);
+    if (nvalid > 1) r.y = ld_elem(p, i + 1, dt);
+    if (nvalid > 2) r.z = ld_elem(p, i + 2, dt);
+    if (nvalid > 3) r.w = ld_elem(p, i + 3, dt);
+    return r;
+}
+__device__ __forceinline__ void st4(void *p, int64_t i, int dt, bool vec, int nvalid, float4 v) {
+    if (nvalid <= 0) return;
+    if (vec && nvalid >= 4) {
+        if (dt == CS2D_F32) {
+            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(p) + i) = v;
+        } else {
+            uint2 raw;
+            if (dt == CS2D_BF16) {
+                *reinterpret_cast<__nv_bfloat162 *>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+                *reinterpret_cast<__nv_bfloat162 *>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+            } else {
+                *reinterpret_cast<__half2 *>(&raw.x) = __floats2half2_rn(v.x, v.y);
+                *reinterpret_cast<__half2 *>(&raw.y) = __floats2half2_rn(v.z, v.w);
+            }
+            *reinterpret_cast<uint2 *>(reinterpret_cast<uint16_t *>(p) + i) = raw;
+        }
+        return;
+    }
+    st_elem(p, i, dt, v.x);
+    if (nvalid > 1) st_elem(p, i + 1, dt, v.y);
+    if (nvalid > 2) st_elem(p, i + 2, dt, v.z);
+    if (nvalid > 3) st_elem(p, i + 3, dt, v.w);
+}
 
 // softplus with the reference's threshold (fwd kernel :221-224).
 __device__ __forceinline__ float softplus20(float x) { return x <= 20.f ? log1pf(__expf(x)) : x; }
+
+// ---- shared-memory tile layouts ---------------------------------------------------
+// Per-channel float tiles are [channel][row][Wp]; inside a row the 8 columns of
+// strip j are stored as two float4 at 4j and 4L+4j, so the two LDS.128 of the
+// L lanes of a row hit consecutive 16-byte words.  The channel stride is padded
+// so that the CW channel groups of a warp fall on different banks.
+template <int L>
+__host__ __device__ constexpr int chan_stride(int rows) {
+    const int base = rows * L * STRIP;
+    const int want = (4 * L) % 32;
+    return base + ((want - base % 32) + 32) % 32;
+}
+// float offset of the float4 holding columns 4t..4t+3 of a row
+template <int L>
+__device__ __forceinline__ int pos4(int t) { return (t & 1) * (4 * L) + 4 * (t >> 1); }
+// Pair tiles are [slot][row][Wp] float2; the 8 columns of strip j are four
+// float4 (two columns x two states) at float2 offsets k*2L + 2j, k = 0..3.
+template <int L>
+__device__ __forceinline__ int pos2(int c) { return ((c & 7) >> 1) * (2 * L) + 2 * (c >> 3) + (c & 1); }
+
+__device__ __forceinline__ void unpack8(const float *row, int L4, int j, float (&v)[STRIP]) {
+    const float4 a = *reinterpret_cast<const float4 *>(row + 4 * j);
+    const float4 b = *reinterpret_cast<const float4 *>(row + L4 + 4 * j);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void pack8(float *row, int L4, int j, const float (&v)[STRIP]) {
+    *reinterpret_cast<float4 *>(row + 4 * j) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4 *>(row + L4 + 4 * j) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void unpack8x2(const float2 *row, int L2, int j, float2 (&v)[STRIP]) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float4 q = *reinterpret_cast<const float4 *>(row + k * L2 + 2 * j);
+        v[2 * k] = f2(q.x, q.y); v[2 * k + 1] = f2(q.z, q.w);
+    }
+}
 
 // ---- row scans ---------------------------------------------------------------
 // Exclusive carry for a forward (left-to-right) scan of h' = a*h + b across the
@@ -186,6 +285,36 @@ __device__ __forceinline__ void row_forward(int j, const float (&dl)[STRIP], con
         ch = fma2(a[i], ch, beta[i]);
         h[i] = ch;
         if (WITH_S) { cs = fma2(a[i], cs, p[i]); s[i] = cs; }
+    }
+}
+
+// ---- staging shared by both kernels ---------------------------------------------
+// B and C of one row block for every state pair: sB/sC[NPp][RB][Wp] float2.
+template <int L>
+__device__ __forceinline__ void stage_BC(const Dev &P, int b, int g, int r0, int nr, float2 *sB, float2 *sC) {
+    constexpr int Wp = L * STRIP, T4 = Wp / 4;
+    const int items = P.NPp * RB * T4;
+    const int nthr = blockDim.x;
+    for (int it = threadIdx.x; it < items; it += nthr) {
+        const int t = it % T4, rr = (it / T4) % RB, sp = it / (T4 * RB);
+        const int c = 4 * t, n0 = 2 * sp;
+        float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0, c0 = b0, c1 = b0;
+        if (rr < nr && n0 < P.N) {
+            const int r = r0 + rr, nv = P.W - c;
+            const int64_t ob = (int64_t)b * P.B_bs + (int64_t)g * P.B_gs + (int64_t)r * P.B_hs + c;
+            const int64_t oc = (int64_t)b * P.C_bs + (int64_t)g * P.C_gs + (int64_t)r * P.C_hs + c;
+            b0 = ld4(P.B, ob + (int64_t)n0 * P.B_ns, P.io_dt, P.vec & VEC_B, nv);
+            c0 = ld4(P.C, oc + (int64_t)n0 * P.C_ns, P.io_dt, P.vec & VEC_C, nv);
+            if (n0 + 1 < P.N) {
+                b1 = ld4(P.B, ob + (int64_t)(n0 + 1) * P.B_ns, P.io_dt, P.vec & VEC_B, nv);
+                c1 = ld4(P.C, oc + (int64_t)(n0 + 1) * P.C_ns, P.io_dt, P.vec & VEC_C, nv);
+            }
+        }
+        const int base = (sp * RB + rr) * Wp + pos2<L>(c);  // columns c, c+1; c+2, c+3 follow 2L float2 later
+        *reinterpret_cast<float4 *>(sB + base) = make_float4(b0.x, b1.x, b0.y, b1.y);
+        *reinterpret_cast<float4 *>(sB + base + 2 * L) = make_float4(b0.z, b1.z, b0.w, b1.w);
+        *reinterpret_cast<float4 *>(sC + base) = make_float4(c0.x, c1.x, c0.y, c1.y);
+        *reinterpret_cast<float4 *>(sC + base + 2 * L) = make_float4(c0.z, c1.z, c0.w, c1.w);
     }
 }
 

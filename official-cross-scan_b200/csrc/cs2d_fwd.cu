@@ -6,173 +6,217 @@
 //   h(r,c) = a*(h(r,c-1) + h(r-1,c) - 0.5*(a(r-1,c)+a(r,c-1))*h(r-1,c-1)) + p
 //   s(r,c) = a*s(r,c-1) + p
 //   y      = D*u + sum_n C_n*(h_n - s_n + 0.25*p_n)
-// One CTA owns DC channels of one (batch, group); B and C are staged once for
-// all of them.  Every RB-th row of h is written to the saved-state buffer as a
-// checkpoint for the backward pass.
+// One CTA owns CT channels of one (batch, group) and walks them in passes of CP
+// channels per block of RB rows; B and C are staged once per row block for all
+// of them.  The last h row of every block is written to the saved-state buffer:
+// it is the checkpoint the backward starts from and the state this kernel
+// itself reloads when it comes back to the channel for the next row block.
 #include "cs2d_common.cuh"
 
 namespace cs2d {
 
 template <int L>
-__global__ void __launch_bounds__(256) fwd_kernel(const Dev P) {
-    constexpr int Wp = L * STRIP;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int DC = P.DC, NP = P.NP;
-    float *su = reinterpret_cast<float *>(smem_raw);          // [DC][RB][Wp]
-    float *sdl = su + DC * RB * Wp;                           // [DC][RB][Wp]
-    float *sy = sdl + DC * RB * Wp;                           // [DC][RB][Wp]
-    float2 *sB = reinterpret_cast<float2 *>(sy + DC * RB * Wp);  // [NP][RB][Wp]
-    float2 *sC = sB + NP * RB * Wp;                              // [NP][RB][Wp]
+struct FwdSmem {
+    static constexpr int Wp = L * STRIP, CW = 32 / L;
+    static constexpr int CS4 = chan_stride<L>(RB), CS5 = chan_stride<L>(RB + 1);
+    // float offsets
+    static __host__ __device__ constexpr int u(int) { return 0; }
+    static __host__ __device__ constexpr int dl(int CP) { return CP * CS4; }
+    static __host__ __device__ constexpr int y(int CP) { return dl(CP) + CP * CS5; }            // [warps][CW][CS4]
+    static __host__ __device__ constexpr int B(int CP, int nw) { return y(CP) + nw * CW * CS4; }  // float2 tiles
+    static __host__ __device__ constexpr int total(int CP, int NPp, int nw) {
+        return B(CP, nw) + 2 * 2 * NPp * RB * Wp;
+    }
+};
 
-    const int tid = threadIdx.x;
-    const int j = tid & (L - 1);
-    const int q = tid / L;
-    const int pp = q % NP;
-    const int dc = q / NP;
-    const int tile = blockIdx.x % P.ntiles;
-    const int bg = blockIdx.x / P.ntiles;
-    const int g = bg % P.G;
-    const int b = bg / P.G;
-    const int d0 = g * P.dpg + tile * DC;
-    const int dvalid = min(DC, (g + 1) * P.dpg - d0);
-    const int d = d0 + min(dc, dvalid - 1);
-    const bool ch_ok = dc < dvalid;
+template <int L>
+__global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
+    using S = FwdSmem<L>;
+    constexpr int Wp = S::Wp, CW = S::CW, T4 = Wp / 4, CS4 = S::CS4, CS5 = S::CS5, L4 = 4 * L, L2 = 2 * L;
+    extern __shared__ __align__(16) float smem[];
+    const int NPp = P.NPp, CG = P.CG, CP = CG * CW;
+    const int nthr = blockDim.x, nw = nthr >> 5;  // NPp * CG warps
+    float *su = smem + S::u(CP);
+    float *sdl = smem + S::dl(CP);   // row 0 = row above the block
+    float *sy = smem + S::y(CP);     // per-warp partial sums over the warp's state pair
+    float2 *sB = reinterpret_cast<float2 *>(smem + S::B(CP, nw));
+    float2 *sC = sB + NPp * RB * Wp;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int j = lane & (L - 1), cl = lane / L;
+    const int pp = warp % NPp, cg = warp / NPp;
+    const int cp = cg * CW + cl;  // channel slot inside a pass
+    const int tile = blockIdx.x % P.ntiles, bg = blockIdx.x / P.ntiles;
+    const int g = bg % P.G, b = bg / P.G;
+    const int dbase = g * P.dpg + tile * P.CT;
+    const int nch = min(P.CT, (g + 1) * P.dpg - dbase);  // valid channels of this CTA
     const int H = P.H, W = P.W, N = P.N;
-    const int c0 = j * STRIP;
-    const int n0 = 2 * pp, n1 = 2 * pp + 1;
+    const int n0 = 2 * pp, n1 = n0 + 1;
+    const bool pair_on = n0 < N;  // warp-uniform
+    const float lgdv = P.decay ? log2f(__ldg(P.decay)) : 0.f;
+    const float2 lgd = bc(lgdv);
 
-    const float decay = P.decay ? __ldg(P.decay) : 1.f;
-    const float2 lgd = bc(P.decay ? log2f(decay) : 0.f);
-    const float2 A2 = f2(__ldg(P.A + d * P.A_ds + n0 * P.A_ns) * LOG2E,
-                         n1 < N ? __ldg(P.A + d * P.A_ds + n1 * P.A_ns) * LOG2E : 0.f);
+    // the partial tiles of idle pair slots are summed too: keep them zero
+    for (int i = tid; i < nw * CW * CS4; i += nthr) sy[i] = 0.f;
 
-    float2 h_up[STRIP], a_up[STRIP];
-#pragma unroll
-    for (int i = 0; i < STRIP; ++i) { h_up[i] = bc(0.f); a_up[i] = bc(0.f); }
-
-    const int n_in = DC * RB * Wp;   // elements of the per-channel tiles
-    const int n_bc = NP * RB * Wp;   // float2 elements of the B/C tiles
-
-    for (int r0 = 0; r0 < H; r0 += RB) {
-        const int nr = min(RB, H - r0);
-        // ---- write out the previous block's y, then stage this block --------
-        for (int idx = tid; idx < n_in; idx += blockDim.x) {
-            const int c = idx % Wp, rr = (idx / Wp) % RB, sdc = idx / (Wp * RB);
-            const int sd = d0 + sdc;
-            const bool okc = sdc < dvalid && c < W;
-            if (r0 > 0 && okc) {  // previous block always has RB rows
-                const int64_t o = (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + (int64_t)(r0 - RB + rr) * P.o_hs + c;
-                st_elem(P.out, o, P.out_dt, sy[idx]);
-            }
-            float uv = 0.f, dlv = 0.f, yv = 0.f;
-            if (okc && rr < nr) {
-                const int r = r0 + rr;
-                uv = ld_elem(P.u, (int64_t)b * P.u_bs + (int64_t)sd * P.u_ds + (int64_t)r * P.u_hs + c, P.io_dt);
-                const int sdd = sd / P.drep;
-                float x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)r * P.dl_hs + c,
-                                  P.io_dt);
-                if (P.bias) x += __ldg(P.bias + sdd);
-                dlv = P.softplus ? softplus20(x) : x;
-                yv = P.D ? __ldg(P.D + sd) * uv : 0.f;
-            }
-            su[idx] = uv; sdl[idx] = dlv; sy[idx] = yv;
-        }
-        for (int idx = tid; idx < n_bc; idx += blockDim.x) {
-            const int c = idx % Wp, rr = (idx / Wp) % RB, sp = idx / (Wp * RB);
-            float2 bv = bc(0.f), cv = bc(0.f);
-            if (c < W && rr < nr) {
-                const int r = r0 + rr;
-                const int64_t ob = (int64_t)b * P.B_bs + (int64_t)g * P.B_gs + (int64_t)r * P.B_hs + c;
-                const int64_t oc = (int64_t)b * P.C_bs + (int64_t)g * P.C_gs + (int64_t)r * P.C_hs + c;
-                bv.x = ld_elem(P.B, ob + (int64_t)(2 * sp) * P.B_ns, P.io_dt);
-                cv.x = ld_elem(P.C, oc + (int64_t)(2 * sp) * P.C_ns, P.io_dt);
-                if (2 * sp + 1 < N) {
-                    bv.y = ld_elem(P.B, ob + (int64_t)(2 * sp + 1) * P.B_ns, P.io_dt);
-                    cv.y = ld_elem(P.C, oc + (int64_t)(2 * sp + 1) * P.C_ns, P.io_dt);
+    const int nblk = P.nck;
+    const int steps = nblk * P.npass;
+    for (int step = 0; step <= steps; ++step) {
+        const int blk = step / P.npass, pass = step % P.npass;
+        const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
+        const int ch0 = pass * CP;
+        // ---- phase A: write out the previous step, stage this one -------------------
+        {
+            const int pstep = step - 1;
+            const int pblk = pstep / P.npass, ppass = pstep % P.npass;
+            const int pr0 = pblk * RB, pnr = step > 0 ? min(RB, H - pr0) : 0, pch0 = ppass * CP;
+            const int items = CP * RB * T4;
+            for (int it = tid; it < items; it += nthr) {
+                const int t = it % T4, rr = (it / T4) % RB, sc = it / (T4 * RB);
+                const int c = 4 * t, o4 = sc * CS4 + rr * Wp + pos4<L>(t);
+                if (pnr > 0 && rr < pnr && pch0 + sc < nch) {
+                    const int sd = dbase + pch0 + sc;
+                    const int scg = sc / CW, scl = sc % CW;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int q = 0; q < NPp; ++q) {
+                        const float4 v = *reinterpret_cast<const float4 *>(
+                            sy + ((scg * NPp + q) * CW + scl) * CS4 + rr * Wp + pos4<L>(t));
+                        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                    }
+                    if (P.D) {
+                        const float Dv = __ldg(P.D + sd);
+                        const float4 uv = *reinterpret_cast<const float4 *>(su + o4);
+                        acc.x = fmaf(Dv, uv.x, acc.x); acc.y = fmaf(Dv, uv.y, acc.y);
+                        acc.z = fmaf(Dv, uv.z, acc.z); acc.w = fmaf(Dv, uv.w, acc.w);
+                    }
+                    st4(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + (int64_t)(pr0 + rr) * P.o_hs + c,
+                        P.out_dt, P.vec & VEC_OUT, W - c, acc);
                 }
+                float4 uv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (rr < nr && ch0 + sc < nch)
+                    uv = ld4(P.u, (int64_t)b * P.u_bs + (int64_t)(dbase + ch0 + sc) * P.u_ds +
+                                      (int64_t)(r0 + rr) * P.u_hs + c, P.io_dt, P.vec & VEC_U, W - c);
+                *reinterpret_cast<float4 *>(su + o4) = uv;
             }
-            sB[idx] = bv; sC[idx] = cv;
+            if (nr > 0) {
+                const int items5 = CP * (RB + 1) * T4;
+                for (int it = tid; it < items5; it += nthr) {
+                    const int t = it % T4, rr = (it / T4) % (RB + 1), sc = it / (T4 * (RB + 1));
+                    const int c = 4 * t, r = r0 + rr - 1;
+                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (r >= 0 && rr - 1 < nr && ch0 + sc < nch) {
+                        const int sdd = (dbase + ch0 + sc) / P.drep;
+                        x = ld4(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)r * P.dl_hs + c,
+                                P.io_dt, P.vec & VEC_DELTA, W - c);
+                        const float bv = P.bias ? __ldg(P.bias + sdd) : 0.f;
+                        x.x += bv; x.y += bv; x.z += bv; x.w += bv;
+                        if (P.softplus) {
+                            x.x = softplus20(x.x); x.y = softplus20(x.y); x.z = softplus20(x.z); x.w = softplus20(x.w);
+                        }
+                        const int nv = W - c;  // columns past the image keep dl = 0
+                        if (nv < 4) { x.w = 0.f; if (nv < 3) x.z = 0.f; if (nv < 2) x.y = 0.f; if (nv < 1) x.x = 0.f; }
+                    }
+                    *reinterpret_cast<float4 *>(sdl + sc * CS5 + rr * Wp + pos4<L>(t)) = x;
+                }
+                if (pass == 0) stage_BC<L>(P, b, g, r0, nr, sB, sC);
+            }
         }
         __syncthreads();
+        if (nr == 0) break;
 
-        // ---- scan the rows of this block ------------------------------------
-        for (int rr = 0; rr < nr; ++rr) {
-            float dl[STRIP], dlu[STRIP];
-            float2 Bv[STRIP], Cv[STRIP];
-            {
-                const float4 *pu = reinterpret_cast<const float4 *>(su + (dc * RB + rr) * Wp + c0);
-                const float4 *pd = reinterpret_cast<const float4 *>(sdl + (dc * RB + rr) * Wp + c0);
-                const float4 u0 = pu[0], u1 = pu[1], e0 = pd[0], e1 = pd[1];
-                dl[0] = e0.x; dl[1] = e0.y; dl[2] = e0.z; dl[3] = e0.w;
-                dl[4] = e1.x; dl[5] = e1.y; dl[6] = e1.z; dl[7] = e1.w;
-                dlu[0] = e0.x * u0.x; dlu[1] = e0.y * u0.y; dlu[2] = e0.z * u0.z; dlu[3] = e0.w * u0.w;
-                dlu[4] = e1.x * u1.x; dlu[5] = e1.y * u1.y; dlu[6] = e1.z * u1.z; dlu[7] = e1.w * u1.w;
-                const float4 *pb = reinterpret_cast<const float4 *>(sB + (pp * RB + rr) * Wp + c0);
-                const float4 *pc = reinterpret_cast<const float4 *>(sC + (pp * RB + rr) * Wp + c0);
+        // ---- compute: RB rows of CP channels ----------------------------------------
+        if (pair_on) {
+            const bool ch_ok = ch0 + cp < nch;
+            const int d = dbase + min(ch0 + cp, nch - 1);
+            const float2 A2 = f2(__ldg(P.A + d * P.A_ds + n0 * P.A_ns) * LOG2E,
+                                 n1 < N ? __ldg(P.A + d * P.A_ds + n1 * P.A_ns) * LOG2E : 0.f);
+            float2 h_up[STRIP], a_up[STRIP];
+            float2 *ck = P.saved + ((((int64_t)b * P.dim + d) * P.nck + blk) * NPp + pp) * Wp + j * STRIP;
+            if (r0 > 0) {
+                float dlt[STRIP];
+                unpack8(sdl + cp * CS5, L4, j, dlt);
+                const float4 *pk = reinterpret_cast<const float4 *>(ck - (int64_t)NPp * Wp);
 #pragma unroll
                 for (int k = 0; k < STRIP / 2; ++k) {
-                    const float4 bq = pb[k], cq = pc[k];
-                    Bv[2 * k] = f2(bq.x, bq.y); Bv[2 * k + 1] = f2(bq.z, bq.w);
-                    Cv[2 * k] = f2(cq.x, cq.y); Cv[2 * k + 1] = f2(cq.z, cq.w);
+                    const float4 v = ch_ok ? pk[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    h_up[2 * k] = f2(v.x, v.y); h_up[2 * k + 1] = f2(v.z, v.w);
+                }
+#pragma unroll
+                for (int i = 0; i < STRIP; ++i) a_up[i] = ex2_2(fma2(bc(dlt[i]), A2, lgd));
+            } else {
+#pragma unroll
+                for (int i = 0; i < STRIP; ++i) { h_up[i] = bc(0.f); a_up[i] = bc(0.f); }
+            }
+#pragma unroll
+            for (int rr = 0; rr < RB; ++rr) {
+                if (rr < nr) {
+                    float dl[STRIP], uu[STRIP], dlu[STRIP];
+                    float2 Bv[STRIP], Cv[STRIP];
+                    unpack8(su + cp * CS4 + rr * Wp, L4, j, uu);
+                    unpack8(sdl + cp * CS5 + (rr + 1) * Wp, L4, j, dl);
+#pragma unroll
+                    for (int i = 0; i < STRIP; ++i) dlu[i] = dl[i] * uu[i];
+                    unpack8x2(sB + (pp * RB + rr) * Wp, L2, j, Bv);
+                    unpack8x2(sC + (pp * RB + rr) * Wp, L2, j, Cv);
+                    float2 a[STRIP], p[STRIP], h[STRIP], s[STRIP];
+                    row_forward<L, true>(j, dl, dlu, Bv, A2, lgd, h_up, a_up, a, p, h, s);
+                    float yv[STRIP];
+#pragma unroll
+                    for (int i = 0; i < STRIP; ++i) {
+                        // C*(h - s + 0.25 p), summed over the two states of the pair
+                        const float2 t = mul2(Cv[i], fma2(p[i], bc(0.25f), sub2(h[i], s[i])));
+                        yv[i] = t.x + t.y;
+                        h_up[i] = h[i];
+                        a_up[i] = a[i];
+                    }
+                    pack8(sy + (warp * CW + cl) * CS4 + rr * Wp, L4, j, yv);
                 }
             }
-            float2 a[STRIP], p[STRIP], h[STRIP], s[STRIP];
-            row_forward<L, true>(j, dl, dlu, Bv, A2, lgd, h_up, a_up, a, p, h, s);
-            float *yrow = sy + (dc * RB + rr) * Wp + c0;
-#pragma unroll
-            for (int i = 0; i < STRIP; ++i) {
-                // C*(h - s + 0.25 p), summed over the two states of the pair
-                const float2 t = mul2(Cv[i], fma2(p[i], bc(0.25f), sub2(h[i], s[i])));
-                atomicAdd(yrow + i, t.x + t.y);
-                h_up[i] = h[i];
-                a_up[i] = a[i];
-            }
-            const int r = r0 + rr;
-            if (rr == RB - 1 && r + 1 < H && ch_ok) {
-                float4 *ck = reinterpret_cast<float4 *>(
-                    P.saved + ((((int64_t)b * P.dim + d) * P.nck + r / RB) * NP + pp) * Wp + c0);
+            if (r0 + RB < H && ch_ok) {
+                float4 *pk = reinterpret_cast<float4 *>(ck);
 #pragma unroll
                 for (int k = 0; k < STRIP / 2; ++k)
-                    ck[k] = make_float4(h[2 * k].x, h[2 * k].y, h[2 * k + 1].x, h[2 * k + 1].y);
+                    pk[k] = make_float4(h_up[2 * k].x, h_up[2 * k].y, h_up[2 * k + 1].x, h_up[2 * k + 1].y);
             }
         }
         __syncthreads();
-    }
-    // ---- write out the last block -----------------------------------------------
-    const int rl = ((H - 1) / RB) * RB, nl = H - rl;
-    for (int idx = tid; idx < n_in; idx += blockDim.x) {
-        const int c = idx % Wp, rr = (idx / Wp) % RB, sdc = idx / (Wp * RB);
-        if (sdc < dvalid && c < W && rr < nl) {
-            const int64_t o = (int64_t)b * P.o_bs + (int64_t)(d0 + sdc) * P.o_ds + (int64_t)(rl + rr) * P.o_hs + c;
-            st_elem(P.out, o, P.out_dt, sy[idx]);
-        }
     }
 }
 
-size_t fwd_smem_bytes(int L, int DC, int NP) {
-    const int Wp = L * STRIP;
-    return (size_t)(3 * DC * RB * Wp) * 4 + (size_t)(2 * NP * RB * Wp) * 8;
+size_t fwd_smem_bytes(int L, int CG, int NPp) {
+    const int nw = CG * NPp;
+    const int CP = CG * (32 / L);
+    switch (L) {
+        case 1: return (size_t)FwdSmem<1>::total(CP, NPp, nw) * 4;
+        case 2: return (size_t)FwdSmem<2>::total(CP, NPp, nw) * 4;
+        case 4: return (size_t)FwdSmem<4>::total(CP, NPp, nw) * 4;
+        case 8: return (size_t)FwdSmem<8>::total(CP, NPp, nw) * 4;
+        case 16: return (size_t)FwdSmem<16>::total(CP, NPp, nw) * 4;
+        default: return (size_t)FwdSmem<32>::total(CP, NPp, nw) * 4;
+    }
 }
 
 template <int L>
-static cudaError_t launch(const Dev &P, int grid, int threads, size_t smem, cudaStream_t st) {
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(fwd_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) {
+    static bool attr_done = false;  // per template instance; the value only ever grows to the device limit
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(fwd_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
+        attr_done = true;
     }
-    fwd_kernel<L><<<grid, threads, smem, st>>>(P);
+    fwd_kernel<L><<<grid, 32 * P.CG * P.NPp, smem, st>>>(P);
     return cudaGetLastError();
 }
 
-cudaError_t launch_fwd(const Dev &P, int L, int grid, int threads, cudaStream_t st) {
-    const size_t smem = fwd_smem_bytes(L, P.DC, P.NP);
+cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st) {
+    const size_t smem = fwd_smem_bytes(L, P.CG, P.NPp);
     switch (L) {
-        case 1: return launch<1>(P, grid, threads, smem, st);
-        case 2: return launch<2>(P, grid, threads, smem, st);
-        case 4: return launch<4>(P, grid, threads, smem, st);
-        case 8: return launch<8>(P, grid, threads, smem, st);
-        case 16: return launch<16>(P, grid, threads, smem, st);
-        case 32: return launch<32>(P, grid, threads, smem, st);
+        case 1: return launch<1>(P, grid, smem, st);
+        case 2: return launch<2>(P, grid, smem, st);
+        case 4: return launch<4>(P, grid, smem, st);
+        case 8: return launch<8>(P, grid, smem, st);
+        case 16: return launch<16>(P, grid, smem, st);
+        case 32: return launch<32>(P, grid, smem, st);
     }
     return cudaErrorInvalidValue;
 }
