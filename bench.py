@@ -1,0 +1,300 @@
+#!/usr/bin/env python
+"""Benchmark of the 2D-CrossScan selective scan: forward + backward scanned
+elements per second (B*K*D*H*W*N per pass) and the fraction of the HBM roofline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config NAME]
+
+One process per GPU (torchrun for N > 1).  A step is one forward plus one
+backward of the operator over one synthetic batch; with N > 1 every rank owns
+its own batch shard (weak scaling) and the step ends with the single
+all-reduce of the per-channel parameter gradients.  Rank 0 prints one JSON line.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (os.path.join(ROOT, "official-cross-scan_b200"), ROOT):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+METRIC = "fwd+bwd scanned elems/s (B*K*D*H*W*N)"
+UNIT = "elements/s"
+DEFAULT_CONFIG = "c2_vmamba_t_stage1"
+
+
+def load_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def load_traffic(workload):
+    """DRAM bytes per backward launch from the committed ncu capture, if any."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            return json.load(f).get(workload)
+    except Exception:
+        return None
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        mhz, mx, reasons = [], 0, set()
+        for r in self.rows:
+            try:
+                mhz.append(int(r[1])); mx = max(mx, int(r[2]))
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def cpu_port(shape, sample_batch, steps=1):
+    """Times the CPU restatement (float32, all host threads) on `sample_batch` samples."""
+    import torch
+    from cs2d.synthetic import make_inputs, elements
+    from oracle import cs2d_oracle as O
+    import numpy as np
+    B, K, D, N, H, W = shape
+    inp = make_inputs(sample_batch, K, D, N, H, W, dtype=torch.float32, seed=0)
+    a = [inp[k].numpy() if inp[k] is not None else None for k in ("u", "delta", "A", "B", "C", "D", "delta_bias")]
+    dout = inp["dout"].numpy()
+    O.fwd(*[x[:1] if i in (0, 1, 3, 4) else x for i, x in enumerate(a)], True, dtype=np.float32)  # build + warm
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        O.fwd(*a, True, dtype=np.float32)
+        O.bwd(*a, dout, True, dtype=np.float32)
+        times.append(time.perf_counter() - t0)
+    el = elements(sample_batch, K, D, N, H, W)
+    return el / (sum(times) / len(times)), O.max_threads(), sum(times) / len(times)
+
+
+def cpu_sample_size(shape, budget_s):
+    """Samples of the workload the CPU port gets through in about `budget_s` seconds."""
+    from cs2d.synthetic import elements
+    rate, _, _ = cpu_port(shape, 1, 1)
+    per_sample = elements(1, *shape[1:])
+    return int(max(1, min(shape[0], budget_s * rate / per_sample)))
+
+
+def run_reference(args, shape, name):
+    """The reference ships no CPU implementation of this operator (its only
+    implementation is the CUDA extension), so the reference arm times the CPU
+    restatement of its algorithm on the host cores, as a bounded sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    B, K, D, N, H, W = shape
+    for _ in range(args.warmup):
+        cpu_port(shape, 1, 1)
+    sample = cpu_sample_size(shape, budget_s=20.0 / max(1, args.steps))
+    val, cores, sec = cpu_port(shape, sample, max(1, args.steps))
+    what = f"{sample} of {B} samples of {name} per step, float32, OpenMP"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "shape_BKDNHW": list(shape), "sample": what},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": what},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default=DEFAULT_CONFIG)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling captures only)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    from cs2d.synthetic import CONFIGS, algorithmic_bytes, elements, make_inputs
+    B, K, D, N, H, W, dtype = CONFIGS[args.config]
+    if args.batch > 0:
+        B = args.batch
+    shape = (B, K, D, N, H, W)
+    if args.impl == "reference":
+        return run_reference(args, shape, args.config)
+
+    import torch
+    import torch.distributed as dist
+    import cs2d
+    from cs2d import _lib, ops, parallel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    s = 4 if dtype == torch.float32 else 2
+
+    # ---- inputs: generated on the host, pinned, then made resident -----------------
+    host = make_inputs(B, K, D, N, H, W, dtype=dtype, seed=rank)
+    host = {k: (v.pin_memory() if v is not None else None) for k, v in host.items()}
+    d = {k: (v.to(dev, non_blocking=True) if v is not None else None) for k, v in host.items()}
+    torch.cuda.synchronize()
+    fwd_args = lambda t: (t["u"], t["delta"], t["A"], t["B"], t["C"], t["D"], t["delta_bias"], True, False, None)
+
+    def step(t):
+        out, x, xv, xsd = cs2d.fwd(*fwd_args(t))
+        g = parallel.bwd_data_parallel(t["u"], t["delta"], t["A"], t["B"], t["C"], t["D"], t["delta_bias"], t["dout"],
+                                       x, xv, True, None, xsd)
+        return out, g
+
+    def timed(fn, n):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.barrier()
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms)
+
+    # ---- value: inputs resident in HBM ------------------------------------------------
+    for _ in range(args.warmup):
+        step(d)
+    n0 = cs2d.launch_count()
+    with ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local) as clk:
+        ms = timed(lambda: step(d), args.steps)
+    launches = cs2d.launch_count() - n0
+    el_step = elements(B, K, D, N, H, W) * world
+    value = el_step / (ms / args.steps * 1e-3)
+
+    # ---- roofline of the dominant kernel (backward), timed alone on its stream ---------
+    out, x, xv, xsd = cs2d.fwd(*fwd_args(d))
+    L = _lib.lib()
+    p = ops._problem(d["u"], d["delta"], d["A"], d["B"], d["C"], d["D"], d["delta_bias"], None, True, dtype,
+                     "bench")
+    du, dd = torch.empty_like(d["u"]), torch.empty_like(d["u"])
+    dA = torch.zeros(K * D, N, device=dev)
+    dB, dC = torch.zeros_like(d["B"], dtype=torch.float32), torch.zeros_like(d["C"], dtype=torch.float32)
+    dD, dbias = torch.zeros(K * D, device=dev), torch.zeros(K * D, device=dev)
+    scratch = torch.empty(L.cs2d_bwd_scratch_bytes(ctypes.byref(p)) // 4, device=dev)
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def bwd_kernel():
+        rc = L.cs2d_bwd(ctypes.byref(p), vp(d["dout"]), d["dout"].stride(0), d["dout"].stride(1), d["dout"].stride(2),
+                        vp(xv), vp(scratch), vp(du), vp(dd), vp(dA), vp(dB), vp(dC), vp(dD), vp(dbias), None, stream)
+        assert rc == 0, _lib.last_error()
+
+    def fwd_kernel():
+        rc = L.cs2d_fwd(ctypes.byref(p), vp(out), out.stride(0), out.stride(1), out.stride(2), vp(xv), stream)
+        assert rc == 0, _lib.last_error()
+
+    for _ in range(3):
+        bwd_kernel(); fwd_kernel()
+    bwd_ms = timed(bwd_kernel, args.steps) / args.steps
+    fwd_ms = timed(fwd_kernel, args.steps) / args.steps
+    peak, peak_kind = load_peaks()
+    bwd_bytes = algorithmic_bytes(B, K, D, N, H, W, s, fwd=False, bwd=True)
+    fwd_bytes = algorithmic_bytes(B, K, D, N, H, W, s, fwd=True, bwd=False)
+    achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "bwd_kernel", "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
+                "unit": "GB/s", "frac": achieved / peak, "traffic": load_traffic(args.config),
+                "algorithmic_bytes": bwd_bytes, "launch_ms": bwd_ms,
+                "fwd_kernel": {"launch_ms": fwd_ms, "achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
+                               "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},
+                "fwd_plus_bwd_frac": (fwd_bytes + bwd_bytes) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak}
+    del du, dd, dB, dC, scratch
+
+    # ---- end to end: host buffers in, host buffers out, copies inside the timed region ----
+    big = ("u", "delta", "B", "C", "dout")
+    h2d = sum(host[k].numel() * host[k].element_size() for k in big)
+    o, g = step(d)
+    outs = [o, g[0], g[1], g[3], g[4], g[2], g[5], g[6]]
+    hout = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outs]
+    d2h = sum(t.numel() * t.element_size() for t in outs)
+    del o, g, outs
+
+    def e2e_step():
+        t = dict(d)
+        for k in big:
+            t[k] = host[k].to(dev, non_blocking=True)
+        o, g = step(t)
+        for hb, src in zip(hout, [o, g[0], g[1], g[3], g[4], g[2], g[5], g[6]]):
+            hb.copy_(src, non_blocking=True)
+
+    e2e_step()
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    e2e = {"value": el_step / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "ms_per_step": e2e_ms}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sample = cpu_sample_size(shape, budget_s=15.0)
+        val, cores, sec = cpu_port(shape, sample, 1)
+        cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": f"{sample} of {B} samples of {args.config}, float32, OpenMP, {sec:.1f} s"}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.config, "shape_BKDNHW": list(shape), "io_dtype": str(dtype)[6:],
+                       "per_gpu_batch": B, "l2": "inputs larger than L2 (no flush needed)",
+                       "sharding": "batch per rank, one all-reduce of the parameter gradients" if world > 1 else "none"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clk.summary(),
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

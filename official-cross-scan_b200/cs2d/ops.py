@@ -115,11 +115,34 @@ def fwd(u, delta, A, B, C, D_=None, delta_bias_=None, delta_softplus=False, out_
     return [out, x, x_v, x_sd]
 
 
-def bwd(u, delta, A, B, C, D_, delta_bias_, dout, x_, x_v_, delta_softplus, A_decay_=None, x_sd_=None):
+def param_grad_layout(dim, dstate, has_D, has_bias, has_decay):
+    """Offsets of the per-channel parameter gradients inside one flat fp32 buffer.
+
+    ``[dA (dim*dstate) | dD (dim) | ddelta_bias (dim) | dA_decay (1)]`` with absent
+    parts omitted.  These are the only outputs that sum over the batch, so a
+    batch-sharded job all-reduces exactly this buffer (see ``cs2d.parallel``).
+    Returns ``(total, {name: (offset, numel)})``.
+    """
+    parts, off = {}, 0
+    for name, n, on in (("dA", dim * dstate, True), ("dD", dim, has_D), ("ddelta_bias", dim, has_bias),
+                        ("dA_decay", 1, has_decay)):
+        if on:
+            parts[name] = (off, n)
+            off += n
+    return off, parts
+
+
+def bwd(u, delta, A, B, C, D_, delta_bias_, dout, x_, x_v_, delta_softplus, A_decay_=None, x_sd_=None,
+        param_grads=None):
     """Selective nd scan backward.
 
     Returns ``[du, ddelta, dA, dB, dC, dD, ddelta_bias, dA_decay]`` with ``None``
     for the gradients of absent optional inputs.
+
+    ``param_grads`` (not part of the reference signature) may be a zero-filled
+    flat fp32 CUDA tensor of ``param_grad_layout(...)[0]`` elements; dA, dD,
+    ddelta_bias and dA_decay are then views into it, so that one collective can
+    reduce them across ranks without packing copies.
     """
     L = _lib.lib()
     _check(dout.is_cuda, "dout must be a CUDA tensor")
@@ -139,12 +162,23 @@ def bwd(u, delta, A, B, C, D_, delta_bias_, dout, x_, x_v_, delta_softplus, A_de
     with torch.cuda.device(dev):
         du = torch.empty(tuple(u.shape), dtype=u.dtype, device=dev)
         ddelta = torch.empty(tuple(u.shape), dtype=u.dtype, device=dev)
-        dA = torch.zeros(tuple(A.shape), dtype=torch.float32, device=dev)
+        total, parts = param_grad_layout(dim, A.size(1), D_ is not None, delta_bias_ is not None,
+                                         A_decay_ is not None)
+        if param_grads is None:
+            param_grads = torch.zeros(total, dtype=torch.float32, device=dev)
+        _check(param_grads.is_cuda and param_grads.dtype == torch.float32 and param_grads.is_contiguous()
+               and param_grads.numel() == total, "param_grads must be a flat float32 CUDA tensor of the layout size")
+
+        def part(name):
+            if name not in parts:
+                return None
+            off, n = parts[name]
+            return param_grads[off:off + n]
+
+        dA = part("dA").view(dim, A.size(1))
+        dD, ddelta_bias, dA_decay = part("dD"), part("ddelta_bias"), part("dA_decay")
         dB = torch.zeros(tuple(B.shape), dtype=torch.float32, device=dev)
         dC = torch.zeros(tuple(C.shape), dtype=torch.float32, device=dev)
-        dD = torch.zeros(dim, dtype=torch.float32, device=dev) if D_ is not None else None
-        ddelta_bias = torch.zeros(dim, dtype=torch.float32, device=dev) if delta_bias_ is not None else None
-        dA_decay = torch.zeros(1, dtype=torch.float32, device=dev) if A_decay_ is not None else None
         scratch = torch.empty(L.cs2d_bwd_scratch_bytes(ctypes.byref(p)) // 4, dtype=torch.float32, device=dev)
         stream = torch.cuda.current_stream(dev).cuda_stream
         rc = L.cs2d_bwd(ctypes.byref(p), _ptr(dout), dout.stride(0), dout.stride(1), dout.stride(2), _ptr(x_v_),

@@ -39,7 +39,7 @@ struct BwdSmem {
     static __host__ __device__ constexpr int pdu(int CP) { return dl(CP) + CP * CS6; }           // [warps][CW][CS4]
     static __host__ __device__ constexpr int pdd(int CP, int nw) { return pdu(CP) + nw * CW * CS4; }
     static __host__ __device__ constexpr int tr(int CP, int nw) { return pdd(CP, nw) + nw * CW * CS4; }   // [warps][2][256] float2
-    static __host__ __device__ constexpr int aB(int CP, int nw) { return tr(CP, nw) + nw * 1024; }        // [warps][RB][Wp] float2
+    static __host__ __device__ constexpr int aB(int CP, int nw) { return tr(CP, nw) + (CW > 1 ? nw * 1024 : 0); }        // [warps][RB][Wp] float2
     static __host__ __device__ constexpr int aC(int CP, int nw, bool acc) { return aB(CP, nw) + (acc ? nw * RB * Wp * 2 : 0); }
     static __host__ __device__ constexpr int B(int CP, int nw, bool acc) { return aC(CP, nw, acc) + (acc ? nw * RB * Wp * 2 : 0); }  // [NPp][RB][Wp] float2
     static __host__ __device__ constexpr int C(int CP, int NPp, int nw, bool acc) { return B(CP, nw, acc) + NPp * RB * Wp * 2; }
@@ -100,6 +100,22 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
         const int pstep = step - 1;
         const int pblk = nblk - 1 - pstep / npass, ppass = pstep % npass;
         const int pr0 = pblk * RB, pnr = step > 0 ? min(RB, H - pr0) : 0, pch0 = ppass * CP;
+        // The checkpoint row above this block and the adjoint row below it are private
+        // to this thread; fetch them now so that they arrive while phase A runs.
+        float4 ck_pre[STRIP / 2], adj_pre[STRIP / 2];
+        {
+            const bool ok = nr > 0 && pair_on && ch0 + cp < nch;
+            const int dq = dbase + min(ch0 + cp, nch - 1);
+            const float4 *pk = reinterpret_cast<const float4 *>(
+                P.saved + ((((int64_t)b * P.dim + dq) * P.nck + (blk - 1)) * NPp + pp) * Wp + j * STRIP);
+            const float4 *pa = reinterpret_cast<const float4 *>(
+                P.adj + (((int64_t)b * P.dim + dq) * NPp + pp) * Wp + j * STRIP);
+#pragma unroll
+            for (int k = 0; k < STRIP / 2; ++k) {
+                ck_pre[k] = (ok && r0 > 0) ? __ldg(pk + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                adj_pre[k] = (ok && r0 + RB < H) ? pa[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
         // ---- phase A: write out the previous step, stage this one -------------------
         {
             const int items = CP * RB * T4;
@@ -221,29 +237,33 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                                    n1 < N ? __ldg(P.A + d * P.A_ds + n1 * P.A_ns) : 0.f);
             const float2 A2 = mul2(Araw, bc(LOG2E));
             const float *dlc = sdl + cp * CS6;
-            float2 hs[RB + 1][STRIP];  // hs[0] = row above the block
+            // The recomputed h rows are parked in this thread's own slots of the partial
+            // tiles: a row of h (8 x float2) is exactly the size of the du and ddl
+            // partial sums (8 + 8 floats) that replace it once the reverse sweep has
+            // consumed the row.  Only the row above the block stays in registers.
+            float *slot_u = spdu + (warp * CW + cl) * CS4, *slot_d = spdd + (warp * CW + cl) * CS4;
+            float2 htop[STRIP];
             // -- recompute h for the block from the checkpoint row --
             {
-                float2 a_up[STRIP];
+                float2 a_up[STRIP], hprev[STRIP];
                 if (r0 > 0) {
                     float dlt[STRIP];
                     unpack8(dlc, L4, j, dlt);
-                    const float4 *pk = reinterpret_cast<const float4 *>(
-                        P.saved + ((((int64_t)b * P.dim + d) * P.nck + (blk - 1)) * NPp + pp) * Wp + j * STRIP);
 #pragma unroll
                     for (int k = 0; k < STRIP / 2; ++k) {
-                        const float4 v = ch_ok ? __ldg(pk + k) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        hs[0][2 * k] = f2(v.x, v.y); hs[0][2 * k + 1] = f2(v.z, v.w);
+                        htop[2 * k] = f2(ck_pre[k].x, ck_pre[k].y); htop[2 * k + 1] = f2(ck_pre[k].z, ck_pre[k].w);
                     }
 #pragma unroll
                     for (int i = 0; i < STRIP; ++i) a_up[i] = ex2_2(fma2(bc(dlt[i]), A2, lgd));
                 } else {
 #pragma unroll
-                    for (int i = 0; i < STRIP; ++i) { hs[0][i] = bc(0.f); a_up[i] = bc(0.f); }
+                    for (int i = 0; i < STRIP; ++i) { htop[i] = bc(0.f); a_up[i] = bc(0.f); }
                 }
 #pragma unroll
+                for (int i = 0; i < STRIP; ++i) hprev[i] = htop[i];
+#pragma unroll
                 for (int rr = 0; rr < RB; ++rr) {
-                    if (rr < nr) {
+                    {   // rows past the image are staged as zeros and carry zero adjoints
                         float dl[STRIP], uu[STRIP], dlu[STRIP];
                         float2 Bv[STRIP];
                         unpack8(su + cp * CS4 + rr * Wp, L4, j, uu);
@@ -251,10 +271,11 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
 #pragma unroll
                         for (int i = 0; i < STRIP; ++i) dlu[i] = dl[i] * uu[i];
                         unpack8x2(sB + (pp * RB + rr) * Wp, L2, j, Bv);
-                        float2 a[STRIP], p[STRIP], sdummy[STRIP];
-                        row_forward<L, false>(j, dl, dlu, Bv, A2, lgd, hs[rr], a_up, a, p, hs[rr + 1], sdummy);
+                        float2 a[STRIP], p[STRIP], hcur[STRIP], sdummy[STRIP];
+                        row_forward<L, false>(j, dl, dlu, Bv, A2, lgd, hprev, a_up, a, p, hcur, sdummy);
+                        park8x2(slot_u + rr * Wp, slot_d + rr * Wp, L4, j, hcur);
 #pragma unroll
-                        for (int i = 0; i < STRIP; ++i) a_up[i] = a[i];
+                        for (int i = 0; i < STRIP; ++i) { a_up[i] = a[i]; hprev[i] = hcur[i]; }
                     }
                 }
             }
@@ -264,11 +285,9 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
             if (r0 + RB < H) {
                 float dlt[STRIP];
                 unpack8(dlc + (RB + 1) * Wp, L4, j, dlt);
-                const float4 *pk = reinterpret_cast<const float4 *>(adj);
 #pragma unroll
                 for (int k = 0; k < STRIP / 2; ++k) {
-                    const float4 v = ch_ok ? pk[k] : make_float4(0.f, 0.f, 0.f, 0.f);
-                    m_dn[2 * k] = f2(v.x, v.y); m_dn[2 * k + 1] = f2(v.z, v.w);
+                    m_dn[2 * k] = f2(adj_pre[k].x, adj_pre[k].y); m_dn[2 * k + 1] = f2(adj_pre[k].z, adj_pre[k].w);
                 }
 #pragma unroll
                 for (int i = 0; i < STRIP; ++i) a_dn[i] = ex2_2(fma2(bc(dlt[i]), A2, lgd));
@@ -278,9 +297,11 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
             }
             float2 dAacc = bc(0.f);
             // -- reverse sweep over the block --
+            float2 hrow[STRIP], hup[STRIP];
+            fetch8x2(slot_u + (RB - 1) * Wp, slot_d + (RB - 1) * Wp, L4, j, hrow);
 #pragma unroll
             for (int rr = RB - 1; rr >= 0; --rr) {
-                if (rr < nr) {
+                {
                     float dl[STRIP], uu[STRIP], gg[STRIP];
                     float2 Bv[STRIP], Cv[STRIP];
                     unpack8(su + cp * CS4 + rr * Wp, L4, j, uu);
@@ -288,8 +309,12 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                     unpack8(dlc + (rr + 1) * Wp, L4, j, dl);
                     unpack8x2(sB + (pp * RB + rr) * Wp, L2, j, Bv);
                     unpack8x2(sC + (pp * RB + rr) * Wp, L2, j, Cv);
-                    const float2 (&hrow)[STRIP] = hs[rr + 1];
-                    const float2 (&hup)[STRIP] = hs[rr];
+                    if (rr > 0) {
+                        fetch8x2(slot_u + (rr - 1) * Wp, slot_d + (rr - 1) * Wp, L4, j, hup);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < STRIP; ++i) hup[i] = htop[i];
+                    }
                     float2 a[STRIP], p[STRIP], s[STRIP], gC[STRIP];
                     {   // a, p and the plain row scan s (recomputed)
                         float2 Pm = bc(1.f), St = bc(0.f);
@@ -310,7 +335,9 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                     if constexpr (L > 1) {
                         a_r7 = shfl_down2<L>(a[0], 1);
                         mdr7 = shfl_down2<L>(m_dn[0], 1);
-                        if (j == L - 1) { a_r7 = bc(0.f); mdr7 = bc(0.f); }
+                        const bool last = j == L - 1;
+                    a_r7.x = last ? 0.f : a_r7.x; a_r7.y = last ? 0.f : a_r7.y;
+                    mdr7.x = last ? 0.f : mdr7.x; mdr7.y = last ? 0.f : mdr7.y;
                     }
                     float2 bt[STRIP], dh[STRIP], ds[STRIP];
                     {   // reverse scans for dh and ds (shared multipliers a(r,c+1))
@@ -340,8 +367,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                     if constexpr (L > 1) {
                         m_r7 = shfl_down2<L>(m[0], 1);
                         h_l0 = shfl_up2<L>(hrow[STRIP - 1], 1);
-                        if (j == L - 1) m_r7 = bc(0.f);
-                        if (j == 0) h_l0 = bc(0.f);
+                        m_r7.x = j == L - 1 ? 0.f : m_r7.x; m_r7.y = j == L - 1 ? 0.f : m_r7.y;
+                        h_l0.x = j == 0 ? 0.f : h_l0.x; h_l0.y = j == 0 ? 0.f : h_l0.y;
                     }
                     float duv[STRIP], ddv[STRIP];
                     // dB/dC are summed over the warp's CW channels by transposing through
@@ -425,7 +452,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         __syncwarp();
                     }
 #pragma unroll
-                    for (int i = 0; i < STRIP; ++i) { m_dn[i] = m[i]; a_dn[i] = a[i]; }
+                    for (int i = 0; i < STRIP; ++i) { m_dn[i] = m[i]; a_dn[i] = a[i]; hrow[i] = hup[i]; }
                 }
             }
             if (r0 > 0 && ch_ok) {  // park the adjoint row for the block above

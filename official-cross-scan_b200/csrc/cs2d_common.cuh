@@ -185,6 +185,21 @@ __device__ __forceinline__ void pack8(float *row, int L4, int j, const float (&v
     *reinterpret_cast<float4 *>(row + 4 * j) = make_float4(v[0], v[1], v[2], v[3]);
     *reinterpret_cast<float4 *>(row + L4 + 4 * j) = make_float4(v[4], v[5], v[6], v[7]);
 }
+// A row of 8 float2 parked in two float rows (columns 0-3 in `ra`, 4-7 in `rb`).
+__device__ __forceinline__ void park8x2(float *ra, float *rb, int L4, int j, const float2 (&v)[STRIP]) {
+    *reinterpret_cast<float4 *>(ra + 4 * j) = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
+    *reinterpret_cast<float4 *>(ra + L4 + 4 * j) = make_float4(v[2].x, v[2].y, v[3].x, v[3].y);
+    *reinterpret_cast<float4 *>(rb + 4 * j) = make_float4(v[4].x, v[4].y, v[5].x, v[5].y);
+    *reinterpret_cast<float4 *>(rb + L4 + 4 * j) = make_float4(v[6].x, v[6].y, v[7].x, v[7].y);
+}
+__device__ __forceinline__ void fetch8x2(const float *ra, const float *rb, int L4, int j, float2 (&v)[STRIP]) {
+    const float4 a = *reinterpret_cast<const float4 *>(ra + 4 * j);
+    const float4 b = *reinterpret_cast<const float4 *>(ra + L4 + 4 * j);
+    const float4 c = *reinterpret_cast<const float4 *>(rb + 4 * j);
+    const float4 d = *reinterpret_cast<const float4 *>(rb + L4 + 4 * j);
+    v[0] = f2(a.x, a.y); v[1] = f2(a.z, a.w); v[2] = f2(b.x, b.y); v[3] = f2(b.z, b.w);
+    v[4] = f2(c.x, c.y); v[5] = f2(c.z, c.w); v[6] = f2(d.x, d.y); v[7] = f2(d.z, d.w);
+}
 __device__ __forceinline__ void unpack8x2(const float2 *row, int L2, int j, float2 (&v)[STRIP]) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -205,18 +220,25 @@ __device__ __forceinline__ void carry_fwd(int j, float2 P, float2 H, float2 S, f
     } else {
 #pragma unroll
         for (int off = 1; off < L; off <<= 1) {
+            // lanes without a partner 'off' to the left combine with the identity (1, 0): no branch
+            const bool on = j >= off;
             float2 Pp = shfl_up2<L>(P, off);
             float2 Hp = shfl_up2<L>(H, off);
-            float2 Sp = TWO ? shfl_up2<L>(S, off) : bc(0.f);
-            if (j >= off) {
-                H = fma2(P, Hp, H);
-                if (TWO) S = fma2(P, Sp, S);
-                P = mul2(P, Pp);
+            Pp.x = on ? Pp.x : 1.f; Pp.y = on ? Pp.y : 1.f;
+            Hp.x = on ? Hp.x : 0.f; Hp.y = on ? Hp.y : 0.f;
+            H = fma2(P, Hp, H);
+            if (TWO) {
+                float2 Sp = shfl_up2<L>(S, off);
+                Sp.x = on ? Sp.x : 0.f; Sp.y = on ? Sp.y : 0.f;
+                S = fma2(P, Sp, S);
             }
+            P = mul2(P, Pp);
         }
         cH = shfl_up2<L>(H, 1);
         cS = TWO ? shfl_up2<L>(S, 1) : bc(0.f);
-        if (j == 0) { cH = bc(0.f); cS = bc(0.f); }
+        const bool first = j == 0;
+        cH.x = first ? 0.f : cH.x; cH.y = first ? 0.f : cH.y;
+        cS.x = first ? 0.f : cS.x; cS.y = first ? 0.f : cS.y;
     }
 }
 // Same for a reverse (right-to-left) scan: carry = value just right of the strip.
@@ -227,18 +249,24 @@ __device__ __forceinline__ void carry_rev(int j, float2 P, float2 H, float2 S, f
     } else {
 #pragma unroll
         for (int off = 1; off < L; off <<= 1) {
+            const bool on = j + off < L;
             float2 Pp = shfl_down2<L>(P, off);
             float2 Hp = shfl_down2<L>(H, off);
-            float2 Sp = TWO ? shfl_down2<L>(S, off) : bc(0.f);
-            if (j + off < L) {
-                H = fma2(P, Hp, H);
-                if (TWO) S = fma2(P, Sp, S);
-                P = mul2(P, Pp);
+            Pp.x = on ? Pp.x : 1.f; Pp.y = on ? Pp.y : 1.f;
+            Hp.x = on ? Hp.x : 0.f; Hp.y = on ? Hp.y : 0.f;
+            H = fma2(P, Hp, H);
+            if (TWO) {
+                float2 Sp = shfl_down2<L>(S, off);
+                Sp.x = on ? Sp.x : 0.f; Sp.y = on ? Sp.y : 0.f;
+                S = fma2(P, Sp, S);
             }
+            P = mul2(P, Pp);
         }
         cH = shfl_down2<L>(H, 1);
         cS = TWO ? shfl_down2<L>(S, 1) : bc(0.f);
-        if (j == L - 1) { cH = bc(0.f); cS = bc(0.f); }
+        const bool last = j == L - 1;
+        cH.x = last ? 0.f : cH.x; cH.y = last ? 0.f : cH.y;
+        cS.x = last ? 0.f : cS.x; cS.y = last ? 0.f : cS.y;
     }
 }
 
@@ -263,7 +291,7 @@ __device__ __forceinline__ void row_forward(int j, const float (&dl)[STRIP], con
     if constexpr (L > 1) {
         hdiag0 = shfl_up2<L>(h_up[STRIP - 1], 1);
         aleft0 = shfl_up2<L>(a[STRIP - 1], 1);
-        if (j == 0) hdiag0 = bc(0.f);
+        hdiag0.x = j == 0 ? 0.f : hdiag0.x; hdiag0.y = j == 0 ? 0.f : hdiag0.y;
     }
     float2 beta[STRIP];
     float2 P = bc(1.f), Ht = bc(0.f), St = bc(0.f);

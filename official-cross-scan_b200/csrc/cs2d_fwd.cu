@@ -65,6 +65,17 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
         const int blk = step / P.npass, pass = step % P.npass;
         const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
         const int ch0 = pass * CP;
+        // The checkpoint row above this block is private to this thread (it wrote it
+        // when it last had the channel); fetch it now so it arrives during phase A.
+        float4 ck_pre[STRIP / 2];
+        {
+            const bool ok = nr > 0 && r0 > 0 && pair_on && ch0 + cp < nch;
+            const int dq = dbase + min(ch0 + cp, nch - 1);
+            const float4 *pk = reinterpret_cast<const float4 *>(
+                P.saved + ((((int64_t)b * P.dim + dq) * P.nck + (blk - 1)) * NPp + pp) * Wp + j * STRIP);
+#pragma unroll
+            for (int k = 0; k < STRIP / 2; ++k) ck_pre[k] = ok ? pk[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
         // ---- phase A: write out the previous step, stage this one -------------------
         {
             const int pstep = step - 1;
@@ -135,11 +146,9 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
             if (r0 > 0) {
                 float dlt[STRIP];
                 unpack8(sdl + cp * CS5, L4, j, dlt);
-                const float4 *pk = reinterpret_cast<const float4 *>(ck - (int64_t)NPp * Wp);
 #pragma unroll
                 for (int k = 0; k < STRIP / 2; ++k) {
-                    const float4 v = ch_ok ? pk[k] : make_float4(0.f, 0.f, 0.f, 0.f);
-                    h_up[2 * k] = f2(v.x, v.y); h_up[2 * k + 1] = f2(v.z, v.w);
+                    h_up[2 * k] = f2(ck_pre[k].x, ck_pre[k].y); h_up[2 * k + 1] = f2(ck_pre[k].z, ck_pre[k].w);
                 }
 #pragma unroll
                 for (int i = 0; i < STRIP; ++i) a_up[i] = ex2_2(fma2(bc(dlt[i]), A2, lgd));
@@ -149,7 +158,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
             }
 #pragma unroll
             for (int rr = 0; rr < RB; ++rr) {
-                if (rr < nr) {
+                {   // rows past the image are staged as zeros: their results are never written out
                     float dl[STRIP], uu[STRIP], dlu[STRIP];
                     float2 Bv[STRIP], Cv[STRIP];
                     unpack8(su + cp * CS4 + rr * Wp, L4, j, uu);
