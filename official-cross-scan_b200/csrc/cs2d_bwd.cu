@@ -316,48 +316,61 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         for (int i = 0; i < STRIP; ++i) hup[i] = htop[i];
                     }
                     float2 a[STRIP], p[STRIP], s[STRIP], gC[STRIP];
-                    {   // a, p and the plain row scan s (recomputed)
-                        float2 Pm = bc(1.f), St = bc(0.f);
 #pragma unroll
-                        for (int i = 0; i < STRIP; ++i) {
-                            a[i] = ex2_2(fma2(bc(dl[i]), A2, lgd));
-                            p[i] = mul2(Bv[i], bc(dl[i] * uu[i]));
-                            gC[i] = mul2(Cv[i], bc(gg[i]));
-                            St = fma2(a[i], St, p[i]);
-                            Pm = mul2(Pm, a[i]);
-                        }
-                        float2 cs, unused;
-                        carry_fwd<L, false>(j, Pm, St, bc(0.f), cs, unused);
-#pragma unroll
-                        for (int i = 0; i < STRIP; ++i) { cs = fma2(a[i], cs, p[i]); s[i] = cs; }
+                    for (int i = 0; i < STRIP; ++i) {
+                        a[i] = ex2_2(fma2(bc(dl[i]), A2, lgd));
+                        p[i] = mul2(Bv[i], bc(dl[i] * uu[i]));
+                        gC[i] = mul2(Cv[i], bc(gg[i]));
                     }
                     float2 a_r7 = bc(0.f), mdr7 = bc(0.f);  // next lane's first column
                     if constexpr (L > 1) {
                         a_r7 = shfl_down2<L>(a[0], 1);
                         mdr7 = shfl_down2<L>(m_dn[0], 1);
                         const bool last = j == L - 1;
-                    a_r7.x = last ? 0.f : a_r7.x; a_r7.y = last ? 0.f : a_r7.y;
-                    mdr7.x = last ? 0.f : mdr7.x; mdr7.y = last ? 0.f : mdr7.y;
+                        a_r7.x = last ? 0.f : a_r7.x; a_r7.y = last ? 0.f : a_r7.y;
+                        mdr7.x = last ? 0.f : mdr7.x; mdr7.y = last ? 0.f : mdr7.y;
                     }
+                    // Three scans share this row: s forward (recomputed plain row scan), dh and ds
+                    // reverse with multipliers a(r,c+1).  They are independent, so they are folded
+                    // together, each as two 4-column half chains.
                     float2 bt[STRIP], dh[STRIP], ds[STRIP];
-                    {   // reverse scans for dh and ds (shared multipliers a(r,c+1))
-                        float2 Pm = bc(1.f), Dh = bc(0.f), Ds = bc(0.f);
 #pragma unroll
-                        for (int i = STRIP - 1; i >= 0; --i) {
-                            const float2 ar = i < STRIP - 1 ? a[i + 1] : a_r7;
-                            const float2 mdr = i < STRIP - 1 ? m_dn[i + 1] : mdr7;
-                            bt[i] = fma2(mul2(add2(ar, a_dn[i]), mdr), bc(-0.5f), add2(gC[i], m_dn[i]));
-                            Dh = fma2(ar, Dh, bt[i]);
-                            Ds = fma2(ar, Ds, neg2(gC[i]));
-                            Pm = mul2(Pm, ar);
+                    for (int i = 0; i < STRIP; ++i) {
+                        const float2 ar = i < STRIP - 1 ? a[i + 1] : a_r7;
+                        const float2 mdr = i < STRIP - 1 ? m_dn[i + 1] : mdr7;
+                        bt[i] = fma2(mul2(add2(ar, a_dn[i]), mdr), bc(-0.5f), add2(gC[i], m_dn[i]));
+                    }
+                    {
+                        constexpr int HS = STRIP / 2;
+                        // forward halves: columns 0..3 and 4..7; reverse halves: 7..4 and 3..0
+                        float2 Pf0 = a[0], Pf1 = a[HS], S0 = p[0], S1 = p[HS];
+                        float2 Pr0 = a_r7, Pr1 = a[HS], H0 = bt[STRIP - 1], H1 = bt[HS - 1];
+                        float2 D0 = neg2(gC[STRIP - 1]), D1 = neg2(gC[HS - 1]);
+#pragma unroll
+                        for (int k = 1; k < HS; ++k) {
+                            S0 = fma2(a[k], S0, p[k]); Pf0 = mul2(Pf0, a[k]);
+                            S1 = fma2(a[HS + k], S1, p[HS + k]); Pf1 = mul2(Pf1, a[HS + k]);
+                            const float2 ar0 = a[STRIP - k];  // multiplier of column 7-k is a of column 8-k
+                            const float2 ar1 = a[HS - k];
+                            H0 = fma2(ar0, H0, bt[STRIP - 1 - k]); D0 = fma2(ar0, D0, neg2(gC[STRIP - 1 - k]));
+                            H1 = fma2(ar1, H1, bt[HS - 1 - k]); D1 = fma2(ar1, D1, neg2(gC[HS - 1 - k]));
+                            Pr0 = mul2(Pr0, ar0); Pr1 = mul2(Pr1, ar1);
                         }
-                        float2 cdh, cds;
-                        carry_rev<L, true>(j, Pm, Dh, Ds, cdh, cds);
+                        float2 cs, unused, cdh, cds;
+                        carry_fwd<L, false>(j, mul2(Pf0, Pf1), fma2(Pf1, S0, S1), bc(0.f), cs, unused);
+                        carry_rev<L, true>(j, mul2(Pr0, Pr1), fma2(Pr1, H0, H1), fma2(Pr1, D0, D1), cdh, cds);
+                        float2 cs1 = fma2(Pf0, cs, S0);                           // into columns 4..7
+                        float2 cdh1 = fma2(Pr0, cdh, H0), cds1 = fma2(Pr0, cds, D0);  // into columns 3..0
 #pragma unroll
-                        for (int i = STRIP - 1; i >= 0; --i) {
-                            const float2 ar = i < STRIP - 1 ? a[i + 1] : a_r7;
-                            cdh = fma2(ar, cdh, bt[i]); dh[i] = cdh;
-                            cds = fma2(ar, cds, neg2(gC[i])); ds[i] = cds;
+                        for (int k = 0; k < HS; ++k) {
+                            cs = fma2(a[k], cs, p[k]); s[k] = cs;
+                            cs1 = fma2(a[HS + k], cs1, p[HS + k]); s[HS + k] = cs1;
+                            const float2 ar0 = k ? a[STRIP - k] : a_r7;
+                            const float2 ar1 = a[HS - k];
+                            cdh = fma2(ar0, cdh, bt[STRIP - 1 - k]); dh[STRIP - 1 - k] = cdh;
+                            cds = fma2(ar0, cds, neg2(gC[STRIP - 1 - k])); ds[STRIP - 1 - k] = cds;
+                            cdh1 = fma2(ar1, cdh1, bt[HS - 1 - k]); dh[HS - 1 - k] = cdh1;
+                            cds1 = fma2(ar1, cds1, neg2(gC[HS - 1 - k])); ds[HS - 1 - k] = cds1;
                         }
                     }
                     float2 m[STRIP];

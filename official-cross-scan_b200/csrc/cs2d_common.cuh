@@ -293,8 +293,9 @@ __device__ __forceinline__ void row_forward(int j, const float (&dl)[STRIP], con
         aleft0 = shfl_up2<L>(a[STRIP - 1], 1);
         hdiag0.x = j == 0 ? 0.f : hdiag0.x; hdiag0.y = j == 0 ? 0.f : hdiag0.y;
     }
+    // Each strip is folded as two independent 4-column halves so that the serial
+    // chains are half as long and twice as many (h and s, low and high half).
     float2 beta[STRIP];
-    float2 P = bc(1.f), Ht = bc(0.f), St = bc(0.f);
 #pragma unroll
     for (int i = 0; i < STRIP; ++i) {
         const float2 al = i ? a[i - 1] : aleft0;
@@ -302,17 +303,28 @@ __device__ __forceinline__ void row_forward(int j, const float (&dl)[STRIP], con
         const float2 t = mul2(add2(a_up[i], al), hd);
         const float2 kappa = fma2(t, bc(-0.5f), h_up[i]);
         beta[i] = fma2(a[i], kappa, p[i]);
-        Ht = fma2(a[i], Ht, beta[i]);
-        if (WITH_S) St = fma2(a[i], St, p[i]);
-        P = mul2(P, a[i]);
+    }
+    constexpr int HS = STRIP / 2;
+    float2 P0 = a[0], P1 = a[HS], H0 = beta[0], H1 = beta[HS], S0 = p[0], S1 = p[HS];
+#pragma unroll
+    for (int i = 1; i < HS; ++i) {
+        H0 = fma2(a[i], H0, beta[i]);
+        H1 = fma2(a[HS + i], H1, beta[HS + i]);
+        if (WITH_S) { S0 = fma2(a[i], S0, p[i]); S1 = fma2(a[HS + i], S1, p[HS + i]); }
+        P0 = mul2(P0, a[i]);
+        P1 = mul2(P1, a[HS + i]);
     }
     float2 ch, cs;
-    carry_fwd<L, WITH_S>(j, P, Ht, St, ch, cs);
+    carry_fwd<L, WITH_S>(j, mul2(P0, P1), fma2(P1, H0, H1), WITH_S ? fma2(P1, S0, S1) : bc(0.f), ch, cs);
+    float2 ch1 = fma2(P0, ch, H0), cs1 = WITH_S ? fma2(P0, cs, S0) : bc(0.f);  // carries into the high half
 #pragma unroll
-    for (int i = 0; i < STRIP; ++i) {
-        ch = fma2(a[i], ch, beta[i]);
-        h[i] = ch;
-        if (WITH_S) { cs = fma2(a[i], cs, p[i]); s[i] = cs; }
+    for (int i = 0; i < HS; ++i) {
+        ch = fma2(a[i], ch, beta[i]); h[i] = ch;
+        ch1 = fma2(a[HS + i], ch1, beta[HS + i]); h[HS + i] = ch1;
+        if (WITH_S) {
+            cs = fma2(a[i], cs, p[i]); s[i] = cs;
+            cs1 = fma2(a[HS + i], cs1, p[HS + i]); s[HS + i] = cs1;
+        }
     }
 }
 
