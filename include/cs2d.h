@@ -114,6 +114,16 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
              const void *saved, void *scratch, void *du, void *ddelta, float *dA, float *dB, float *dC,
              float *dD, float *ddelta_bias, float *dA_decay, void *stream);
 
+/*
+ * Reads and clears the device-side status word of the current device
+ * (synchronises with the device).  0 = no kernel reported a problem; nonzero =
+ * a kernel gave up on a bounded wait for one of its asynchronous copies and
+ * returned early, so the outputs of the calls since the last check are invalid
+ * (cs2d_last_error() then describes it).  Negative: the query itself failed.
+ * The reference has no counterpart; its kernels contain no waits.
+ */
+int cs2d_device_status(void);
+
 /* Message of the last failure on the calling thread ("" if none). */
 const char *cs2d_last_error(void);
 

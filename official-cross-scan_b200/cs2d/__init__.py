@@ -4,4 +4,4 @@ Drop-in for the ``fwd`` / ``bwd`` operators of the reference CUDA extension
 ``selective_nd_scan_cuda_oflex`` plus an autograd Function.
 """
 from .ops import SelectiveScan2D, bwd, fwd, selective_scan_2d  # noqa: F401
-from ._lib import LIB_PATH, build, launch_count  # noqa: F401
+from ._lib import LIB_PATH, build, device_status, launch_count  # noqa: F401

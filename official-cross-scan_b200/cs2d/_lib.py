@@ -58,6 +58,7 @@ def lib():
         L.cs2d_last_error.restype = ctypes.c_char_p
         L.cs2d_abi_version.restype = ctypes.c_int
         L.cs2d_launch_count.restype = ctypes.c_int64
+        L.cs2d_device_status.restype = ctypes.c_int
         if L.cs2d_abi_version() != 1:
             raise RuntimeError("cs2d: ABI version mismatch between libcs2d.so and the Python binding")
         _lib = L
@@ -66,6 +67,11 @@ def lib():
 
 def last_error() -> str:
     return lib().cs2d_last_error().decode()
+
+
+def device_status() -> int:
+    """Reads and clears the device status word (0 = fine); synchronises."""
+    return int(lib().cs2d_device_status())
 
 
 def launch_count() -> int:

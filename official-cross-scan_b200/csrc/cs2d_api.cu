@@ -11,8 +11,19 @@
 namespace cs2d {
 cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st);
 cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st);
-size_t fwd_smem_bytes(int L, int CG, int NPp);
-size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc);
+size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk);
+size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk);
+static __device__ int g_cs2d_status = 0;  // see ERR_* in cs2d_common.cuh
+
+// Device address of the status word on the current device (looked up once per device).
+static int *status_ptr() {
+    static int *ptr[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptr[dev] && cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr[dev]), g_cs2d_status) != cudaSuccess)
+        ptr[dev] = nullptr;
+    return ptr[dev];
+}
 
 static thread_local char g_err[512] = "";
 static std::atomic<int64_t> g_launches{0};
@@ -25,13 +36,14 @@ static int fail(int code, const char *fmt, ...) {
     return code;
 }
 
-struct Geometry { int L, NPp, CG, CP, CT, npass, ntiles, grid, nck, acc; };
+struct Geometry { int L, NPp, CG, CP, CT, npass, ntiles, grid, nck, acc, bulk; };
 
 static const size_t kMaxSmem = 227 * 1024;
 static const int kSMs = 148;
 
 // Lanes per row, state-pair slots, channels per pass and per CTA, and the grid.
-static int plan(const cs2d_problem *p, bool backward, Geometry *g) {
+static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, Geometry *g) {
+    const int W = p->ncols, es = p->io_dtype == CS2D_F32 ? 4 : 2, eso = p->out_dtype == CS2D_F32 ? 4 : 2;
     const int strips = (p->ncols + STRIP - 1) / STRIP;
     int L = 1;
     while (L < strips) L <<= 1;
@@ -44,7 +56,8 @@ static int plan(const cs2d_problem *p, bool backward, Geometry *g) {
     // Channel groups per pass: fill the CTA up to 8 warps, but keep the staged
     // per-channel tiles small enough that the shared memory fits.
     int CG = MAX_WARPS / NPp;
-    while (CG > 1 && (backward ? bwd_smem_bytes(L, CG, NPp, CG * (32 / L), false) : 2 * fwd_smem_bytes(L, CG, NPp)) > kMaxSmem)
+    while (CG > 1 && (backward ? bwd_smem_bytes(L, CG, NPp, CG * (32 / L), false, W, es, eso, false)
+                               : 2 * fwd_smem_bytes(L, CG, NPp, W, es, false)) > kMaxSmem)
         CG >>= 1;
     const int CP = CG * (32 / L);
     const int pmax = (dpg + CP - 1) / CP;  // passes that cover a whole group
@@ -62,15 +75,20 @@ static int plan(const cs2d_problem *p, bool backward, Geometry *g) {
         if (eff > best) { best = eff; npass = np; }
     }
     g->acc = 1;
+    g->bulk = bulk_ok ? 1 : 0;
     if (backward) {
-        if (bwd_smem_bytes(L, CG, NPp, npass * CP, true) > kMaxSmem) g->acc = 0;
-        while (npass > 1 && bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc) > kMaxSmem) --npass;
-        if (bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc) > kMaxSmem)
+        // drop, in this order, the bulk staging buffers, then the dB/dC accumulators, then passes
+        if (bwd_smem_bytes(L, CG, NPp, npass * CP, true, W, es, eso, g->bulk) > kMaxSmem) g->bulk = 0;
+        if (bwd_smem_bytes(L, CG, NPp, npass * CP, true, W, es, eso, false) > kMaxSmem) g->acc = 0;
+        while (npass > 1 && bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false) > kMaxSmem) --npass;
+        if (bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false) > kMaxSmem)
             return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d with dstate=%d needs more shared memory than one SM has",
                         p->ncols, p->dstate);
-    } else if (fwd_smem_bytes(L, CG, NPp) > kMaxSmem) {
-        return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d with dstate=%d needs more shared memory than one SM has",
-                    p->ncols, p->dstate);
+    } else {
+        if (2 * fwd_smem_bytes(L, CG, NPp, W, es, g->bulk) > kMaxSmem) g->bulk = 0;  // keep two CTAs per SM
+        if (fwd_smem_bytes(L, CG, NPp, W, es, false) > kMaxSmem)
+            return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d with dstate=%d needs more shared memory than one SM has",
+                        p->ncols, p->dstate);
     }
     g->L = L; g->NPp = NPp; g->CG = CG; g->CP = CP; g->npass = npass; g->CT = npass * CP;
     g->ntiles = (dpg + g->CT - 1) / g->CT;
@@ -108,11 +126,19 @@ static bool vec_ok(const void *ptr, int esize, int ncols, std::initializer_list<
 }
 static int esize(int dt) { return dt == CS2D_F32 ? 4 : 2; }
 
+// A (batch, channel, nrows, ncols) tensor can be fetched with bulk copies of whole
+// row blocks when its rows are 16-byte multiples, rows of a plane are contiguous,
+// and the base address and the plane/batch strides are 16-byte multiples.
+static bool bulk_ok1(const void *ptr, int es, int ncols, int64_t bs, int64_t ds, int64_t hs) {
+    return ptr && (ncols * es) % 16 == 0 && hs == ncols && reinterpret_cast<uintptr_t>(ptr) % 16 == 0 &&
+           (bs * es) % 16 == 0 && (ds * es) % 16 == 0;
+}
+
 static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     d.batch = p->batch; d.dim = p->dim; d.H = p->nrows; d.W = p->ncols; d.N = p->dstate; d.G = p->n_groups;
     d.ddim = p->delta_dim; d.io_dt = p->io_dtype; d.out_dt = p->out_dtype; d.softplus = p->delta_softplus;
     d.dpg = p->dim / p->n_groups; d.drep = p->dim / p->delta_dim;
-    d.acc_dbc = g.acc; d.NPp = g.NPp; d.CG = g.CG; d.CT = g.CT; d.npass = g.npass; d.ntiles = g.ntiles; d.nck = g.nck;
+    d.acc_dbc = g.acc; d.bulk = g.bulk; d.NPp = g.NPp; d.CG = g.CG; d.CT = g.CT; d.npass = g.npass; d.ntiles = g.ntiles; d.nck = g.nck;
     d.u = p->u; d.delta = p->delta; d.B = p->B; d.C = p->C; d.A = p->A; d.D = p->D; d.bias = p->delta_bias;
     d.decay = p->A_decay;
     d.u_bs = p->u_bs; d.u_ds = p->u_ds; d.u_hs = p->u_hs;
@@ -127,6 +153,7 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     if (vec_ok(p->B, es, p->ncols, {p->B_bs, p->B_gs, p->B_ns, p->B_hs})) d.vec |= VEC_B;
     if (vec_ok(p->C, es, p->ncols, {p->C_bs, p->C_gs, p->C_ns, p->C_hs})) d.vec |= VEC_C;
     d.adj = nullptr;
+    d.status = nullptr;
     d.du = d.ddelta = nullptr; d.dA = d.dB = d.dC = d.dD = d.dbias = d.ddecay = nullptr;
 }
 }  // namespace cs2d
@@ -137,13 +164,13 @@ extern "C" {
 
 size_t cs2d_saved_bytes(const cs2d_problem *p) {
     Geometry g;
-    if (validate(p) != CS2D_OK || plan(p, false, &g) != CS2D_OK) return 0;
+    if (validate(p) != CS2D_OK || plan(p, false, false, &g) != CS2D_OK) return 0;
     return (size_t)p->batch * p->dim * g.nck * g.NPp * (g.L * STRIP) * sizeof(float2);
 }
 
 size_t cs2d_bwd_scratch_bytes(const cs2d_problem *p) {
     Geometry g;
-    if (validate(p) != CS2D_OK || plan(p, true, &g) != CS2D_OK) return 0;
+    if (validate(p) != CS2D_OK || plan(p, true, false, &g) != CS2D_OK) return 0;
     return (size_t)p->batch * p->dim * g.NPp * (g.L * STRIP) * sizeof(float2);
 }
 
@@ -154,12 +181,16 @@ int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, i
     if (!out || !saved) return fail(CS2D_ERR_INVALID, "out and saved must be given");
     if (reinterpret_cast<uintptr_t>(saved) & 15) return fail(CS2D_ERR_INVALID, "saved must be 16-byte aligned");
     Geometry g;
-    if ((rc = plan(p, false, &g))) return rc;
+    const int es = esize(p->io_dtype);
+    const bool bulk = bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
+                      bulk_ok1(p->delta, es, p->ncols, p->delta_bs, p->delta_ds, p->delta_hs);
+    if ((rc = plan(p, false, bulk, &g))) return rc;
     Dev d;
     fill(d, p, g);
     d.out = out; d.o_bs = out_bs; d.o_ds = out_ds; d.o_hs = out_hs;
     if (vec_ok(out, esize(p->out_dtype), p->ncols, {out_bs, out_ds, out_hs})) d.vec |= VEC_OUT;
     d.saved = reinterpret_cast<float2 *>(saved);
+    if (!(d.status = status_ptr())) return fail(CS2D_ERR_CUDA, "cannot locate the device status word");
     cudaError_t e = launch_fwd(d, g.L, g.grid, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
     g_launches.fetch_add(1);
@@ -177,7 +208,11 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
         return fail(CS2D_ERR_INVALID, "saved and scratch must be 16-byte aligned");
     if (dA_decay && !p->A_decay) return fail(CS2D_ERR_INVALID, "dA_decay requested without A_decay");
     Geometry g;
-    if ((rc = plan(p, true, &g))) return rc;
+    const int es = esize(p->io_dtype);
+    const bool bulk = bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
+                      bulk_ok1(p->delta, es, p->ncols, p->delta_bs, p->delta_ds, p->delta_hs) &&
+                      bulk_ok1(dout, esize(p->out_dtype), p->ncols, dout_bs, dout_ds, dout_hs);
+    if ((rc = plan(p, true, bulk, &g))) return rc;
     Dev d;
     fill(d, p, g);
     d.out = const_cast<void *>(dout); d.o_bs = dout_bs; d.o_ds = dout_ds; d.o_hs = dout_hs;
@@ -188,10 +223,21 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
     d.adj = reinterpret_cast<float2 *>(scratch);
     d.du = du; d.ddelta = ddelta; d.dA = dA; d.dB = dB; d.dC = dC; d.dD = dD; d.dbias = ddelta_bias;
     d.ddecay = dA_decay;
+    if (!(d.status = status_ptr())) return fail(CS2D_ERR_CUDA, "cannot locate the device status word");
     cudaError_t e = launch_bwd(d, g.L, g.grid, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
     g_launches.fetch_add(1);
     return CS2D_OK;
+}
+
+int cs2d_device_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_cs2d_status, sizeof(int)) != cudaSuccess) return CS2D_ERR_CUDA;
+    if (v != 0) {
+        cudaMemcpyToSymbol(g_cs2d_status, &zero, sizeof(int));
+        fail(CS2D_ERR_CUDA, "a kernel gave up waiting for a bulk copy (status %d); its outputs are invalid", v);
+    }
+    return v;
 }
 
 const char *cs2d_last_error(void) { return g_err; }

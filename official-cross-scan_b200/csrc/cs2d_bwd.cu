@@ -93,6 +93,42 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
 
     const int nblk = P.nck, npass = P.npass;
     const int steps = nblk * npass;
+
+    // Bulk asynchronous staging: the raw row blocks of u, dout and delta of step k+1
+    // are copied global -> shared by the copy engine while step k computes; an
+    // mbarrier per stage counts the bytes.  One thread issues, everybody waits (bounded).
+    const bool bulk = P.bulk != 0;
+    const int es = P.io_dt == CS2D_F32 ? 4 : 2, eso = P.out_dt == CS2D_F32 ? 4 : 2;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + ((S::total(CP, NPp, CT, nw, acc_on) + 3) & ~3));
+    unsigned char *raw = reinterpret_cast<unsigned char *>(bars + 2);
+    const int stage_bytes = CP * W * (RB * es + RB * eso + (RB + 2) * es);
+    auto issue = [&](int k) {
+        const int kblk = nblk - 1 - k / npass, kpass = k % npass;
+        const int kr0 = kblk * RB, knr = min(RB, H - kr0), kch0 = kpass * CP;
+        const int lo = max(kr0 - 1, 0), hi = min(kr0 + knr + 1, H);
+        const int nv = max(0, min(CP, nch - kch0));
+        uint64_t *bar = bars + (k & 1);
+        unsigned char *ru = raw + (size_t)(k & 1) * stage_bytes, *rg = ru + (size_t)CP * RB * W * es;
+        unsigned char *rd = rg + (size_t)CP * RB * W * eso;
+        mbar_expect_tx(bar, (uint32_t)(nv * W * (knr * es + knr * eso + (hi - lo) * es)));
+        for (int sc = 0; sc < nv; ++sc) {
+            const int sd = dbase + kch0 + sc, sdd = sd / P.drep;
+            const char *srcu = reinterpret_cast<const char *>(P.u) +
+                               ((int64_t)b * P.u_bs + (int64_t)sd * P.u_ds + (int64_t)kr0 * W) * es;
+            const char *srcg = reinterpret_cast<const char *>(P.out) +
+                               ((int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + (int64_t)kr0 * W) * eso;
+            const char *srcd = reinterpret_cast<const char *>(P.delta) +
+                               ((int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)lo * W) * es;
+            bulk_g2s(ru + (size_t)sc * RB * W * es, srcu, (uint32_t)(knr * W * es), bar);
+            bulk_g2s(rg + (size_t)sc * RB * W * eso, srcg, (uint32_t)(knr * W * eso), bar);
+            bulk_g2s(rd + (size_t)sc * (RB + 2) * W * es, srcd, (uint32_t)((hi - lo) * W * es), bar);
+        }
+    };
+    if (bulk) {
+        if (tid == 0) { mbar_init(bars, 1); mbar_init(bars + 1, 1); mbar_init_fence(); }
+        __syncthreads();
+        if (tid == 0 && steps > 0) issue(0);
+    }
     for (int step = 0; step <= steps; ++step) {
         const int blk = nblk - 1 - step / npass, pass = step % npass;  // bottom-up
         const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
@@ -117,7 +153,20 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
             }
         }
         // ---- phase A: write out the previous step, stage this one -------------------
+        if (bulk) {
+            if (tid == 0 && step + 1 < steps) issue(step + 1);   // lands while this step computes
+            bool ok = nr == 0 || mbar_wait_bounded(bars + (step & 1), (step >> 1) & 1);
+            if (__syncthreads_or(!ok)) {  // give up: flag it, drain the other stage, leave
+                if (tid == 0) atomicOr(P.status, ERR_BULK_COPY_TIMEOUT);
+                if (step + 1 < steps) mbar_wait_bounded(bars + ((step + 1) & 1), ((step + 1) >> 1) & 1);
+                return;
+            }
+        }
         {
+            const unsigned char *raw_u = raw + (size_t)(step & 1) * stage_bytes;
+            const unsigned char *raw_g = raw_u + (size_t)CP * RB * W * es;
+            const unsigned char *raw_dl = raw_g + (size_t)CP * RB * W * eso;
+            const int lo = max(r0 - 1, 0);
             const int items = CP * RB * T4;
             for (int it = tid; it < items; it += nthr) {
                 const int t = it % T4, rr = (it / T4) % RB, sc = it / (T4 * RB);
@@ -161,46 +210,46 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         atomicAdd(sred + 2 * (pch0 + sc) + 1, dbp);
                     }
                 }
-                float4 uv = make_float4(0.f, 0.f, 0.f, 0.f), gv = uv;
-                if (rr < nr && ch0 + sc < nch) {
-                    const int sd = dbase + ch0 + sc, r = r0 + rr;
-                    uv = ld4(P.u, (int64_t)b * P.u_bs + (int64_t)sd * P.u_ds + (int64_t)r * P.u_hs + c, P.io_dt,
-                             P.vec & VEC_U, W - c);
-                    gv = ld4(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + (int64_t)r * P.o_hs + c, P.out_dt,
-                             P.vec & VEC_OUT, W - c);
+                // stage this step's u, dout, delta (row rr) for the same item: the thread that
+                // read the old tile entries above is the one that replaces them
+                float4 uv = make_float4(0.f, 0.f, 0.f, 0.f), gv = uv, xv = uv, sv = uv;
+                if (rr < nr && ch0 + sc < nch && c < W) {
+                    const int sd = dbase + ch0 + sc, r = r0 + rr, sdd = sd / P.drep;
+                    if (bulk) {
+                        uv = lds4(raw_u, (sc * RB + rr) * W + c, P.io_dt);
+                        gv = lds4(raw_g, (sc * RB + rr) * W + c, P.out_dt);
+                        xv = lds4(raw_dl, (sc * (RB + 2) + (r - lo)) * W + c, P.io_dt);
+                    } else {
+                        uv = ld4(P.u, (int64_t)b * P.u_bs + (int64_t)sd * P.u_ds + (int64_t)r * P.u_hs + c, P.io_dt,
+                                 P.vec & VEC_U, W - c);
+                        gv = ld4(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + (int64_t)r * P.o_hs + c,
+                                 P.out_dt, P.vec & VEC_OUT, W - c);
+                        xv = ld4(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)r * P.dl_hs + c,
+                                 P.io_dt, P.vec & VEC_DELTA, W - c);
+                    }
+                    soft4(xv, sv, P.bias ? __ldg(P.bias + sdd) : 0.f, P.softplus, W - c);
                 }
                 *reinterpret_cast<float4 *>(su + o4) = uv;
                 *reinterpret_cast<float4 *>(sg + o4) = gv;
+                *reinterpret_cast<float4 *>(ssig + o4) = sv;
+                *reinterpret_cast<float4 *>(sdl + sc * CS6 + (rr + 1) * Wp + pos4<L>(t)) = xv;
             }
-            __syncthreads();  // the write-out above read ssig; the loop below refills it item by item
-            if (nr > 0) {
-                const int items6 = CP * (RB + 2) * T4;
-                for (int it = tid; it < items6; it += nthr) {
-                    const int t = it % T4, rr = (it / T4) % (RB + 2), sc = it / (T4 * (RB + 2));
-                    const int c = 4 * t, r = r0 + rr - 1;
-                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), sg4 = x;
-                    // rows r0-1 .. r0+nr (the row below the block only if it exists)
-                    if (r >= 0 && r < H && rr - 1 <= nr && ch0 + sc < nch) {
+            if (nr > 0) {  // delta of the rows just above and just below the block
+                const int itemsH = CP * 2 * T4;
+                for (int it = tid; it < itemsH; it += nthr) {
+                    const int t = it % T4, which = (it / T4) & 1, sc = it / (T4 * 2);
+                    const int c = 4 * t, rr = which ? RB + 1 : 0, r = r0 + rr - 1;
+                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), unused = x;
+                    if (r >= 0 && r < H && rr - 1 <= nr && ch0 + sc < nch && c < W) {
                         const int sdd = (dbase + ch0 + sc) / P.drep;
-                        x = ld4(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)r * P.dl_hs + c,
-                                P.io_dt, P.vec & VEC_DELTA, W - c);
-                        const float bv = P.bias ? __ldg(P.bias + sdd) : 0.f;
-                        float xs[4] = {x.x + bv, x.y + bv, x.z + bv, x.w + bv}, sgs[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            sgs[e] = 1.f;
-                            if (P.softplus && xs[e] <= 20.f) {
-                                sgs[e] = 1.f / (1.f + __expf(-xs[e]));
-                                xs[e] = log1pf(__expf(xs[e]));
-                            }
-                            if (c + e >= W) { xs[e] = 0.f; sgs[e] = 0.f; }
-                        }
-                        x = make_float4(xs[0], xs[1], xs[2], xs[3]);
-                        sg4 = make_float4(sgs[0], sgs[1], sgs[2], sgs[3]);
+                        if (bulk)
+                            x = lds4(raw_dl, (sc * (RB + 2) + (r - lo)) * W + c, P.io_dt);
+                        else
+                            x = ld4(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)r * P.dl_hs + c,
+                                    P.io_dt, P.vec & VEC_DELTA, W - c);
+                        soft4(x, unused, P.bias ? __ldg(P.bias + sdd) : 0.f, P.softplus, W - c);
                     }
                     *reinterpret_cast<float4 *>(sdl + sc * CS6 + rr * Wp + pos4<L>(t)) = x;
-                    if (rr >= 1 && rr <= RB)
-                        *reinterpret_cast<float4 *>(ssig + sc * CS4 + (rr - 1) * Wp + pos4<L>(t)) = sg4;
                 }
             }
             // a row block is complete when its last pass has been written out
@@ -511,16 +560,17 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
     }
 }
 
-size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc) {
+size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk) {
     const int nw = CG * NPp;
+    const size_t extra = bulk ? 16 + 2 * (size_t)(CG * (32 / L)) * W * (RB * es + RB * eso + (RB + 2) * es) : 0;
     const int CP = CG * (32 / L);
     switch (L) {
-        case 1: return (size_t)BwdSmem<1>::total(CP, NPp, CT, nw, acc) * 4;
-        case 2: return (size_t)BwdSmem<2>::total(CP, NPp, CT, nw, acc) * 4;
-        case 4: return (size_t)BwdSmem<4>::total(CP, NPp, CT, nw, acc) * 4;
-        case 8: return (size_t)BwdSmem<8>::total(CP, NPp, CT, nw, acc) * 4;
-        case 16: return (size_t)BwdSmem<16>::total(CP, NPp, CT, nw, acc) * 4;
-        default: return (size_t)BwdSmem<32>::total(CP, NPp, CT, nw, acc) * 4;
+        case 1: return (size_t)((BwdSmem<1>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
+        case 2: return (size_t)((BwdSmem<2>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
+        case 4: return (size_t)((BwdSmem<4>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
+        case 8: return (size_t)((BwdSmem<8>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
+        case 16: return (size_t)((BwdSmem<16>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
+        default: return (size_t)((BwdSmem<32>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
     }
 }
 
@@ -539,7 +589,8 @@ static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) 
 }
 
 cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st) {
-    const size_t smem = bwd_smem_bytes(L, P.CG, P.NPp, P.CT, P.acc_dbc != 0);
+    const size_t smem = bwd_smem_bytes(L, P.CG, P.NPp, P.CT, P.acc_dbc != 0, P.W, P.io_dt == CS2D_F32 ? 4 : 2,
+                                       P.out_dt == CS2D_F32 ? 4 : 2, P.bulk != 0);
     switch (L) {
         case 1: return launch<1>(P, grid, smem, st);
         case 2: return launch<2>(P, grid, smem, st);

@@ -54,6 +54,9 @@ struct Dev {
     int acc_dbc; // backward: 1 = dB/dC accumulated over the CTA's passes in shared memory,
                  //           0 = added to global memory row by row (wide rows: tiles do not fit)
     int vec;    // bit i set: tensor i may be accessed 4 elements at a time
+    int bulk;   // 1: row blocks of u, delta (and dout) are fetched with bulk asynchronous copies
+                //    (rows are 16-byte multiples, planes contiguous and aligned); 0: plain loads
+    int *status; // device status word (see ERR_*)
     const void *u, *delta, *B, *C;
     const float *A, *D, *bias, *decay;
     int64_t u_bs, u_ds, u_hs, dl_bs, dl_ds, dl_hs, A_ds, A_ns;
@@ -66,6 +69,11 @@ struct Dev {
     float *dA, *dB, *dC, *dD, *dbias, *ddecay;
 };
 enum { VEC_U = 1, VEC_DELTA = 2, VEC_B = 4, VEC_C = 8, VEC_OUT = 16, VEC_DU = 32 };
+
+// Device-side status word of the library (0 = fine).  A kernel that gives up on a
+// bounded wait records why here instead of spinning; the host reads and clears it
+// through cs2d_device_status().
+enum { ERR_BULK_COPY_TIMEOUT = 1 };
 
 // ---- packed fp32x2 helpers -------------------------------------------------
 __device__ __forceinline__ float2 f2(float x, float y) { return make_float2(x, y); }
@@ -154,8 +162,73 @@ __device__ __forceinline__ void st4(void *p, int64_t i, int dt, bool vec, int nv
     if (nvalid > 3) st_elem(p, i + 3, dt, v.w);
 }
 
+// ---- bulk asynchronous copies (TMA engine, untiled form) + mbarrier ----------------
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+// global -> this CTA's shared memory; both addresses and the size are multiples of 16 bytes
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Waits for a phase of the barrier, but never forever: after ~2^22 polls (seconds)
+// it reports failure so that the caller can flag the error and leave.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+    for (int i = 0; i < (1 << 22); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 64) __nanosleep(64);
+    }
+    return false;
+}
+// 4 consecutive elements of a raw (input dtype) shared-memory row as floats
+__device__ __forceinline__ float4 lds4(const unsigned char *raw, int idx, int dt) {
+    if (dt == CS2D_F32) return *reinterpret_cast<const float4 *>(raw + (size_t)idx * 4);
+    const uint2 v = *reinterpret_cast<const uint2 *>(raw + (size_t)idx * 2);
+    if (dt == CS2D_BF16) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&v.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
 // softplus with the reference's threshold (fwd kernel :221-224).
 __device__ __forceinline__ float softplus20(float x) { return x <= 20.f ? log1pf(__expf(x)) : x; }
+
+// delta -> softplus(delta + bias) in place, d softplus/dx into `sig`; the reference's
+// threshold and chain rule (bwd kernel :785-806).  Columns past the image read as 0.
+__device__ __forceinline__ void soft4(float4 &x, float4 &sig, float bias, int softplus, int nvalid) {
+    float xs[4] = {x.x + bias, x.y + bias, x.z + bias, x.w + bias}, sg[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        sg[e] = 1.f;
+        if (softplus && xs[e] <= 20.f) {
+            sg[e] = 1.f / (1.f + __expf(-xs[e]));
+            xs[e] = log1pf(__expf(xs[e]));
+        }
+        if (e >= nvalid) { xs[e] = 0.f; sg[e] = 0.f; }
+    }
+    x = make_float4(xs[0], xs[1], xs[2], xs[3]);
+    sig = make_float4(sg[0], sg[1], sg[2], sg[3]);
+}
 
 // ---- shared-memory tile layouts ---------------------------------------------------
 // Per-channel float tiles are [channel][row][Wp]; inside a row the 8 columns of

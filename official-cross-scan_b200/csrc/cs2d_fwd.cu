@@ -27,6 +27,11 @@ struct FwdSmem {
     static __host__ __device__ constexpr int total(int CP, int NPp, int nw) {
         return B(CP, nw) + 2 * 2 * NPp * RB * Wp;
     }
+    // after the tiles: two mbarriers (4 floats), then two stages of raw row blocks
+    // (u: RB rows, delta: RB+1 rows per channel, in the input dtype)
+    static __host__ __device__ constexpr int bars(int CP, int NPp, int nw) { return total(CP, NPp, nw); }
+    static __host__ __device__ constexpr int raw(int CP, int NPp, int nw) { return total(CP, NPp, nw) + 4; }
+    static __host__ __device__ constexpr int stage_bytes(int CP, int W, int es) { return CP * (2 * RB + 1) * W * es; }
 };
 
 template <int L>
@@ -61,6 +66,38 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
 
     const int nblk = P.nck;
     const int steps = nblk * P.npass;
+
+    // Bulk asynchronous staging: the raw row blocks of u and delta of step k+1 are
+    // copied global -> shared by the copy engine while step k computes; an mbarrier
+    // per stage counts the bytes.  One thread issues, everybody waits (bounded).
+    const bool bulk = P.bulk != 0;
+    const int es = P.io_dt == CS2D_F32 ? 4 : 2;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::bars(CP, NPp, nw));
+    unsigned char *raw = reinterpret_cast<unsigned char *>(smem + S::raw(CP, NPp, nw));
+    const int stage_bytes = S::stage_bytes(CP, W, es);
+    auto issue = [&](int k) {
+        const int kblk = k / P.npass, kpass = k % P.npass;
+        const int kr0 = kblk * RB, knr = min(RB, H - kr0), kch0 = kpass * CP;
+        const int lo = max(kr0 - 1, 0), nrows_dl = kr0 + knr - lo;
+        const int nv = max(0, min(CP, nch - kch0));
+        uint64_t *bar = bars + (k & 1);
+        unsigned char *ru = raw + (size_t)(k & 1) * stage_bytes, *rd = ru + (size_t)CP * RB * W * es;
+        mbar_expect_tx(bar, (uint32_t)(nv * (knr + nrows_dl) * W * es));
+        for (int sc = 0; sc < nv; ++sc) {
+            const int sd = dbase + kch0 + sc, sdd = sd / P.drep;
+            const char *srcu = reinterpret_cast<const char *>(P.u) +
+                               ((int64_t)b * P.u_bs + (int64_t)sd * P.u_ds + (int64_t)kr0 * W) * es;
+            const char *srcd = reinterpret_cast<const char *>(P.delta) +
+                               ((int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)lo * W) * es;
+            bulk_g2s(ru + (size_t)sc * RB * W * es, srcu, (uint32_t)(knr * W * es), bar);
+            bulk_g2s(rd + (size_t)sc * (RB + 1) * W * es, srcd, (uint32_t)(nrows_dl * W * es), bar);
+        }
+    };
+    if (bulk) {
+        if (tid == 0) { mbar_init(bars, 1); mbar_init(bars + 1, 1); mbar_init_fence(); }
+        __syncthreads();
+        if (tid == 0 && steps > 0) issue(0);
+    }
     for (int step = 0; step <= steps; ++step) {
         const int blk = step / P.npass, pass = step % P.npass;
         const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
@@ -77,7 +114,19 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
             for (int k = 0; k < STRIP / 2; ++k) ck_pre[k] = ok ? pk[k] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         // ---- phase A: write out the previous step, stage this one -------------------
+        if (bulk) {
+            if (tid == 0 && step + 1 < steps) issue(step + 1);   // lands while this step computes
+            bool ok = nr == 0 || mbar_wait_bounded(bars + (step & 1), (step >> 1) & 1);
+            if (__syncthreads_or(!ok)) {  // give up: flag it, drain the other stage, leave
+                if (tid == 0) atomicOr(P.status, ERR_BULK_COPY_TIMEOUT);
+                if (step + 1 < steps) mbar_wait_bounded(bars + ((step + 1) & 1), ((step + 1) >> 1) & 1);
+                return;
+            }
+        }
         {
+            const unsigned char *raw_u = raw + (size_t)(step & 1) * stage_bytes;
+            const unsigned char *raw_dl = raw_u + (size_t)CP * RB * W * es;
+            const int lo = max(r0 - 1, 0);
             const int pstep = step - 1;
             const int pblk = pstep / P.npass, ppass = pstep % P.npass;
             const int pr0 = pblk * RB, pnr = step > 0 ? min(RB, H - pr0) : 0, pch0 = ppass * CP;
@@ -104,9 +153,14 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                         P.out_dt, P.vec & VEC_OUT, W - c, acc);
                 }
                 float4 uv = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (rr < nr && ch0 + sc < nch)
-                    uv = ld4(P.u, (int64_t)b * P.u_bs + (int64_t)(dbase + ch0 + sc) * P.u_ds +
-                                      (int64_t)(r0 + rr) * P.u_hs + c, P.io_dt, P.vec & VEC_U, W - c);
+                if (rr < nr && ch0 + sc < nch) {
+                    if (bulk) {
+                        if (c < W) uv = lds4(raw_u, (sc * RB + rr) * W + c, P.io_dt);
+                    } else {
+                        uv = ld4(P.u, (int64_t)b * P.u_bs + (int64_t)(dbase + ch0 + sc) * P.u_ds +
+                                          (int64_t)(r0 + rr) * P.u_hs + c, P.io_dt, P.vec & VEC_U, W - c);
+                    }
+                }
                 *reinterpret_cast<float4 *>(su + o4) = uv;
             }
             if (nr > 0) {
@@ -115,17 +169,20 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                     const int t = it % T4, rr = (it / T4) % (RB + 1), sc = it / (T4 * (RB + 1));
                     const int c = 4 * t, r = r0 + rr - 1;
                     float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (r >= 0 && rr - 1 < nr && ch0 + sc < nch) {
+                    if (r >= 0 && rr - 1 < nr && ch0 + sc < nch && c < W) {
                         const int sdd = (dbase + ch0 + sc) / P.drep;
-                        x = ld4(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)r * P.dl_hs + c,
-                                P.io_dt, P.vec & VEC_DELTA, W - c);
+                        if (bulk)
+                            x = lds4(raw_dl, (sc * (RB + 1) + (r - lo)) * W + c, P.io_dt);
+                        else
+                            x = ld4(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)r * P.dl_hs + c,
+                                    P.io_dt, P.vec & VEC_DELTA, W - c);
                         const float bv = P.bias ? __ldg(P.bias + sdd) : 0.f;
                         x.x += bv; x.y += bv; x.z += bv; x.w += bv;
                         if (P.softplus) {
                             x.x = softplus20(x.x); x.y = softplus20(x.y); x.z = softplus20(x.z); x.w = softplus20(x.w);
                         }
                         const int nv = W - c;  // columns past the image keep dl = 0
-                        if (nv < 4) { x.w = 0.f; if (nv < 3) x.z = 0.f; if (nv < 2) x.y = 0.f; if (nv < 1) x.x = 0.f; }
+                        if (nv < 4) { x.w = 0.f; if (nv < 3) x.z = 0.f; if (nv < 2) x.y = 0.f; }
                     }
                     *reinterpret_cast<float4 *>(sdl + sc * CS5 + rr * Wp + pos4<L>(t)) = x;
                 }
@@ -192,16 +249,17 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
     }
 }
 
-size_t fwd_smem_bytes(int L, int CG, int NPp) {
+size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk) {
     const int nw = CG * NPp;
+    const size_t extra = bulk ? 16 + 2 * (size_t)(CG * (32 / L)) * (2 * RB + 1) * W * es : 0;
     const int CP = CG * (32 / L);
     switch (L) {
-        case 1: return (size_t)FwdSmem<1>::total(CP, NPp, nw) * 4;
-        case 2: return (size_t)FwdSmem<2>::total(CP, NPp, nw) * 4;
-        case 4: return (size_t)FwdSmem<4>::total(CP, NPp, nw) * 4;
-        case 8: return (size_t)FwdSmem<8>::total(CP, NPp, nw) * 4;
-        case 16: return (size_t)FwdSmem<16>::total(CP, NPp, nw) * 4;
-        default: return (size_t)FwdSmem<32>::total(CP, NPp, nw) * 4;
+        case 1: return (size_t)FwdSmem<1>::total(CP, NPp, nw) * 4 + extra;
+        case 2: return (size_t)FwdSmem<2>::total(CP, NPp, nw) * 4 + extra;
+        case 4: return (size_t)FwdSmem<4>::total(CP, NPp, nw) * 4 + extra;
+        case 8: return (size_t)FwdSmem<8>::total(CP, NPp, nw) * 4 + extra;
+        case 16: return (size_t)FwdSmem<16>::total(CP, NPp, nw) * 4 + extra;
+        default: return (size_t)FwdSmem<32>::total(CP, NPp, nw) * 4 + extra;
     }
 }
 
@@ -218,7 +276,7 @@ static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) 
 }
 
 cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st) {
-    const size_t smem = fwd_smem_bytes(L, P.CG, P.NPp);
+    const size_t smem = fwd_smem_bytes(L, P.CG, P.NPp, P.W, P.io_dt == CS2D_F32 ? 4 : 2, P.bulk != 0);
     switch (L) {
         case 1: return launch<1>(P, grid, smem, st);
         case 2: return launch<2>(P, grid, smem, st);

@@ -23,7 +23,7 @@ def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(_lib.LIB_PATH)
     names = _declared()
     assert {"cs2d_fwd", "cs2d_bwd", "cs2d_saved_bytes", "cs2d_bwd_scratch_bytes", "cs2d_last_error",
-            "cs2d_abi_version", "cs2d_launch_count"} <= set(names)
+            "cs2d_abi_version", "cs2d_launch_count", "cs2d_device_status"} <= set(names)
     for n in names:
         assert hasattr(lib, n), n
     assert _lib.lib().cs2d_abi_version() == 1
