@@ -115,6 +115,28 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
              float *dD, float *ddelta_bias, float *dA_decay, void *stream);
 
 /*
+ * Backward without any allocation on the caller's side: identical to cs2d_bwd
+ * except that the scratch buffer is a fixed device array inside the library
+ * (CS2D_NOALLOC_SCRATCH_BYTES per GPU, held from library load to process exit).
+ * It is meant for hosts that cannot call cudaMalloc where they run the backward
+ * - a runtime that owns all device memory through its own pool, a plugin invoked
+ * from an allocator callback, a thin FFI stub that only sees its arguments.
+ * This entry point has no counterpart in the reference (whose host binding
+ * allocates with torch).
+ *   - inputs, saved state and ALL outputs are still passed by the caller;
+ *   - problems whose cs2d_bwd_scratch_bytes() exceeds CS2D_NOALLOC_SCRATCH_BYTES
+ *     are rejected with CS2D_ERR_UNSUPPORTED and a message (split the batch);
+ *   - the first call on a device looks up the array's device address (a host
+ *     call, no allocation); make that first call before starting a stream capture;
+ *   - nothing needs clearing between calls, but the array is shared: calls that
+ *     may overlap on the same GPU (different streams or threads) race on it.
+ */
+#define CS2D_NOALLOC_SCRATCH_BYTES (32u << 20)
+int cs2d_bwd_noalloc(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t dout_ds,
+                     int64_t dout_hs, const void *saved, void *du, void *ddelta, float *dA, float *dB,
+                     float *dC, float *dD, float *ddelta_bias, float *dA_decay, void *stream);
+
+/*
  * Reads and clears the device-side status word of the current device
  * (synchronises with the device).  0 = no kernel reported a problem; nonzero =
  * a kernel gave up on a bounded wait for one of its asynchronous copies and

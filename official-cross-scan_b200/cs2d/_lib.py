@@ -8,6 +8,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libcs2d.so")
 
 F32, F16, BF16 = 0, 1, 2
+NOALLOC_SCRATCH_BYTES = 32 << 20  # CS2D_NOALLOC_SCRATCH_BYTES
 
 
 _i32, _i64, _p = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p
@@ -55,6 +56,8 @@ def lib():
         L.cs2d_fwd.argtypes = [ctypes.POINTER(Problem), vp, i64, i64, i64, vp, vp]
         L.cs2d_bwd.restype = ctypes.c_int
         L.cs2d_bwd.argtypes = [ctypes.POINTER(Problem), vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+        L.cs2d_bwd_noalloc.restype = ctypes.c_int
+        L.cs2d_bwd_noalloc.argtypes = [ctypes.POINTER(Problem), vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
         L.cs2d_last_error.restype = ctypes.c_char_p
         L.cs2d_abi_version.restype = ctypes.c_int
         L.cs2d_launch_count.restype = ctypes.c_int64

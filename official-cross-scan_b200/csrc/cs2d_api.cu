@@ -230,6 +230,62 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
     return CS2D_OK;
 }
 
+/*
+ * Backward for callers that must not allocate.
+ *
+ * Some hosts of this library cannot call cudaMalloc at the point where they run
+ * the backward: a serving or training runtime that hands every byte of device
+ * memory to its own pool at start-up, a plugin called from inside somebody
+ * else's allocator callback, or a binding (a JNI / cgo stub, say) that is only
+ * given the tensors it was called with.  For them the adjoint-row scratch that
+ * cs2d_bwd takes as an argument lives inside the library instead: a fixed
+ * device array that every GPU loading the library carries until the process
+ * exits.  In host code the array's name is only a handle, not a device address,
+ * so the address is looked up with cudaGetSymbolAddress - once per device, with
+ * that device current, on the first call there.  That first call should
+ * therefore happen before any stream capture is started.
+ *
+ * Everything else is cs2d_bwd: same inputs, same caller-provided outputs, same
+ * kernel.  Nothing in the array has to be cleared between calls (each row is
+ * written before it is read), but all calls share it: two calls that can run
+ * at the same time on one GPU would overwrite each other's rows.
+ */
+static __device__ __align__(256) unsigned char g_noalloc_scratch[CS2D_NOALLOC_SCRATCH_BYTES];
+
+static void *noalloc_scratch_ptr() {
+    static void *ptr[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptr[dev]) {
+        void *q = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&q, g_noalloc_scratch);
+        if (e != cudaSuccess || !q) {
+            fail(CS2D_ERR_CUDA, "cudaGetSymbolAddress(built-in scratch) failed: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        ptr[dev] = q;
+    }
+    return ptr[dev];
+}
+
+int cs2d_bwd_noalloc(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t dout_ds, int64_t dout_hs,
+                     const void *saved, void *du, void *ddelta, float *dA, float *dB, float *dC, float *dD,
+                     float *ddelta_bias, float *dA_decay, void *stream) {
+    int rc = validate(p);
+    if (rc) return rc;
+    const size_t need = cs2d_bwd_scratch_bytes(p);
+    if (need == 0) return CS2D_ERR_UNSUPPORTED;  // message already set by the planner
+    if (need > (size_t)CS2D_NOALLOC_SCRATCH_BYTES)
+        return fail(CS2D_ERR_UNSUPPORTED,
+                    "this problem needs %zu bytes of backward scratch but the built-in buffer holds %zu; "
+                    "split the batch or call cs2d_bwd with your own scratch",
+                    need, (size_t)CS2D_NOALLOC_SCRATCH_BYTES);
+    void *scratch = noalloc_scratch_ptr();
+    if (!scratch) return CS2D_ERR_CUDA;
+    return cs2d_bwd(p, dout, dout_bs, dout_ds, dout_hs, saved, scratch, du, ddelta, dA, dB, dC, dD, ddelta_bias,
+                    dA_decay, stream);
+}
+
 int cs2d_device_status(void) {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_cs2d_status, sizeof(int)) != cudaSuccess) return CS2D_ERR_CUDA;
