@@ -188,3 +188,26 @@ def fwd_torch(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=False, 
     if D is not None:
         y = y + D[None, :, None, None] * u
     return y
+
+
+def cross_fwd_torch(u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplus=True):
+    """Differentiable float64 restatement of the four-corner CrossScan with fusion weights.
+
+    The reference has no code for the merge; the definition is: flip the inputs of
+    direction k into the kernel's scan order, run the reference recurrence
+    (``fwd_torch``), flip the result back, and sum the directions with ``w[k, d]``.
+    Inputs are in image coordinates: u (b, D, h, w), delta (b, K*D, h, w), A (K*D, n),
+    B, C (b, K, n, h, w), w (K, D).  Small cases only.
+    """
+    import torch
+    flips = ((), (-1,), (-2,), (-2, -1))  # k: 0 none, 1 columns, 2 rows, 3 both
+    fl = lambda t, k: torch.flip(t, flips[k % 4]) if flips[k % 4] else t
+    b, d, h, wd = u.shape
+    K = B.shape[1]
+    y = 0
+    for k in range(K):
+        sl = slice(k * d, (k + 1) * d)
+        yk = fwd_torch(fl(u, k), fl(delta[:, sl], k), A[sl], fl(B[:, k:k + 1], k), fl(C[:, k:k + 1], k),
+                       None if D is None else D[sl], None if delta_bias is None else delta_bias[sl], delta_softplus)
+        y = y + w[k][None, :, None, None] * fl(yk, k)
+    return y
