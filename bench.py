@@ -167,6 +167,11 @@ def main():
     from cs2d import _lib, ops, parallel
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    # Libraries (NCCL prints its version banner at communicator creation) must not write into
+    # the one-JSON-line stdout: route fd 1 to stderr until the result is printed.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -282,6 +287,8 @@ def main():
         cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
                "sample": f"{sample} of {B} samples of {args.config}, float32, OpenMP, {sec:.1f} s"}
 
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
     if rank == 0:
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,

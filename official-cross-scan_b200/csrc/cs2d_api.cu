@@ -47,8 +47,7 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, Geometry *g)
     const int strips = (p->ncols + STRIP - 1) / STRIP;
     int L = 1;
     while (L < strips) L <<= 1;
-    if (L > 32) return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d: rows wider than %d columns are not supported yet",
-                            p->ncols, 32 * STRIP);
+    if (L > 32) return fail(CS2D_ERR_INVALID, "internal: a column tile of %d columns", p->ncols);
     const int NP = (p->dstate + 1) / 2;
     int NPp = 1;
     while (NPp < NP) NPp <<= 1;
@@ -154,6 +153,8 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     if (vec_ok(p->C, es, p->ncols, {p->C_bs, p->C_gs, p->C_ns, p->C_hs})) d.vec |= VEC_C;
     d.adj = nullptr;
     d.status = nullptr;
+    d.tile_left = d.tile_right = 0; d.Wout = p->ncols;
+    d.edge_in = nullptr; d.edge_out = nullptr; d.adj_in = nullptr; d.adj_out = nullptr;
     d.du = d.ddelta = nullptr; d.dA = d.dB = d.dC = d.dD = d.dbias = d.ddecay = nullptr;
 }
 }  // namespace cs2d
@@ -162,17 +163,65 @@ using namespace cs2d;
 
 extern "C" {
 
-size_t cs2d_saved_bytes(const cs2d_problem *p) {
+// ---- column tiles ------------------------------------------------------------------------
+// A launch covers at most 256 columns (32 lanes x 8).  Wider rows are cut into tiles of 256
+// columns that are processed by successive launches on the same stream: left to right in
+// the forward (each tile leaves h and s of its last column for its right neighbour), right
+// to left in the backward (each tile leaves dh and ds of its first column for its left
+// neighbour).  Stream order is the only synchronisation between tiles.
+static const int kTileCols = 32 * STRIP;
+static int n_tiles(int ncols) { return (ncols + kTileCols - 1) / kTileCols; }
+
+struct TileView {
+    cs2d_problem q;   // the problem restricted to the tile (pointers moved, ncols = tile width)
+    int c0;           // first column
     Geometry g;
-    if (validate(p) != CS2D_OK || plan(p, false, false, &g) != CS2D_OK) return 0;
-    return (size_t)p->batch * p->dim * g.nck * g.NPp * (g.L * STRIP) * sizeof(float2);
+    size_t saved_off, saved_bytes, adj_off, adj_bytes;   // byte offsets inside saved / scratch
+};
+
+static const char *at(const void *p, int64_t elems, int es) {
+    return p ? reinterpret_cast<const char *>(p) + elems * es : nullptr;
 }
 
-size_t cs2d_bwd_scratch_bytes(const cs2d_problem *p) {
-    Geometry g;
-    if (validate(p) != CS2D_OK || plan(p, true, false, &g) != CS2D_OK) return 0;
-    return (size_t)p->batch * p->dim * g.NPp * (g.L * STRIP) * sizeof(float2);
+// Fills `tv` for tile t and returns the bytes of the per-tile buffers; edge buffers follow them.
+static int tile_view(const cs2d_problem *p, int t, bool backward, bool bulk_ok, TileView *tv) {
+    const int es = esize(p->io_dtype);
+    tv->c0 = t * kTileCols;
+    tv->q = *p;
+    tv->q.ncols = p->ncols - tv->c0 < kTileCols ? p->ncols - tv->c0 : kTileCols;
+    tv->q.u = at(p->u, tv->c0, es);
+    tv->q.delta = at(p->delta, tv->c0, es);
+    tv->q.B = at(p->B, tv->c0, es);
+    tv->q.C = at(p->C, tv->c0, es);
+    int rc = plan(&tv->q, backward, bulk_ok, &tv->g);
+    if (rc) return rc;
+    const size_t per = (size_t)p->batch * p->dim * tv->g.NPp * (tv->g.L * STRIP) * sizeof(float2);
+    tv->saved_bytes = per * tv->g.nck;
+    tv->adj_bytes = per;
+    return CS2D_OK;
 }
+
+static size_t edge_bytes(const cs2d_problem *p, int NPp) {
+    return (size_t)p->batch * p->dim * NPp * p->nrows * sizeof(float4);
+}
+
+static size_t layout_bytes(const cs2d_problem *p, bool backward) {
+    if (validate(p) != CS2D_OK) return 0;
+    const int nt = n_tiles(p->ncols);
+    size_t total = 0;
+    int NPp = 1;
+    for (int t = 0; t < nt; ++t) {
+        TileView tv;
+        if (tile_view(p, t, backward, false, &tv) != CS2D_OK) return 0;
+        total += backward ? tv.adj_bytes : tv.saved_bytes;
+        NPp = tv.g.NPp;
+    }
+    return total + (size_t)(nt - 1) * edge_bytes(p, NPp);
+}
+
+size_t cs2d_saved_bytes(const cs2d_problem *p) { return layout_bytes(p, false); }
+
+size_t cs2d_bwd_scratch_bytes(const cs2d_problem *p) { return layout_bytes(p, true); }
 
 int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, int64_t out_hs, void *saved,
              void *stream) {
@@ -180,20 +229,38 @@ int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, i
     if (rc) return rc;
     if (!out || !saved) return fail(CS2D_ERR_INVALID, "out and saved must be given");
     if (reinterpret_cast<uintptr_t>(saved) & 15) return fail(CS2D_ERR_INVALID, "saved must be 16-byte aligned");
-    Geometry g;
-    const int es = esize(p->io_dtype);
-    const bool bulk = bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
-                      bulk_ok1(p->delta, es, p->ncols, p->delta_bs, p->delta_ds, p->delta_hs);
-    if ((rc = plan(p, false, bulk, &g))) return rc;
-    Dev d;
-    fill(d, p, g);
-    d.out = out; d.o_bs = out_bs; d.o_ds = out_ds; d.o_hs = out_hs;
-    if (vec_ok(out, esize(p->out_dtype), p->ncols, {out_bs, out_ds, out_hs})) d.vec |= VEC_OUT;
-    d.saved = reinterpret_cast<float2 *>(saved);
-    if (!(d.status = status_ptr())) return fail(CS2D_ERR_CUDA, "cannot locate the device status word");
-    cudaError_t e = launch_fwd(d, g.L, g.grid, reinterpret_cast<cudaStream_t>(stream));
-    if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
-    g_launches.fetch_add(1);
+    int *status = status_ptr();
+    if (!status) return fail(CS2D_ERR_CUDA, "cannot locate the device status word");
+    const int es = esize(p->io_dtype), eso = esize(p->out_dtype), nt = n_tiles(p->ncols);
+    // saved = [checkpoints tile 0 | ... | checkpoints tile nt-1 | edge 0|1 | ... | edge nt-2|nt-1]
+    size_t ck_total = 0;
+    for (int t = 0; t < nt; ++t) {
+        TileView tv;
+        if ((rc = tile_view(p, t, false, false, &tv))) return rc;
+        ck_total += tv.saved_bytes;
+    }
+    size_t ck_off = 0;
+    for (int t = 0; t < nt; ++t) {
+        TileView tv;
+        const bool bulk = nt == 1 && bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
+                          bulk_ok1(p->delta, es, p->ncols, p->delta_bs, p->delta_ds, p->delta_hs);
+        if ((rc = tile_view(p, t, false, bulk, &tv))) return rc;
+        Dev d;
+        fill(d, &tv.q, tv.g);
+        d.out = const_cast<char *>(at(out, tv.c0, eso)); d.o_bs = out_bs; d.o_ds = out_ds; d.o_hs = out_hs;
+        if (vec_ok(d.out, eso, tv.q.ncols, {out_bs, out_ds, out_hs})) d.vec |= VEC_OUT;
+        d.saved = reinterpret_cast<float2 *>(reinterpret_cast<char *>(saved) + ck_off);
+        ck_off += tv.saved_bytes;
+        d.status = status;
+        d.tile_left = t > 0; d.tile_right = t + 1 < nt; d.Wout = p->ncols;
+        const size_t eb = edge_bytes(p, tv.g.NPp);
+        char *edges = reinterpret_cast<char *>(saved) + ck_total;
+        d.edge_in = t > 0 ? reinterpret_cast<const float4 *>(edges + (size_t)(t - 1) * eb) : nullptr;
+        d.edge_out = t + 1 < nt ? reinterpret_cast<float4 *>(edges + (size_t)t * eb) : nullptr;
+        cudaError_t e = launch_fwd(d, tv.g.L, tv.g.grid, reinterpret_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
+        g_launches.fetch_add(1);
+    }
     return CS2D_OK;
 }
 
@@ -207,26 +274,48 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
     if ((reinterpret_cast<uintptr_t>(saved) | reinterpret_cast<uintptr_t>(scratch)) & 15)
         return fail(CS2D_ERR_INVALID, "saved and scratch must be 16-byte aligned");
     if (dA_decay && !p->A_decay) return fail(CS2D_ERR_INVALID, "dA_decay requested without A_decay");
-    Geometry g;
-    const int es = esize(p->io_dtype);
-    const bool bulk = bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
-                      bulk_ok1(p->delta, es, p->ncols, p->delta_bs, p->delta_ds, p->delta_hs) &&
-                      bulk_ok1(dout, esize(p->out_dtype), p->ncols, dout_bs, dout_ds, dout_hs);
-    if ((rc = plan(p, true, bulk, &g))) return rc;
-    Dev d;
-    fill(d, p, g);
-    d.out = const_cast<void *>(dout); d.o_bs = dout_bs; d.o_ds = dout_ds; d.o_hs = dout_hs;
-    if (vec_ok(dout, esize(p->out_dtype), p->ncols, {dout_bs, dout_ds, dout_hs})) d.vec |= VEC_OUT;
-    if (vec_ok(du, esize(p->io_dtype), p->ncols, {}) && vec_ok(ddelta, esize(p->io_dtype), p->ncols, {}))
-        d.vec |= VEC_DU;
-    d.saved = reinterpret_cast<float2 *>(const_cast<void *>(saved));
-    d.adj = reinterpret_cast<float2 *>(scratch);
-    d.du = du; d.ddelta = ddelta; d.dA = dA; d.dB = dB; d.dC = dC; d.dD = dD; d.dbias = ddelta_bias;
-    d.ddecay = dA_decay;
-    if (!(d.status = status_ptr())) return fail(CS2D_ERR_CUDA, "cannot locate the device status word");
-    cudaError_t e = launch_bwd(d, g.L, g.grid, reinterpret_cast<cudaStream_t>(stream));
-    if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
-    g_launches.fetch_add(1);
+    int *status = status_ptr();
+    if (!status) return fail(CS2D_ERR_CUDA, "cannot locate the device status word");
+    const int es = esize(p->io_dtype), eso = esize(p->out_dtype), nt = n_tiles(p->ncols);
+    // saved as laid out by the forward; scratch = [adjoint rows tile 0 | ... | dh/ds edges]
+    size_t ck_total = 0, adj_total = 0;
+    size_t ck_offs[64], adj_offs[64];
+    if (nt > 64) return fail(CS2D_ERR_UNSUPPORTED, "more than 64 column tiles");
+    for (int t = 0; t < nt; ++t) {
+        TileView tv;
+        if ((rc = tile_view(p, t, true, false, &tv))) return rc;
+        ck_offs[t] = ck_total; adj_offs[t] = adj_total;
+        ck_total += tv.saved_bytes; adj_total += tv.adj_bytes;
+    }
+    for (int t = nt - 1; t >= 0; --t) {
+        TileView tv;
+        const bool bulk = nt == 1 && bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
+                          bulk_ok1(p->delta, es, p->ncols, p->delta_bs, p->delta_ds, p->delta_hs) &&
+                          bulk_ok1(dout, eso, p->ncols, dout_bs, dout_ds, dout_hs);
+        if ((rc = tile_view(p, t, true, bulk, &tv))) return rc;
+        Dev d;
+        fill(d, &tv.q, tv.g);
+        d.out = const_cast<char *>(at(dout, tv.c0, eso)); d.o_bs = dout_bs; d.o_ds = dout_ds; d.o_hs = dout_hs;
+        if (vec_ok(d.out, eso, tv.q.ncols, {dout_bs, dout_ds, dout_hs})) d.vec |= VEC_OUT;
+        d.du = const_cast<char *>(at(du, tv.c0, es));
+        d.ddelta = const_cast<char *>(at(ddelta, tv.c0, es));
+        if (vec_ok(d.du, es, tv.q.ncols, {(int64_t)p->ncols}) && vec_ok(d.ddelta, es, tv.q.ncols, {(int64_t)p->ncols}))
+            d.vec |= VEC_DU;
+        d.saved = reinterpret_cast<float2 *>(const_cast<char *>(reinterpret_cast<const char *>(saved)) + ck_offs[t]);
+        d.adj = reinterpret_cast<float2 *>(reinterpret_cast<char *>(scratch) + adj_offs[t]);
+        d.dA = dA; d.dB = dB + tv.c0; d.dC = dC + tv.c0; d.dD = dD; d.dbias = ddelta_bias; d.ddecay = dA_decay;
+        d.status = status;
+        d.tile_left = t > 0; d.tile_right = t + 1 < nt; d.Wout = p->ncols;
+        const size_t eb = edge_bytes(p, tv.g.NPp);
+        const char *edges = reinterpret_cast<const char *>(saved) + ck_total;
+        char *aedges = reinterpret_cast<char *>(scratch) + adj_total;
+        d.edge_in = t > 0 ? reinterpret_cast<const float4 *>(edges + (size_t)(t - 1) * eb) : nullptr;
+        d.adj_in = t + 1 < nt ? reinterpret_cast<const float4 *>(aedges + (size_t)t * eb) : nullptr;
+        d.adj_out = t > 0 ? reinterpret_cast<float4 *>(aedges + (size_t)(t - 1) * eb) : nullptr;
+        cudaError_t e = launch_bwd(d, tv.g.L, tv.g.grid, reinterpret_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
+        g_launches.fetch_add(1);
+    }
     return CS2D_OK;
 }
 

@@ -39,33 +39,35 @@ struct BwdSmem {
     static __host__ __device__ constexpr int pdu(int CP) { return dl(CP) + CP * CS6; }           // [warps][CW][CS4]
     static __host__ __device__ constexpr int pdd(int CP, int nw) { return pdu(CP) + nw * CW * CS4; }
     static __host__ __device__ constexpr int tr(int CP, int nw) { return pdd(CP, nw) + nw * CW * CS4; }   // [warps][2][256] float2
-    static __host__ __device__ constexpr int aB(int CP, int nw) { return tr(CP, nw) + (CW > 1 ? nw * 1024 : 0); }        // [warps][RB][Wp] float2
-    static __host__ __device__ constexpr int aC(int CP, int nw, bool acc) { return aB(CP, nw) + (acc ? nw * RB * Wp * 2 : 0); }
-    static __host__ __device__ constexpr int B(int CP, int nw, bool acc) { return aC(CP, nw, acc) + (acc ? nw * RB * Wp * 2 : 0); }  // [NPp][RB][Wp] float2
-    static __host__ __device__ constexpr int C(int CP, int NPp, int nw, bool acc) { return B(CP, nw, acc) + NPp * RB * Wp * 2; }
-    static __host__ __device__ constexpr int dA(int CP, int NPp, int nw, bool acc) { return C(CP, NPp, nw, acc) + NPp * RB * Wp * 2; }
+    static __host__ __device__ constexpr int B(int CP, int nw) { return tr(CP, nw) + (CW > 1 ? nw * 1024 : 0); }  // [NPp][RB][Wp] float2
+    static __host__ __device__ constexpr int C(int CP, int NPp, int nw) { return B(CP, nw) + NPp * RB * Wp * 2; }
+    static __host__ __device__ constexpr int aB(int CP, int NPp, int nw) { return C(CP, NPp, nw) + NPp * RB * Wp * 2; }  // [warps][RB][Wp] float2
+    static __host__ __device__ constexpr int aC(int CP, int NPp, int nw, bool acc) { return aB(CP, NPp, nw) + (acc ? nw * RB * Wp * 2 : 0); }
+    static __host__ __device__ constexpr int dA(int CP, int NPp, int nw, bool acc) { return aC(CP, NPp, nw, acc) + (acc ? nw * RB * Wp * 2 : 0); }
     // dA: [CT][2*NPp], red: [CT][2], decay: [warps]
     static __host__ __device__ constexpr int total(int CP, int NPp, int CT, int nw, bool acc) {
         return dA(CP, NPp, nw, acc) + CT * 2 * NPp + CT * 2 + nw;
     }
 };
 
-template <int L>
+// NPC = 8 specialises the common geometry (8 state-pair slots, one channel group, 8 warps) so
+// that every shared-memory offset is a compile-time constant; NPC = 0 reads it from P.
+template <int L, int NPC>
 __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
     using S = BwdSmem<L>;
     constexpr int Wp = S::Wp, CW = S::CW, T4 = Wp / 4, CS4 = S::CS4, CS6 = S::CS6, L4 = 4 * L, L2 = 2 * L;
     constexpr int NU = CW >= 8 ? 1 : 8 / CW;  // columns of a strip owned by a lane after the channel sum
     extern __shared__ __align__(16) float smem[];
-    const int NPp = P.NPp, CG = P.CG, CP = CG * CW, CT = P.CT;
-    const int nthr = blockDim.x, nw = nthr >> 5;  // NPp * CG warps
+    const int NPp = NPC ? NPC : P.NPp, CG = NPC ? MAX_WARPS / NPC : P.CG, CP = CG * CW, CT = P.CT;
+    const int nw = NPp * CG, nthr = nw * 32;
     float *su = smem + S::u(CP), *sg = smem + S::g(CP), *ssig = smem + S::sig(CP), *sdl = smem + S::dl(CP);
     float *spdu = smem + S::pdu(CP), *spdd = smem + S::pdd(CP, nw);
     float2 *str = reinterpret_cast<float2 *>(smem + S::tr(CP, nw));
-    float2 *saB = reinterpret_cast<float2 *>(smem + S::aB(CP, nw));
     const bool acc_on = P.acc_dbc != 0;  // dB/dC accumulated over passes in shared memory
-    float2 *saC = reinterpret_cast<float2 *>(smem + S::aC(CP, nw, acc_on));
-    float2 *sB = reinterpret_cast<float2 *>(smem + S::B(CP, nw, acc_on));
-    float2 *sC = reinterpret_cast<float2 *>(smem + S::C(CP, NPp, nw, acc_on));
+    float2 *sB = reinterpret_cast<float2 *>(smem + S::B(CP, nw));
+    float2 *sC = reinterpret_cast<float2 *>(smem + S::C(CP, NPp, nw));
+    float2 *saB = reinterpret_cast<float2 *>(smem + S::aB(CP, NPp, nw));
+    float2 *saC = reinterpret_cast<float2 *>(smem + S::aC(CP, NPp, nw, acc_on));
     float *sdA = smem + S::dA(CP, NPp, nw, acc_on);
     float *sred = sdA + CT * 2 * NPp;
     float *sdecay = sred + CT * 2;
@@ -99,7 +101,16 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
     // mbarrier per stage counts the bytes.  One thread issues, everybody waits (bounded).
     const bool bulk = P.bulk != 0;
     const int es = P.io_dt == CS2D_F32 ? 4 : 2, eso = P.out_dt == CS2D_F32 ? 4 : 2;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + ((S::total(CP, NPp, CT, nw, acc_on) + 3) & ~3));
+    // tile-edge values staged per step (see Dev::edge_in / adj_in): h,s of the column left of
+    // the tile for rows r0-1..r0+RB-1, dh,ds of the column right of it for rows r0..r0+RB, and
+    // the softplus'd delta of those two columns
+    const int tot4 = (S::total(CP, NPp, CT, nw, acc_on) + 3) & ~3;
+    float4 *sedge = reinterpret_cast<float4 *>(smem + tot4);
+    float4 *sadj = sedge + CP * NPp * (RB + 1);
+    float *sedl_l = reinterpret_cast<float *>(sadj + CP * NPp * (RB + 1));   // [CP][RB]
+    float *sedl_r = sedl_l + CP * 4;                                          // [CP][RB+1] (pitch 8)
+    const bool has_left = P.tile_left != 0, has_right = P.tile_right != 0;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sedl_r + CP * 8);
     unsigned char *raw = reinterpret_cast<unsigned char *>(bars + 2);
     const int stage_bytes = CP * W * (RB * es + RB * eso + (RB + 2) * es);
     auto issue = [&](int k) {
@@ -191,7 +202,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         a1.x = fmaf(Dv, gv.x, a1.x); a1.y = fmaf(Dv, gv.y, a1.y);
                         a1.z = fmaf(Dv, gv.z, a1.z); a1.w = fmaf(Dv, gv.w, a1.w);
                         a2.x *= sv.x; a2.y *= sv.y; a2.z *= sv.z; a2.w *= sv.w;
-                        const int64_t o = (((int64_t)b * P.dim + sd) * H + (pr0 + rr)) * W + c;
+                        const int64_t o = (((int64_t)b * P.dim + sd) * H + (pr0 + rr)) * P.Wout + c;
                         st4(P.du, o, P.io_dt, P.vec & VEC_DU, W - c, a1);
                         st4(P.ddelta, o, P.io_dt, P.vec & VEC_DU, W - c, a2);
                         // columns past the image carry g = 0 and ddl = 0
@@ -263,17 +274,49 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                     saB[o] = bc(0.f); saC[o] = bc(0.f);
                     (void)scg;
                     if (c < W && rr < pnr && 2 * spp < N) {
-                        const int64_t og = ((((int64_t)b * P.G + g_) * N + 2 * spp) * H + (pr0 + rr)) * W + c;
+                        const int64_t og = ((((int64_t)b * P.G + g_) * N + 2 * spp) * H + (pr0 + rr)) * P.Wout + c;
                         atomicAdd(P.dB + og, vb.x);
                         atomicAdd(P.dC + og, vc.x);
                         if (2 * spp + 1 < N) {
-                            atomicAdd(P.dB + og + (int64_t)H * W, vb.y);
-                            atomicAdd(P.dC + og + (int64_t)H * W, vc.y);
+                            atomicAdd(P.dB + og + (int64_t)H * P.Wout, vb.y);
+                            atomicAdd(P.dC + og + (int64_t)H * P.Wout, vc.y);
                         }
                     }
                 }
             }
             if (nr > 0 && pass == 0) stage_BC<L>(P, b, g_, r0, nr, sB, sC);
+            if (nr > 0 && (has_left || has_right)) {
+                for (int it = tid; it < CP * NPp * (RB + 1); it += nthr) {
+                    const int k = it % (RB + 1), q = (it / (RB + 1)) % NPp, sc = it / ((RB + 1) * NPp);
+                    const int64_t base = (((int64_t)b * P.dim + dbase + ch0 + sc) * NPp + q) * H;
+                    float4 e = make_float4(0.f, 0.f, 0.f, 0.f), f = e;
+                    if (ch0 + sc < nch) {
+                        const int rl = r0 - 1 + k, rr2 = r0 + k;
+                        if (has_left && rl >= 0 && rl < H) e = __ldg(P.edge_in + base + rl);
+                        if (has_right && rr2 < H) f = P.adj_in[base + rr2];
+                    }
+                    sedge[it] = e; sadj[it] = f;
+                }
+                for (int it = tid; it < CP * 8; it += nthr) {
+                    const int k = it % 8, sc = it / 8;
+                    float xl = 0.f, xr = 0.f;
+                    if (ch0 + sc < nch) {
+                        const int sdd = (dbase + ch0 + sc) / P.drep;
+                        const float bv = P.bias ? __ldg(P.bias + sdd) : 0.f;
+                        const int64_t row0 = (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds;
+                        if (has_left && k < nr) {
+                            xl = ld_elem(P.delta, row0 + (int64_t)(r0 + k) * P.dl_hs - 1, P.io_dt) + bv;
+                            if (P.softplus) xl = softplus20(xl);
+                        }
+                        if (has_right && k <= RB && r0 + k < H) {
+                            xr = ld_elem(P.delta, row0 + (int64_t)(r0 + k) * P.dl_hs + W, P.io_dt) + bv;
+                            if (P.softplus) xr = softplus20(xr);
+                        }
+                    }
+                    if (k < RB) sedl_l[sc * 4 + k] = xl;
+                    sedl_r[sc * 8 + k] = xr;
+                }
+            }
         }
         __syncthreads();
         if (nr == 0) break;
@@ -321,7 +364,14 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         for (int i = 0; i < STRIP; ++i) dlu[i] = dl[i] * uu[i];
                         unpack8x2(sB + (pp * RB + rr) * Wp, L2, j, Bv);
                         float2 a[STRIP], p[STRIP], hcur[STRIP], sdummy[STRIP];
-                        row_forward<L, false>(j, dl, dlu, Bv, A2, lgd, hprev, a_up, a, p, hcur, sdummy);
+                        LeftEdge le = {bc(0.f), bc(0.f), bc(0.f), bc(0.f)};
+                        if (has_left && j == 0) {
+                            const float4 e0 = sedge[(cp * NPp + pp) * (RB + 1) + rr];
+                            const float4 e1 = sedge[(cp * NPp + pp) * (RB + 1) + rr + 1];
+                            le.h_prev = f2(e0.x, e0.y); le.h = f2(e1.x, e1.y);
+                            le.a = ex2_2(fma2(bc(sedl_l[cp * 4 + rr]), A2, lgd));
+                        }
+                        row_forward<L, false>(j, dl, dlu, Bv, A2, lgd, hprev, a_up, a, p, hcur, sdummy, has_left, le);
                         park8x2(slot_u + rr * Wp, slot_d + rr * Wp, L4, j, hcur);
 #pragma unroll
                         for (int i = 0; i < STRIP; ++i) { a_up[i] = a[i]; hprev[i] = hcur[i]; }
@@ -379,6 +429,16 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         a_r7.x = last ? 0.f : a_r7.x; a_r7.y = last ? 0.f : a_r7.y;
                         mdr7.x = last ? 0.f : mdr7.x; mdr7.y = last ? 0.f : mdr7.y;
                     }
+                    // first column of the tile to the right (full tiles end at lane L-1's last column)
+                    float2 e_dh = bc(0.f), e_ds = bc(0.f);
+                    if (has_right && j == L - 1) {
+                        const float4 e0 = sadj[(cp * NPp + pp) * (RB + 1) + rr], e1 = sadj[(cp * NPp + pp) * (RB + 1) + rr + 1];
+                        e_dh = f2(e0.x, e0.y); e_ds = f2(e0.z, e0.w);
+                        a_r7 = ex2_2(fma2(bc(sedl_r[cp * 8 + rr]), A2, lgd));
+                        // m(r+1, c_end) = a(r+1, c_end) * dh(r+1, c_end); zero below the image
+                        mdr7 = r0 + rr + 1 < H ? mul2(ex2_2(fma2(bc(sedl_r[cp * 8 + rr + 1]), A2, lgd)), f2(e1.x, e1.y))
+                                               : bc(0.f);
+                    }
                     // Three scans share this row: s forward (recomputed plain row scan), dh and ds
                     // reverse with multipliers a(r,c+1).  They are independent, so they are folded
                     // together, each as two 4-column half chains.
@@ -405,9 +465,21 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                             H1 = fma2(ar1, H1, bt[HS - 1 - k]); D1 = fma2(ar1, D1, neg2(gC[HS - 1 - k]));
                             Pr0 = mul2(Pr0, ar0); Pr1 = mul2(Pr1, ar1);
                         }
-                        float2 cs, unused, cdh, cds;
-                        carry_fwd<L, false>(j, mul2(Pf0, Pf1), fma2(Pf1, S0, S1), bc(0.f), cs, unused);
-                        carry_rev<L, true>(j, mul2(Pr0, Pr1), fma2(Pr1, H0, H1), fma2(Pr1, D0, D1), cdh, cds);
+                        float2 cs, unused, cdh, cds, Pfin, Prin;
+                        carry_fwd<L, false>(j, mul2(Pf0, Pf1), fma2(Pf1, S0, S1), bc(0.f), cs, unused, Pfin);
+                        carry_rev<L, true>(j, mul2(Pr0, Pr1), fma2(Pr1, H0, H1), fma2(Pr1, D0, D1), cdh, cds, Prin);
+                        if (has_right) {  // dh, ds of the column right of the tile reach every lane
+                            cdh = add2(cdh, edge_term_rev<L>(j, Prin, e_dh));
+                            cds = add2(cds, edge_term_rev<L>(j, Prin, e_ds));
+                        }
+                        if (has_left) {   // s of the column left of the tile
+                            float2 e_s = bc(0.f);
+                            if (j == 0) {
+                                const float4 e1 = sedge[(cp * NPp + pp) * (RB + 1) + rr + 1];
+                                e_s = f2(e1.z, e1.w);
+                            }
+                            cs = add2(cs, edge_term_fwd<L>(j, Pfin, e_s));
+                        }
                         float2 cs1 = fma2(Pf0, cs, S0);                           // into columns 4..7
                         float2 cdh1 = fma2(Pr0, cdh, H0), cds1 = fma2(Pr0, cds, D0);  // into columns 3..0
 #pragma unroll
@@ -431,6 +503,14 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         h_l0 = shfl_up2<L>(hrow[STRIP - 1], 1);
                         m_r7.x = j == L - 1 ? 0.f : m_r7.x; m_r7.y = j == L - 1 ? 0.f : m_r7.y;
                         h_l0.x = j == 0 ? 0.f : h_l0.x; h_l0.y = j == 0 ? 0.f : h_l0.y;
+                    }
+                    if (has_right && j == L - 1) m_r7 = mul2(a_r7, e_dh);
+                    if (has_left && j == 0) {
+                        const float4 e1 = sedge[(cp * NPp + pp) * (RB + 1) + rr + 1];
+                        h_l0 = f2(e1.x, e1.y);
+                        if (ch_ok && r0 + rr < H)  // dh, ds of this tile's first column for the tile to the left
+                            P.adj_out[(((int64_t)b * P.dim + d) * NPp + pp) * H + r0 + rr] =
+                                make_float4(dh[0].x, dh[0].y, ds[0].x, ds[0].y);
                     }
                     float duv[STRIP], ddv[STRIP];
                     // dB/dC are summed over the warp's CW channels by transposing through
@@ -464,12 +544,12 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                                 *qb = add2(*qb, dBv);
                                 *qc = add2(*qc, dCv);
                             } else if (ch_ok && j * STRIP + i < W) {
-                                const int64_t og = ((((int64_t)b * P.G + g_) * N + n0) * H + (r0 + rr)) * W + j * STRIP + i;
+                                const int64_t og = ((((int64_t)b * P.G + g_) * N + n0) * H + (r0 + rr)) * P.Wout + j * STRIP + i;
                                 atomicAdd(P.dB + og, dBv.x);
                                 atomicAdd(P.dC + og, dCv.x);
                                 if (n1 < N) {
-                                    atomicAdd(P.dB + og + (int64_t)H * W, dBv.y);
-                                    atomicAdd(P.dC + og + (int64_t)H * W, dCv.y);
+                                    atomicAdd(P.dB + og + (int64_t)H * P.Wout, dBv.y);
+                                    atomicAdd(P.dC + og + (int64_t)H * P.Wout, dCv.y);
                                 }
                             }
                         } else {
@@ -501,12 +581,12 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                                     *qc = add2(*qc, sc2);
                                 } else if (j * STRIP + col < W) {
                                     const int64_t og =
-                                        ((((int64_t)b * P.G + g_) * N + n0) * H + (r0 + rr)) * W + j * STRIP + col;
+                                        ((((int64_t)b * P.G + g_) * N + n0) * H + (r0 + rr)) * P.Wout + j * STRIP + col;
                                     atomicAdd(P.dB + og, sb.x);
                                     atomicAdd(P.dC + og, sc2.x);
                                     if (n1 < N) {
-                                        atomicAdd(P.dB + og + (int64_t)H * W, sb.y);
-                                        atomicAdd(P.dC + og + (int64_t)H * W, sc2.y);
+                                        atomicAdd(P.dB + og + (int64_t)H * P.Wout, sb.y);
+                                        atomicAdd(P.dC + og + (int64_t)H * P.Wout, sc2.y);
                                     }
                                 }
                             }
@@ -562,7 +642,9 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
 
 size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk) {
     const int nw = CG * NPp;
-    const size_t extra = bulk ? 16 + 2 * (size_t)(CG * (32 / L)) * W * (RB * es + RB * eso + (RB + 2) * es) : 0;
+    const int CPh = CG * (32 / L);
+    const size_t extra = (size_t)(2 * CPh * NPp * (RB + 1) * 4 + CPh * 12) * 4 + 16 +
+                         (bulk ? 2 * (size_t)CPh * W * (RB * es + RB * eso + (RB + 2) * es) : 0);
     const int CP = CG * (32 / L);
     switch (L) {
         case 1: return (size_t)((BwdSmem<1>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
@@ -574,30 +656,31 @@ size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, i
     }
 }
 
-template <int L>
+template <int L, int NPC>
 static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) {
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(bwd_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(bwd_kernel<L, NPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    bwd_kernel<L><<<grid, 32 * P.CG * P.NPp, smem, st>>>(P);
+    bwd_kernel<L, NPC><<<grid, 32 * P.CG * P.NPp, smem, st>>>(P);
     return cudaGetLastError();
 }
 
 cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st) {
+    const bool spec = P.NPp == 8 && P.CG == 1;
     const size_t smem = bwd_smem_bytes(L, P.CG, P.NPp, P.CT, P.acc_dbc != 0, P.W, P.io_dt == CS2D_F32 ? 4 : 2,
                                        P.out_dt == CS2D_F32 ? 4 : 2, P.bulk != 0);
     switch (L) {
-        case 1: return launch<1>(P, grid, smem, st);
-        case 2: return launch<2>(P, grid, smem, st);
-        case 4: return launch<4>(P, grid, smem, st);
-        case 8: return launch<8>(P, grid, smem, st);
-        case 16: return launch<16>(P, grid, smem, st);
-        case 32: return launch<32>(P, grid, smem, st);
+        case 1: return spec ? launch<1, 8>(P, grid, smem, st) : launch<1, 0>(P, grid, smem, st);
+        case 2: return spec ? launch<2, 8>(P, grid, smem, st) : launch<2, 0>(P, grid, smem, st);
+        case 4: return spec ? launch<4, 8>(P, grid, smem, st) : launch<4, 0>(P, grid, smem, st);
+        case 8: return spec ? launch<8, 8>(P, grid, smem, st) : launch<8, 0>(P, grid, smem, st);
+        case 16: return spec ? launch<16, 8>(P, grid, smem, st) : launch<16, 0>(P, grid, smem, st);
+        case 32: return spec ? launch<32, 8>(P, grid, smem, st) : launch<32, 0>(P, grid, smem, st);
     }
     return cudaErrorInvalidValue;
 }

@@ -63,6 +63,15 @@ struct Dev {
     int64_t B_bs, B_gs, B_ns, B_hs, C_bs, C_gs, C_ns, C_hs;
     void *out; int64_t o_bs, o_ds, o_hs;  // forward: out; backward: dout
     float2 *saved;                         // [batch][dim][nck][NPp][L*8] checkpoints of h
+    // Column tiling of rows wider than 256 columns: this launch covers one tile (all
+    // tensor pointers are already moved to the tile's first column).  The values that
+    // cross a tile boundary travel through global edge buffers [batch][dim][NPp][H] float4
+    // written by the neighbouring tile's launch: (h.x, h.y, s.x, s.y) of the column left of
+    // the tile, (dh.x, dh.y, ds.x, ds.y) of the column right of it.
+    int tile_left, tile_right;             // the tile has a neighbour on that side
+    int Wout;                              // row pitch (full image width) of du, ddelta, dB, dC
+    const float4 *edge_in; float4 *edge_out;          // h/s edge: read (left side), written (right side)
+    const float4 *adj_in; float4 *adj_out;            // dh/ds edge: read (right side), written (left side)
     // backward only
     float2 *adj;                           // [batch][dim][NPp][L*8] adjoint row between blocks
     void *du, *ddelta;
@@ -287,9 +296,10 @@ __device__ __forceinline__ void unpack8x2(const float2 *row, int L2, int j, floa
 // zero carry-in), optionally a second sequence S sharing the multipliers.
 // Out: the value of the sequence just left of this lane's strip.
 template <int L, bool TWO>
-__device__ __forceinline__ void carry_fwd(int j, float2 P, float2 H, float2 S, float2 &cH, float2 &cS) {
+__device__ __forceinline__ void carry_fwd(int j, float2 P, float2 H, float2 S, float2 &cH, float2 &cS,
+                                          float2 &Pincl) {
     if constexpr (L == 1) {
-        cH = bc(0.f); cS = bc(0.f);
+        cH = bc(0.f); cS = bc(0.f); Pincl = P;
     } else {
 #pragma unroll
         for (int off = 1; off < L; off <<= 1) {
@@ -307,6 +317,7 @@ __device__ __forceinline__ void carry_fwd(int j, float2 P, float2 H, float2 S, f
             }
             P = mul2(P, Pp);
         }
+        Pincl = P;
         cH = shfl_up2<L>(H, 1);
         cS = TWO ? shfl_up2<L>(S, 1) : bc(0.f);
         const bool first = j == 0;
@@ -314,11 +325,36 @@ __device__ __forceinline__ void carry_fwd(int j, float2 P, float2 H, float2 S, f
         cS.x = first ? 0.f : cS.x; cS.y = first ? 0.f : cS.y;
     }
 }
+// A value c_in entering a row of lanes from outside (a column-tile boundary) reaches
+// lane j as P_excl(j) * c_in, P_excl = product of the multipliers of the lanes before it.
+// `Pincl` is the inclusive product a scan returned, `e` the value held by the boundary lane.
+template <int L>
+__device__ __forceinline__ float2 edge_term_fwd(int j, float2 Pincl, float2 e) {
+    float2 cP = bc(1.f);
+    if constexpr (L > 1) {
+        cP = shfl_up2<L>(Pincl, 1);
+        cP.x = j == 0 ? 1.f : cP.x; cP.y = j == 0 ? 1.f : cP.y;
+        e = make_float2(__shfl_sync(0xffffffffu, e.x, 0, L), __shfl_sync(0xffffffffu, e.y, 0, L));
+    }
+    return mul2(cP, e);
+}
+template <int L>
+__device__ __forceinline__ float2 edge_term_rev(int j, float2 Pincl, float2 e) {
+    float2 cP = bc(1.f);
+    if constexpr (L > 1) {
+        cP = shfl_down2<L>(Pincl, 1);
+        cP.x = j == L - 1 ? 1.f : cP.x; cP.y = j == L - 1 ? 1.f : cP.y;
+        e = make_float2(__shfl_sync(0xffffffffu, e.x, L - 1, L), __shfl_sync(0xffffffffu, e.y, L - 1, L));
+    }
+    return mul2(cP, e);
+}
+
 // Same for a reverse (right-to-left) scan: carry = value just right of the strip.
 template <int L, bool TWO>
-__device__ __forceinline__ void carry_rev(int j, float2 P, float2 H, float2 S, float2 &cH, float2 &cS) {
+__device__ __forceinline__ void carry_rev(int j, float2 P, float2 H, float2 S, float2 &cH, float2 &cS,
+                                          float2 &Pincl) {
     if constexpr (L == 1) {
-        cH = bc(0.f); cS = bc(0.f);
+        cH = bc(0.f); cS = bc(0.f); Pincl = P;
     } else {
 #pragma unroll
         for (int off = 1; off < L; off <<= 1) {
@@ -335,6 +371,7 @@ __device__ __forceinline__ void carry_rev(int j, float2 P, float2 H, float2 S, f
             }
             P = mul2(P, Pp);
         }
+        Pincl = P;
         cH = shfl_down2<L>(H, 1);
         cS = TWO ? shfl_down2<L>(S, 1) : bc(0.f);
         const bool last = j == L - 1;
@@ -342,6 +379,10 @@ __device__ __forceinline__ void carry_rev(int j, float2 P, float2 H, float2 S, f
         cS.x = last ? 0.f : cS.x; cS.y = last ? 0.f : cS.y;
     }
 }
+
+// Values of the column just left of a column tile, for the lane that owns the tile's first
+// column: h of the previous row, a of this row, h and s of this row.
+struct LeftEdge { float2 h_prev, a, h, s; };
 
 // One forward row for a strip: given dl (post-softplus delta), dlu = dl*u, B,
 // the previous row (h_up, a_up) and the packed A*log2(e) (+ log2 decay), computes
@@ -354,7 +395,7 @@ __device__ __forceinline__ void row_forward(int j, const float (&dl)[STRIP], con
                                             const float2 (&Bv)[STRIP], float2 A2, float2 lgd,
                                             const float2 (&h_up)[STRIP], const float2 (&a_up)[STRIP],
                                             float2 (&a)[STRIP], float2 (&p)[STRIP], float2 (&h)[STRIP],
-                                            float2 (&s)[STRIP]) {
+                                            float2 (&s)[STRIP], bool has_left, const LeftEdge &le) {
 #pragma unroll
     for (int i = 0; i < STRIP; ++i) {
         a[i] = ex2_2(fma2(bc(dl[i]), A2, lgd));
@@ -366,6 +407,7 @@ __device__ __forceinline__ void row_forward(int j, const float (&dl)[STRIP], con
         aleft0 = shfl_up2<L>(a[STRIP - 1], 1);
         hdiag0.x = j == 0 ? 0.f : hdiag0.x; hdiag0.y = j == 0 ? 0.f : hdiag0.y;
     }
+    if (has_left && j == 0) { hdiag0 = le.h_prev; aleft0 = le.a; }
     // Each strip is folded as two independent 4-column halves so that the serial
     // chains are half as long and twice as many (h and s, low and high half).
     float2 beta[STRIP];
@@ -387,8 +429,12 @@ __device__ __forceinline__ void row_forward(int j, const float (&dl)[STRIP], con
         P0 = mul2(P0, a[i]);
         P1 = mul2(P1, a[HS + i]);
     }
-    float2 ch, cs;
-    carry_fwd<L, WITH_S>(j, mul2(P0, P1), fma2(P1, H0, H1), WITH_S ? fma2(P1, S0, S1) : bc(0.f), ch, cs);
+    float2 ch, cs, Pin;
+    carry_fwd<L, WITH_S>(j, mul2(P0, P1), fma2(P1, H0, H1), WITH_S ? fma2(P1, S0, S1) : bc(0.f), ch, cs, Pin);
+    if (has_left) {  // h, s of the column left of the tile enter at lane 0 and reach every lane
+        ch = add2(ch, edge_term_fwd<L>(j, Pin, le.h));
+        if (WITH_S) cs = add2(cs, edge_term_fwd<L>(j, Pin, le.s));
+    }
     float2 ch1 = fma2(P0, ch, H0), cs1 = WITH_S ? fma2(P0, cs, S0) : bc(0.f);  // carries into the high half
 #pragma unroll
     for (int i = 0; i < HS; ++i) {

@@ -29,23 +29,32 @@ struct FwdSmem {
     }
     // after the tiles: two mbarriers (4 floats), then two stages of raw row blocks
     // (u: RB rows, delta: RB+1 rows per channel, in the input dtype)
-    static __host__ __device__ constexpr int bars(int CP, int NPp, int nw) { return total(CP, NPp, nw); }
-    static __host__ __device__ constexpr int raw(int CP, int NPp, int nw) { return total(CP, NPp, nw) + 4; }
+    // left-edge values of a column tile: [CP][NPp][RB+1] float4 (h, s of rows r0-1..r0+RB-1)
+    // and the softplus'd delta of the column left of the tile [CP][RB] (padded to 4 floats)
+    static __host__ __device__ constexpr int edge(int CP, int NPp, int nw) { return total(CP, NPp, nw); }
+    static __host__ __device__ constexpr int edl(int CP, int NPp, int nw) { return edge(CP, NPp, nw) + CP * NPp * (RB + 1) * 4; }
+    static __host__ __device__ constexpr int bars(int CP, int NPp, int nw) { return edl(CP, NPp, nw) + CP * 4; }
+    static __host__ __device__ constexpr int raw(int CP, int NPp, int nw) { return bars(CP, NPp, nw) + 4; }
     static __host__ __device__ constexpr int stage_bytes(int CP, int W, int es) { return CP * (2 * RB + 1) * W * es; }
 };
 
-template <int L>
+// NPC = 8 specialises the common geometry (8 state-pair slots, one channel group, 8 warps) so
+// that every shared-memory offset is a compile-time constant; NPC = 0 reads it from P.
+template <int L, int NPC>
 __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
     using S = FwdSmem<L>;
     constexpr int Wp = S::Wp, CW = S::CW, T4 = Wp / 4, CS4 = S::CS4, CS5 = S::CS5, L4 = 4 * L, L2 = 2 * L;
     extern __shared__ __align__(16) float smem[];
-    const int NPp = P.NPp, CG = P.CG, CP = CG * CW;
-    const int nthr = blockDim.x, nw = nthr >> 5;  // NPp * CG warps
+    const int NPp = NPC ? NPC : P.NPp, CG = NPC ? MAX_WARPS / NPC : P.CG, CP = CG * CW;
+    const int nw = NPp * CG, nthr = nw * 32;
     float *su = smem + S::u(CP);
     float *sdl = smem + S::dl(CP);   // row 0 = row above the block
     float *sy = smem + S::y(CP);     // per-warp partial sums over the warp's state pair
     float2 *sB = reinterpret_cast<float2 *>(smem + S::B(CP, nw));
     float2 *sC = sB + NPp * RB * Wp;
+    float4 *sedge = reinterpret_cast<float4 *>(smem + S::edge(CP, NPp, nw));
+    float *sedl = smem + S::edl(CP, NPp, nw);
+    const bool has_left = P.tile_left != 0;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int j = lane & (L - 1), cl = lane / L;
@@ -187,6 +196,28 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                     *reinterpret_cast<float4 *>(sdl + sc * CS5 + rr * Wp + pos4<L>(t)) = x;
                 }
                 if (pass == 0) stage_BC<L>(P, b, g, r0, nr, sB, sC);
+                if (has_left) {  // column left of this tile: h, s written by the tile to the left; delta
+                    for (int it = tid; it < CP * NPp * (RB + 1); it += nthr) {
+                        const int k = it % (RB + 1), q = (it / (RB + 1)) % NPp, sc = it / ((RB + 1) * NPp);
+                        const int r = r0 - 1 + k;
+                        float4 e = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (r >= 0 && r < H && ch0 + sc < nch)
+                            e = __ldg(P.edge_in + (((int64_t)b * P.dim + dbase + ch0 + sc) * NPp + q) * H + r);
+                        sedge[it] = e;
+                    }
+                    for (int it = tid; it < CP * RB; it += nthr) {
+                        const int rr = it % RB, sc = it / RB;
+                        float x = 0.f;
+                        if (rr < nr && ch0 + sc < nch) {
+                            const int sdd = (dbase + ch0 + sc) / P.drep;
+                            x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds +
+                                                     (int64_t)(r0 + rr) * P.dl_hs - 1, P.io_dt);
+                            if (P.bias) x += __ldg(P.bias + sdd);
+                            if (P.softplus) x = softplus20(x);
+                        }
+                        sedl[it] = x;
+                    }
+                }
             }
         }
         __syncthreads();
@@ -225,7 +256,16 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                     unpack8x2(sB + (pp * RB + rr) * Wp, L2, j, Bv);
                     unpack8x2(sC + (pp * RB + rr) * Wp, L2, j, Cv);
                     float2 a[STRIP], p[STRIP], h[STRIP], s[STRIP];
-                    row_forward<L, true>(j, dl, dlu, Bv, A2, lgd, h_up, a_up, a, p, h, s);
+                    LeftEdge le = {bc(0.f), bc(0.f), bc(0.f), bc(0.f)};
+                    if (has_left && j == 0) {
+                        const float4 e0 = sedge[(cp * NPp + pp) * (RB + 1) + rr], e1 = sedge[(cp * NPp + pp) * (RB + 1) + rr + 1];
+                        le.h_prev = f2(e0.x, e0.y); le.h = f2(e1.x, e1.y); le.s = f2(e1.z, e1.w);
+                        le.a = ex2_2(fma2(bc(sedl[cp * RB + rr]), A2, lgd));
+                    }
+                    row_forward<L, true>(j, dl, dlu, Bv, A2, lgd, h_up, a_up, a, p, h, s, has_left, le);
+                    if (P.tile_right && j == L - 1 && ch_ok && r0 + rr < H)  // last column of a full tile
+                        P.edge_out[(((int64_t)b * P.dim + d) * NPp + pp) * H + r0 + rr] =
+                            make_float4(h[STRIP - 1].x, h[STRIP - 1].y, s[STRIP - 1].x, s[STRIP - 1].y);
                     float yv[STRIP];
 #pragma unroll
                     for (int i = 0; i < STRIP; ++i) {
@@ -251,7 +291,9 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
 
 size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk) {
     const int nw = CG * NPp;
-    const size_t extra = bulk ? 16 + 2 * (size_t)(CG * (32 / L)) * (2 * RB + 1) * W * es : 0;
+    const int CPh = CG * (32 / L);
+    const size_t extra = (size_t)(CPh * NPp * (RB + 1) * 4 + CPh * 4) * 4 + 16 +
+                         (bulk ? 2 * (size_t)CPh * (2 * RB + 1) * W * es : 0);
     const int CP = CG * (32 / L);
     switch (L) {
         case 1: return (size_t)FwdSmem<1>::total(CP, NPp, nw) * 4 + extra;
@@ -263,27 +305,30 @@ size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk) {
     }
 }
 
-template <int L>
+template <int L, int NPC>
 static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) {
-    static bool attr_done = false;  // per template instance; the value only ever grows to the device limit
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(fwd_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    static bool attr_done[64] = {};  // per template instance and device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(fwd_kernel<L, NPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
-        attr_done = true;
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    fwd_kernel<L><<<grid, 32 * P.CG * P.NPp, smem, st>>>(P);
+    fwd_kernel<L, NPC><<<grid, 32 * P.CG * P.NPp, smem, st>>>(P);
     return cudaGetLastError();
 }
 
 cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st) {
+    const bool spec = P.NPp == 8 && P.CG == 1;
     const size_t smem = fwd_smem_bytes(L, P.CG, P.NPp, P.W, P.io_dt == CS2D_F32 ? 4 : 2, P.bulk != 0);
     switch (L) {
-        case 1: return launch<1>(P, grid, smem, st);
-        case 2: return launch<2>(P, grid, smem, st);
-        case 4: return launch<4>(P, grid, smem, st);
-        case 8: return launch<8>(P, grid, smem, st);
-        case 16: return launch<16>(P, grid, smem, st);
-        case 32: return launch<32>(P, grid, smem, st);
+        case 1: return spec ? launch<1, 8>(P, grid, smem, st) : launch<1, 0>(P, grid, smem, st);
+        case 2: return spec ? launch<2, 8>(P, grid, smem, st) : launch<2, 0>(P, grid, smem, st);
+        case 4: return spec ? launch<4, 8>(P, grid, smem, st) : launch<4, 0>(P, grid, smem, st);
+        case 8: return spec ? launch<8, 8>(P, grid, smem, st) : launch<8, 0>(P, grid, smem, st);
+        case 16: return spec ? launch<16, 8>(P, grid, smem, st) : launch<16, 0>(P, grid, smem, st);
+        case 32: return spec ? launch<32, 8>(P, grid, smem, st) : launch<32, 0>(P, grid, smem, st);
     }
     return cudaErrorInvalidValue;
 }

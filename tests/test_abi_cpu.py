@@ -48,6 +48,11 @@ def test_sizes_without_gpu():
     assert L.cs2d_bwd_scratch_bytes(ctypes.byref(p)) == 2 * 8 * 8 * 64 * 8
     p1 = _problem(dstate=1, nrows=7, ncols=7)
     assert L.cs2d_saved_bytes(ctypes.byref(p1)) == 2 * 8 * 2 * 1 * 8 * 8
+    # 336 columns = a 256-column tile + an 80-column tile (padded to 128) + one edge buffer
+    pw = _problem(ncols=336)
+    per = 2 * 8 * 8 * 8  # batch x dim x pair slots x bytes per float2
+    assert L.cs2d_saved_bytes(ctypes.byref(pw)) == per * 14 * (256 + 128) + 2 * 8 * 8 * 56 * 16
+    assert L.cs2d_bwd_scratch_bytes(ctypes.byref(pw)) == per * (256 + 128) + 2 * 8 * 8 * 56 * 16
 
 
 @pytest.mark.parametrize("over,msg", [
@@ -56,7 +61,6 @@ def test_sizes_without_gpu():
     (dict(delta_dim=3), "delta_dim"),
     (dict(io_dtype=7), "input type"),
     (dict(io_dtype=_lib.F32, out_dtype=_lib.BF16), "out/dout"),
-    (dict(ncols=300), "wider"),
     (dict(u=None), "must be given"),
 ])
 def test_validation_happens_before_any_cuda_call(over, msg):

@@ -76,6 +76,9 @@ CASES = [
     ((3, 1, 1, 2, 1, 1), torch.float32, {}),                      # a single pixel
     ((1, 4, 40, 16, 16, 128), torch.bfloat16, {}),                # segmentation-scale width
     ((1, 1, 70, 2, 5, 6), torch.float32, {}),                     # more channels than one CTA pass
+    ((1, 2, 3, 16, 9, 300), torch.float32, {}),                   # two column tiles (256 + 44)
+    ((1, 1, 2, 4, 6, 600), torch.float32, {"a_decay": 0.8}),      # three column tiles
+    ((1, 4, 4, 16, 20, 336), torch.bfloat16, {}),                 # detection-scale width
 ]
 
 
@@ -143,10 +146,6 @@ def test_errors_match_the_reference_conditions():
                  torch.zeros(1, 3, 4, 8, 8, device="cuda"), None, None, True, False, None)
     with pytest.raises(RuntimeError, match="last dimension"):
         cs2d.fwd(d["u"].transpose(2, 3), d["delta"], d["A"], d["B"], d["C"], None, None, True, False, None)
-    with pytest.raises(RuntimeError, match="wider"):
-        w = make_inputs(1, 1, 1, 2, 2, 300)
-        w = _dev(w)
-        cs2d.fwd(w["u"], w["delta"], w["A"], w["B"], w["C"], None, None, True, False, None)
 
 
 # ---- properties at the full size of the headline configuration ---------------------
