@@ -65,13 +65,18 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, Geometry *g)
     const int slots = kSMs * (backward ? 1 : 2);
     // Among 1..8 passes pick the one whose grid fills whole waves best (a grid of
     // 5.2 waves wastes 14% of the machine in its last wave); ties go to more passes.
+    // Cost model: a CTA pays the B/C staging of a row block once (about one pass worth of
+    // work when a warp holds a single channel, 1/CW of it otherwise) plus np passes, and the
+    // launch takes waves(np) rounds of CTAs.
     int npass = 1;
-    double best = -1.0;
+    double best = 1e300;
+    const double stage = 1.0 / (32 / L);
     for (int np = 1; np <= (pmax < 8 ? pmax : 8); ++np) {
-        const int64_t grid = (int64_t)p->batch * p->n_groups * ((dpg + np * CP - 1) / (np * CP));
+        const int64_t chunks = (dpg + np * CP - 1) / (np * CP);
+        const int64_t grid = (int64_t)p->batch * p->n_groups * chunks;
         const int64_t waves = (grid + slots - 1) / slots;
-        const double eff = (double)grid / (double)(waves * slots) + 0.004 * np;
-        if (eff > best) { best = eff; npass = np; }
+        const double cost = (double)waves * (stage + np);
+        if (cost < best - 1e-9) { best = cost; npass = np; }
     }
     g->acc = 1;
     g->bulk = bulk_ok ? 1 : 0;

@@ -52,7 +52,8 @@ struct BwdSmem {
 
 // NPC = 8 specialises the common geometry (8 state-pair slots, one channel group, 8 warps) so
 // that every shared-memory offset is a compile-time constant; NPC = 0 reads it from P.
-template <int L, int NPC>
+// TILED compiles the column-tile edge handling in; the common single-tile launch leaves it out.
+template <int L, int NPC, bool TILED>
 __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
     using S = BwdSmem<L>;
     constexpr int Wp = S::Wp, CW = S::CW, T4 = Wp / 4, CS4 = S::CS4, CS6 = S::CS6, L4 = 4 * L, L2 = 2 * L;
@@ -109,7 +110,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
     float4 *sadj = sedge + CP * NPp * (RB + 1);
     float *sedl_l = reinterpret_cast<float *>(sadj + CP * NPp * (RB + 1));   // [CP][RB]
     float *sedl_r = sedl_l + CP * 4;                                          // [CP][RB+1] (pitch 8)
-    const bool has_left = P.tile_left != 0, has_right = P.tile_right != 0;
+    const bool has_left = TILED && P.tile_left != 0, has_right = TILED && P.tile_right != 0;
     uint64_t *bars = reinterpret_cast<uint64_t *>(sedl_r + CP * 8);
     unsigned char *raw = reinterpret_cast<unsigned char *>(bars + 2);
     const int stage_bytes = CP * W * (RB * es + RB * eso + (RB + 2) * es);
@@ -656,31 +657,37 @@ size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, i
     }
 }
 
-template <int L, int NPC>
+template <int L, int NPC, bool TILED>
 static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) {
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(bwd_kernel<L, NPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(bwd_kernel<L, NPC, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    bwd_kernel<L, NPC><<<grid, 32 * P.CG * P.NPp, smem, st>>>(P);
+    bwd_kernel<L, NPC, TILED><<<grid, 32 * P.CG * P.NPp, smem, st>>>(P);
     return cudaGetLastError();
 }
 
 cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st) {
-    const bool spec = P.NPp == 8 && P.CG == 1;
+    const bool spec = P.NPp == 8 && P.CG == 1, tiled = P.tile_left || P.tile_right;
     const size_t smem = bwd_smem_bytes(L, P.CG, P.NPp, P.CT, P.acc_dbc != 0, P.W, P.io_dt == CS2D_F32 ? 4 : 2,
                                        P.out_dt == CS2D_F32 ? 4 : 2, P.bulk != 0);
     switch (L) {
-        case 1: return spec ? launch<1, 8>(P, grid, smem, st) : launch<1, 0>(P, grid, smem, st);
-        case 2: return spec ? launch<2, 8>(P, grid, smem, st) : launch<2, 0>(P, grid, smem, st);
-        case 4: return spec ? launch<4, 8>(P, grid, smem, st) : launch<4, 0>(P, grid, smem, st);
-        case 8: return spec ? launch<8, 8>(P, grid, smem, st) : launch<8, 0>(P, grid, smem, st);
-        case 16: return spec ? launch<16, 8>(P, grid, smem, st) : launch<16, 0>(P, grid, smem, st);
-        case 32: return spec ? launch<32, 8>(P, grid, smem, st) : launch<32, 0>(P, grid, smem, st);
+        case 1: return tiled ? (spec ? launch<1, 8, true>(P, grid, smem, st) : launch<1, 0, true>(P, grid, smem, st))
+                             : (spec ? launch<1, 8, false>(P, grid, smem, st) : launch<1, 0, false>(P, grid, smem, st));
+        case 2: return tiled ? (spec ? launch<2, 8, true>(P, grid, smem, st) : launch<2, 0, true>(P, grid, smem, st))
+                             : (spec ? launch<2, 8, false>(P, grid, smem, st) : launch<2, 0, false>(P, grid, smem, st));
+        case 4: return tiled ? (spec ? launch<4, 8, true>(P, grid, smem, st) : launch<4, 0, true>(P, grid, smem, st))
+                             : (spec ? launch<4, 8, false>(P, grid, smem, st) : launch<4, 0, false>(P, grid, smem, st));
+        case 8: return tiled ? (spec ? launch<8, 8, true>(P, grid, smem, st) : launch<8, 0, true>(P, grid, smem, st))
+                             : (spec ? launch<8, 8, false>(P, grid, smem, st) : launch<8, 0, false>(P, grid, smem, st));
+        case 16: return tiled ? (spec ? launch<16, 8, true>(P, grid, smem, st) : launch<16, 0, true>(P, grid, smem, st))
+                             : (spec ? launch<16, 8, false>(P, grid, smem, st) : launch<16, 0, false>(P, grid, smem, st));
+        case 32: return tiled ? (spec ? launch<32, 8, true>(P, grid, smem, st) : launch<32, 0, true>(P, grid, smem, st))
+                             : (spec ? launch<32, 8, false>(P, grid, smem, st) : launch<32, 0, false>(P, grid, smem, st));
     }
     return cudaErrorInvalidValue;
 }

@@ -40,7 +40,8 @@ struct FwdSmem {
 
 // NPC = 8 specialises the common geometry (8 state-pair slots, one channel group, 8 warps) so
 // that every shared-memory offset is a compile-time constant; NPC = 0 reads it from P.
-template <int L, int NPC>
+// TILED compiles the column-tile edge handling in; the common single-tile launch leaves it out.
+template <int L, int NPC, bool TILED>
 __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
     using S = FwdSmem<L>;
     constexpr int Wp = S::Wp, CW = S::CW, T4 = Wp / 4, CS4 = S::CS4, CS5 = S::CS5, L4 = 4 * L, L2 = 2 * L;
@@ -54,7 +55,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
     float2 *sC = sB + NPp * RB * Wp;
     float4 *sedge = reinterpret_cast<float4 *>(smem + S::edge(CP, NPp, nw));
     float *sedl = smem + S::edl(CP, NPp, nw);
-    const bool has_left = P.tile_left != 0;
+    const bool has_left = TILED && P.tile_left != 0;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int j = lane & (L - 1), cl = lane / L;
@@ -263,7 +264,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                         le.a = ex2_2(fma2(bc(sedl[cp * RB + rr]), A2, lgd));
                     }
                     row_forward<L, true>(j, dl, dlu, Bv, A2, lgd, h_up, a_up, a, p, h, s, has_left, le);
-                    if (P.tile_right && j == L - 1 && ch_ok && r0 + rr < H)  // last column of a full tile
+                    if (TILED && P.tile_right && j == L - 1 && ch_ok && r0 + rr < H)  // last column of a full tile
                         P.edge_out[(((int64_t)b * P.dim + d) * NPp + pp) * H + r0 + rr] =
                             make_float4(h[STRIP - 1].x, h[STRIP - 1].y, s[STRIP - 1].x, s[STRIP - 1].y);
                     float yv[STRIP];
@@ -305,30 +306,36 @@ size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk) {
     }
 }
 
-template <int L, int NPC>
+template <int L, int NPC, bool TILED>
 static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) {
     static bool attr_done[64] = {};  // per template instance and device
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(fwd_kernel<L, NPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(fwd_kernel<L, NPC, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    fwd_kernel<L, NPC><<<grid, 32 * P.CG * P.NPp, smem, st>>>(P);
+    fwd_kernel<L, NPC, TILED><<<grid, 32 * P.CG * P.NPp, smem, st>>>(P);
     return cudaGetLastError();
 }
 
 cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st) {
-    const bool spec = P.NPp == 8 && P.CG == 1;
+    const bool spec = P.NPp == 8 && P.CG == 1, tiled = P.tile_left || P.tile_right;
     const size_t smem = fwd_smem_bytes(L, P.CG, P.NPp, P.W, P.io_dt == CS2D_F32 ? 4 : 2, P.bulk != 0);
     switch (L) {
-        case 1: return spec ? launch<1, 8>(P, grid, smem, st) : launch<1, 0>(P, grid, smem, st);
-        case 2: return spec ? launch<2, 8>(P, grid, smem, st) : launch<2, 0>(P, grid, smem, st);
-        case 4: return spec ? launch<4, 8>(P, grid, smem, st) : launch<4, 0>(P, grid, smem, st);
-        case 8: return spec ? launch<8, 8>(P, grid, smem, st) : launch<8, 0>(P, grid, smem, st);
-        case 16: return spec ? launch<16, 8>(P, grid, smem, st) : launch<16, 0>(P, grid, smem, st);
-        case 32: return spec ? launch<32, 8>(P, grid, smem, st) : launch<32, 0>(P, grid, smem, st);
+        case 1: return tiled ? (spec ? launch<1, 8, true>(P, grid, smem, st) : launch<1, 0, true>(P, grid, smem, st))
+                             : (spec ? launch<1, 8, false>(P, grid, smem, st) : launch<1, 0, false>(P, grid, smem, st));
+        case 2: return tiled ? (spec ? launch<2, 8, true>(P, grid, smem, st) : launch<2, 0, true>(P, grid, smem, st))
+                             : (spec ? launch<2, 8, false>(P, grid, smem, st) : launch<2, 0, false>(P, grid, smem, st));
+        case 4: return tiled ? (spec ? launch<4, 8, true>(P, grid, smem, st) : launch<4, 0, true>(P, grid, smem, st))
+                             : (spec ? launch<4, 8, false>(P, grid, smem, st) : launch<4, 0, false>(P, grid, smem, st));
+        case 8: return tiled ? (spec ? launch<8, 8, true>(P, grid, smem, st) : launch<8, 0, true>(P, grid, smem, st))
+                             : (spec ? launch<8, 8, false>(P, grid, smem, st) : launch<8, 0, false>(P, grid, smem, st));
+        case 16: return tiled ? (spec ? launch<16, 8, true>(P, grid, smem, st) : launch<16, 0, true>(P, grid, smem, st))
+                             : (spec ? launch<16, 8, false>(P, grid, smem, st) : launch<16, 0, false>(P, grid, smem, st));
+        case 32: return tiled ? (spec ? launch<32, 8, true>(P, grid, smem, st) : launch<32, 0, true>(P, grid, smem, st))
+                             : (spec ? launch<32, 8, false>(P, grid, smem, st) : launch<32, 0, false>(P, grid, smem, st));
     }
     return cudaErrorInvalidValue;
 }
