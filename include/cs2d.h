@@ -115,6 +115,32 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
              float *dD, float *ddelta_bias, float *dA_decay, void *stream);
 
 /*
+ * Scan directions for the four-corner CrossScan.  The reference kernel scans one
+ * orientation only and leaves "change the scan order per group" as a TODO
+ * (include/cusoflex/selective_scan_fwd_kernel_oflex.cuh:140); its caller has to
+ * materialise flipped copies.  Here group g (0 <= g < n_groups <= 32) walks the
+ * image rows bottom-up when bit g of flip_rows_mask is set and the columns
+ * right-to-left when bit g of flip_cols_mask is set, while every tensor stays in
+ * IMAGE coordinates (the flips are index maps inside the kernels).  shared_input
+ * bit 0: u has dim/n_groups channels that all groups read - channel d of group g
+ * reads u channel d - g*dim/n_groups, u_ds being the stride of those channels;
+ * bit 1: the same for dout in the backward.  out, du, ddelta keep `dim` channels
+ * (one result per direction).  Not yet combined with ncols > 256.
+ */
+typedef struct {
+    uint32_t flip_rows_mask, flip_cols_mask;
+    int32_t shared_input;
+} cs2d_dirs;
+
+/* cs2d_fwd / cs2d_bwd with scan directions (dirs may be NULL = cs2d_fwd / cs2d_bwd). */
+int cs2d_fwd_dir(const cs2d_problem *p, const cs2d_dirs *dirs, void *out, int64_t out_bs, int64_t out_ds,
+                 int64_t out_hs, void *saved, void *stream);
+int cs2d_bwd_dir(const cs2d_problem *p, const cs2d_dirs *dirs, const void *dout, int64_t dout_bs,
+                 int64_t dout_ds, int64_t dout_hs, const void *saved, void *scratch, void *du, void *ddelta,
+                 float *dA, float *dB, float *dC, float *dD, float *ddelta_bias, float *dA_decay,
+                 void *stream);
+
+/*
  * Backward without any allocation on the caller's side: identical to cs2d_bwd
  * except that the scratch buffer is a fixed device array inside the library
  * (CS2D_NOALLOC_SCRATCH_BYTES per GPU, held from library load to process exit).

@@ -14,6 +14,12 @@ NOALLOC_SCRATCH_BYTES = 32 << 20  # CS2D_NOALLOC_SCRATCH_BYTES
 _i32, _i64, _p = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p
 
 
+class Dirs(ctypes.Structure):
+    """Mirror of ``cs2d_dirs``."""
+    _fields_ = [("flip_rows_mask", ctypes.c_uint32), ("flip_cols_mask", ctypes.c_uint32),
+                ("shared_input", ctypes.c_int32)]
+
+
 class Problem(ctypes.Structure):
     """Mirror of ``cs2d_problem``."""
     _fields_ = (
@@ -56,6 +62,12 @@ def lib():
         L.cs2d_fwd.argtypes = [ctypes.POINTER(Problem), vp, i64, i64, i64, vp, vp]
         L.cs2d_bwd.restype = ctypes.c_int
         L.cs2d_bwd.argtypes = [ctypes.POINTER(Problem), vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+        dp = ctypes.POINTER(Dirs)
+        L.cs2d_fwd_dir.restype = ctypes.c_int
+        L.cs2d_fwd_dir.argtypes = [ctypes.POINTER(Problem), dp, vp, i64, i64, i64, vp, vp]
+        L.cs2d_bwd_dir.restype = ctypes.c_int
+        L.cs2d_bwd_dir.argtypes = [ctypes.POINTER(Problem), dp, vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
+                                   vp]
         L.cs2d_bwd_noalloc.restype = ctypes.c_int
         L.cs2d_bwd_noalloc.argtypes = [ctypes.POINTER(Problem), vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
         L.cs2d_last_error.restype = ctypes.c_char_p

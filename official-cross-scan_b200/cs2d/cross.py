@@ -13,17 +13,32 @@ where ``y_k`` is the scan of direction k (0: rows down / columns right, 1: rows
 down / columns left, 2: rows up / columns right, 3: rows up / columns left)
 over ``u[b, d]`` with the direction's own ``delta[b, k*D+d]``, ``A[k*D+d]``,
 ``B[b, k]``, ``C[b, k]``, ``D[k*D+d]``, ``delta_bias[k*D+d]``; every tensor is in
-image coordinates.  The scan itself runs in the CUDA kernels (``ops.fwd`` /
-``ops.bwd``, one launch for all four directions); flips and the weighted merge
-are done here with torch ops for now.
+image coordinates.
+
+All four directions run in ONE kernel launch each way.  The kernels apply the
+flips as index maps while they stage tiles and write results
+(``cs2d_fwd_dir`` / ``cs2d_bwd_dir``), and the K directions read the same
+``u``: nothing is flipped or replicated in memory.  What remains in torch is
+the weighted sum over the K direction planes (y, du, dw).  Rows wider than 256
+columns take the composed path (materialised flips around ``ops.fwd`` /
+``ops.bwd``) until direction maps and column tiles are combined.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
-from . import ops
+from . import _lib, ops
 
 _FLIPS = ((), (-1,), (-2,), (-2, -1))  # k: 0 none, 1 columns, 2 rows, 3 both
+_MAX_DIRECT_COLS = 256
+
+
+def _masks(K):
+    rows = sum(1 << k for k in range(K) if k % 4 in (2, 3))
+    cols = sum(1 << k for k in range(K) if k % 4 in (1, 3))
+    return rows, cols
 
 
 def _flip(t, k):
@@ -31,15 +46,64 @@ def _flip(t, k):
 
 
 def _to_scan(t, K, per_dir):
-    """(b, K*per_dir, h, w) in image coordinates -> every direction in its scan order."""
     b, _, h, w = t.shape
     v = t.view(b, K, per_dir, h, w)
     return torch.stack([_flip(v[:, k], k) for k in range(K)], 1).reshape(b, K * per_dir, h, w)
 
 
 def _to_scan5(t):
-    """(b, K, n, h, w) -> every direction in its scan order."""
     return torch.stack([_flip(t[:, k], k) for k in range(t.size(1))], 1)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _dir_forward(u, delta, A, B, C, D, delta_bias, delta_softplus):
+    """One launch for all directions; returns per-direction outputs (b, K*d, h, w) fp32 and the saved state."""
+    L = _lib.lib()
+    K, dim = B.size(1), A.size(0)
+    p = ops._problem(u, delta, A, B, C, D, delta_bias, None, delta_softplus, torch.float32, "cross_scan_fwd",
+                     shared_u_dim=dim)
+    rows, cols = _masks(K)
+    dirs = _lib.Dirs(rows, cols, 1)
+    nbytes = L.cs2d_saved_bytes(ctypes.byref(p))
+    if nbytes == 0:
+        raise RuntimeError(f"cs2d forward: {_lib.last_error()}")
+    with torch.cuda.device(u.device):
+        out = torch.empty(u.size(0), dim, u.size(2), u.size(3), dtype=torch.float32, device=u.device)
+        saved = torch.empty(nbytes // 4, dtype=torch.float32, device=u.device)
+        rc = L.cs2d_fwd_dir(ctypes.byref(p), ctypes.byref(dirs), _ptr(out), out.stride(0), out.stride(1),
+                            out.stride(2), _ptr(saved), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    ops._raise_on(rc, "forward")
+    return out, saved
+
+
+def _dir_backward(u, delta, A, B, C, D, delta_bias, g, saved, delta_softplus):
+    """g: per-direction output gradient (b, K*d, h, w) fp32 in image coordinates."""
+    L = _lib.lib()
+    K, dim, n = B.size(1), A.size(0), A.size(1)
+    dev = u.device
+    p = ops._problem(u, delta, A, B, C, D, delta_bias, None, delta_softplus, torch.float32, "cross_scan_bwd",
+                     shared_u_dim=dim)
+    rows, cols = _masks(K)
+    dirs = _lib.Dirs(rows, cols, 1)  # u shared; g is per direction (it carries the fusion weight)
+    with torch.cuda.device(dev):
+        shape = (u.size(0), dim, u.size(2), u.size(3))
+        du = torch.empty(shape, dtype=u.dtype, device=dev)
+        ddelta = torch.empty(shape, dtype=u.dtype, device=dev)
+        total, parts = ops.param_grad_layout(dim, n, D is not None, delta_bias is not None, False)
+        flat = torch.zeros(total, dtype=torch.float32, device=dev)
+        part = lambda name: flat[parts[name][0]:parts[name][0] + parts[name][1]] if name in parts else None
+        dB = torch.zeros(tuple(B.shape), dtype=torch.float32, device=dev)
+        dC = torch.zeros(tuple(C.shape), dtype=torch.float32, device=dev)
+        scratch = torch.empty(L.cs2d_bwd_scratch_bytes(ctypes.byref(p)) // 4, dtype=torch.float32, device=dev)
+        rc = L.cs2d_bwd_dir(ctypes.byref(p), ctypes.byref(dirs), _ptr(g), g.stride(0), g.stride(1), g.stride(2),
+                            _ptr(saved), _ptr(scratch), _ptr(du), _ptr(ddelta), _ptr(part("dA")), _ptr(dB), _ptr(dC),
+                            _ptr(part("dD")), _ptr(part("ddelta_bias")), None,
+                            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    ops._raise_on(rc, "backward")
+    return du, ddelta, part("dA").view(dim, n), dB.to(B.dtype), dC.to(C.dtype), part("dD"), part("ddelta_bias")
 
 
 class CrossScan2D(torch.autograd.Function):
@@ -49,29 +113,42 @@ class CrossScan2D(torch.autograd.Function):
         K = B.size(1)
         if delta.size(1) != K * d or A.size(0) != K * d or tuple(w.shape) != (K, d):
             raise RuntimeError("expected delta (b, K*D, h, w), A (K*D, n), w (K, D)")
-        us = torch.cat([_flip(u, k) for k in range(K)], 1).contiguous()
-        ds = _to_scan(delta, K, d).contiguous()
-        Bs, Cs = _to_scan5(B).contiguous(), _to_scan5(C).contiguous()
-        out, x, x_v, x_sd = ops.fwd(us, ds, A, Bs, Cs, D, delta_bias, delta_softplus, True, None)
-        yk = torch.stack([_flip(out[:, k * d:(k + 1) * d], k) for k in range(K)], 1)   # (b, K, d, h, w) fp32
-        y = (yk * w.float()[None, :, :, None, None]).sum(1)
-        ctx.save_for_backward(us, ds, A, Bs, Cs, D, delta_bias, w, yk, x, x_v, x_sd)
+        ctx.direct = wd <= _MAX_DIRECT_COLS
         ctx.delta_softplus = delta_softplus
+        if ctx.direct:
+            u, delta, B, C = u.contiguous(), delta.contiguous(), B.contiguous(), C.contiguous()
+            out, saved = _dir_forward(u, delta, A, B, C, D, delta_bias, delta_softplus)
+            yk = out.view(b, K, d, h, wd)                       # per direction, image coordinates, fp32
+            ctx.save_for_backward(u, delta, A, B, C, D, delta_bias, w, yk, saved)
+        else:
+            us = torch.cat([_flip(u, k) for k in range(K)], 1).contiguous()
+            ds = _to_scan(delta, K, d).contiguous()
+            Bs, Cs = _to_scan5(B).contiguous(), _to_scan5(C).contiguous()
+            out, x, x_v, x_sd = ops.fwd(us, ds, A, Bs, Cs, D, delta_bias, delta_softplus, True, None)
+            yk = torch.stack([_flip(out[:, k * d:(k + 1) * d], k) for k in range(K)], 1)
+            ctx.save_for_backward(us, ds, A, Bs, Cs, D, delta_bias, w, yk, x_v)
+        y = (yk * w.float()[None, :, :, None, None]).sum(1)
         return y.to(u.dtype)
 
     @staticmethod
     def backward(ctx, dy):
-        us, ds, A, Bs, Cs, D, delta_bias, w, yk, x, x_v, x_sd = ctx.saved_tensors
+        u, delta, A, B, C, D, delta_bias, w, yk, saved = ctx.saved_tensors
         b, K, d, h, wd = yk.shape
         dyf = dy.float()
         dw = (dyf[:, None] * yk).sum((0, 3, 4)).to(w.dtype)
-        g = torch.cat([_flip(dyf * w.float()[k][None, :, None, None], k) for k in range(K)], 1).contiguous()
-        du_s, dd_s, dA, dB_s, dC_s, dD, dbias, _ = ops.bwd(us, ds, A, Bs, Cs, D, delta_bias, g, x, x_v,
-                                                           ctx.delta_softplus, None, x_sd)
-        du = sum(_flip(du_s[:, k * d:(k + 1) * d].float(), k) for k in range(K)).to(us.dtype)
-        ddelta = _to_scan(dd_s, K, d)          # flips are involutions: the same map goes back
-        dB, dC = _to_scan5(dB_s), _to_scan5(dC_s)
-        return du, ddelta, dA, dB, dC, dw, dD, dbias, None
+        gk = dyf[:, None] * w.float()[None, :, :, None, None]   # (b, K, d, h, w): gradient of each y_k
+        if ctx.direct:
+            g = gk.reshape(b, K * d, h, wd).contiguous()
+            du_k, ddelta, dA, dB, dC, dD, dbias = _dir_backward(u, delta, A, B, C, D, delta_bias, g, saved,
+                                                                ctx.delta_softplus)
+            du = du_k.view(b, K, d, h, wd).float().sum(1).to(u.dtype)
+            return du, ddelta, dA, dB, dC, dw, dD, dbias, None
+        g = torch.cat([_flip(gk[:, k], k) for k in range(K)], 1).contiguous()
+        empty = torch.empty(0, dtype=torch.float32, device=u.device)
+        du_s, dd_s, dA, dB_s, dC_s, dD, dbias, _ = ops.bwd(u, delta, A, B, C, D, delta_bias, g, empty, saved,
+                                                           ctx.delta_softplus, None, empty)
+        du = sum(_flip(du_s[:, k * d:(k + 1) * d].float(), k) for k in range(K)).to(u.dtype)
+        return du, _to_scan(dd_s, K, d), dA, _to_scan5(dB_s), _to_scan5(dC_s), dw, dD, dbias, None
 
 
 def cross_scan_2d(u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplus=True):

@@ -40,7 +40,7 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
-def _problem(u, delta, A, B, C, D, delta_bias, A_decay, delta_softplus, out_dtype, who):
+def _problem(u, delta, A, B, C, D, delta_bias, A_decay, delta_softplus, out_dtype, who, shared_u_dim=None):
     input_type = u.dtype
     _check(input_type in _DT, f"{who} not implemented for input type '{input_type}'")
     _check(A.dtype == torch.float32, "A must be float32")
@@ -51,6 +51,9 @@ def _problem(u, delta, A, B, C, D, delta_bias, A_decay, delta_softplus, out_dtyp
     _check(u.dim() == 4, "u must have shape (batch_size, dim, nrows, ncols)")
     _check(_inner_ok(u) and _inner_ok(delta), "u and delta must be contiguous in the last dimension")
     batch, dim, nrows, ncols = u.shape
+    if shared_u_dim is not None:  # u holds the channels of ONE group, read by all groups (cs2d_dirs)
+        _check(B.dim() == 5 and dim * B.size(1) == shared_u_dim, "u must have dim / n_groups channels")
+        dim = shared_u_dim
     _check(A.dim() == 2 and B.dim() == 5 and delta.dim() == 4, "A, B, delta have the wrong rank")
     dstate, n_groups, delta_dim = A.size(1), B.size(1), delta.size(1)
     _check(dim % n_groups == 0, "dims should be dividable by n_groups")

@@ -60,11 +60,9 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, Geometry *g)
         CG >>= 1;
     const int CP = CG * (32 / L);
     const int pmax = (dpg + CP - 1) / CP;  // passes that cover a whole group
-    // Channels per CTA: as many as possible (B/C staging and the dB/dC atomics are
-    // paid once per CTA) while the grid still fills the machine a few times over.
+    // Channels per CTA (1..8 passes): B/C staging and the dB/dC atomics are paid once per CTA,
+    // but the grid has to fill whole waves (5.2 waves waste 14% of the machine in the last one).
     const int slots = kSMs * (backward ? 1 : 2);
-    // Among 1..8 passes pick the one whose grid fills whole waves best (a grid of
-    // 5.2 waves wastes 14% of the machine in its last wave); ties go to more passes.
     // Cost model: a CTA pays the B/C staging of a row block once (about one pass worth of
     // work when a warp holds a single channel, 1/CW of it otherwise) plus np passes, and the
     // launch takes waves(np) rounds of CTAs.
@@ -159,6 +157,7 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     d.adj = nullptr;
     d.status = nullptr;
     d.tile_left = d.tile_right = 0; d.Wout = p->ncols;
+    d.flip_h = d.flip_w = 0; d.u_shared = 0;
     d.edge_in = nullptr; d.edge_out = nullptr; d.adj_in = nullptr; d.adj_out = nullptr;
     d.du = d.ddelta = nullptr; d.dA = d.dB = d.dC = d.dD = d.dbias = d.ddecay = nullptr;
 }
@@ -228,10 +227,21 @@ size_t cs2d_saved_bytes(const cs2d_problem *p) { return layout_bytes(p, false); 
 
 size_t cs2d_bwd_scratch_bytes(const cs2d_problem *p) { return layout_bytes(p, true); }
 
-int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, int64_t out_hs, void *saved,
-             void *stream) {
+static int check_dirs(const cs2d_problem *p, const cs2d_dirs *o) {
+    if (!o || (!o->flip_rows_mask && !o->flip_cols_mask && !o->shared_input)) return CS2D_OK;
+    if (p->n_groups > 32) return fail(CS2D_ERR_INVALID, "direction masks cover at most 32 groups");
+    if (n_tiles(p->ncols) > 1)
+        return fail(CS2D_ERR_UNSUPPORTED, "scan directions are not combined with column tiles (ncols > %d) yet",
+                    kTileCols);
+    return CS2D_OK;
+}
+
+static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_t out_bs, int64_t out_ds,
+                    int64_t out_hs, void *saved, void *stream) {
     int rc = validate(p);
     if (rc) return rc;
+    if ((rc = check_dirs(p, o))) return rc;
+    const bool dirs = o && (o->flip_rows_mask || o->flip_cols_mask || o->shared_input);
     if (!out || !saved) return fail(CS2D_ERR_INVALID, "out and saved must be given");
     if (reinterpret_cast<uintptr_t>(saved) & 15) return fail(CS2D_ERR_INVALID, "saved must be 16-byte aligned");
     int *status = status_ptr();
@@ -247,7 +257,7 @@ int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, i
     size_t ck_off = 0;
     for (int t = 0; t < nt; ++t) {
         TileView tv;
-        const bool bulk = nt == 1 && bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
+        const bool bulk = nt == 1 && !dirs && bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
                           bulk_ok1(p->delta, es, p->ncols, p->delta_bs, p->delta_ds, p->delta_hs);
         if ((rc = tile_view(p, t, false, bulk, &tv))) return rc;
         Dev d;
@@ -262,6 +272,7 @@ int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, i
         char *edges = reinterpret_cast<char *>(saved) + ck_total;
         d.edge_in = t > 0 ? reinterpret_cast<const float4 *>(edges + (size_t)(t - 1) * eb) : nullptr;
         d.edge_out = t + 1 < nt ? reinterpret_cast<float4 *>(edges + (size_t)t * eb) : nullptr;
+        if (dirs) { d.flip_h = o->flip_rows_mask; d.flip_w = o->flip_cols_mask; d.u_shared = o->shared_input; }
         cudaError_t e = launch_fwd(d, tv.g.L, tv.g.grid, reinterpret_cast<cudaStream_t>(stream));
         if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
         g_launches.fetch_add(1);
@@ -269,11 +280,23 @@ int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, i
     return CS2D_OK;
 }
 
-int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t dout_ds, int64_t dout_hs,
-             const void *saved, void *scratch, void *du, void *ddelta, float *dA, float *dB, float *dC,
-             float *dD, float *ddelta_bias, float *dA_decay, void *stream) {
+int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, int64_t out_hs, void *saved,
+             void *stream) {
+    return fwd_impl(p, nullptr, out, out_bs, out_ds, out_hs, saved, stream);
+}
+
+int cs2d_fwd_dir(const cs2d_problem *p, const cs2d_dirs *dirs, void *out, int64_t out_bs, int64_t out_ds,
+                 int64_t out_hs, void *saved, void *stream) {
+    return fwd_impl(p, dirs, out, out_bs, out_ds, out_hs, saved, stream);
+}
+
+static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout, int64_t dout_bs, int64_t dout_ds,
+                    int64_t dout_hs, const void *saved, void *scratch, void *du, void *ddelta, float *dA, float *dB,
+                    float *dC, float *dD, float *ddelta_bias, float *dA_decay, void *stream) {
     int rc = validate(p);
     if (rc) return rc;
+    if ((rc = check_dirs(p, o))) return rc;
+    const bool dirs = o && (o->flip_rows_mask || o->flip_cols_mask || o->shared_input);
     if (!dout || !saved || !scratch || !du || !ddelta || !dA || !dB || !dC)
         return fail(CS2D_ERR_INVALID, "dout, saved, scratch, du, ddelta, dA, dB, dC must be given");
     if ((reinterpret_cast<uintptr_t>(saved) | reinterpret_cast<uintptr_t>(scratch)) & 15)
@@ -294,7 +317,7 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
     }
     for (int t = nt - 1; t >= 0; --t) {
         TileView tv;
-        const bool bulk = nt == 1 && bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
+        const bool bulk = nt == 1 && !dirs && bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
                           bulk_ok1(p->delta, es, p->ncols, p->delta_bs, p->delta_ds, p->delta_hs) &&
                           bulk_ok1(dout, eso, p->ncols, dout_bs, dout_ds, dout_hs);
         if ((rc = tile_view(p, t, true, bulk, &tv))) return rc;
@@ -317,11 +340,26 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
         d.edge_in = t > 0 ? reinterpret_cast<const float4 *>(edges + (size_t)(t - 1) * eb) : nullptr;
         d.adj_in = t + 1 < nt ? reinterpret_cast<const float4 *>(aedges + (size_t)t * eb) : nullptr;
         d.adj_out = t > 0 ? reinterpret_cast<float4 *>(aedges + (size_t)(t - 1) * eb) : nullptr;
+        if (dirs) { d.flip_h = o->flip_rows_mask; d.flip_w = o->flip_cols_mask; d.u_shared = o->shared_input; }
         cudaError_t e = launch_bwd(d, tv.g.L, tv.g.grid, reinterpret_cast<cudaStream_t>(stream));
         if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
         g_launches.fetch_add(1);
     }
     return CS2D_OK;
+}
+
+int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t dout_ds, int64_t dout_hs,
+             const void *saved, void *scratch, void *du, void *ddelta, float *dA, float *dB, float *dC,
+             float *dD, float *ddelta_bias, float *dA_decay, void *stream) {
+    return bwd_impl(p, nullptr, dout, dout_bs, dout_ds, dout_hs, saved, scratch, du, ddelta, dA, dB, dC, dD,
+                    ddelta_bias, dA_decay, stream);
+}
+
+int cs2d_bwd_dir(const cs2d_problem *p, const cs2d_dirs *dirs, const void *dout, int64_t dout_bs, int64_t dout_ds,
+                 int64_t dout_hs, const void *saved, void *scratch, void *du, void *ddelta, float *dA, float *dB,
+                 float *dC, float *dD, float *ddelta_bias, float *dA_decay, void *stream) {
+    return bwd_impl(p, dirs, dout, dout_bs, dout_ds, dout_hs, saved, scratch, du, ddelta, dA, dB, dC, dD,
+                    ddelta_bias, dA_decay, stream);
 }
 
 /*

@@ -111,6 +111,9 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
     float *sedl_l = reinterpret_cast<float *>(sadj + CP * NPp * (RB + 1));   // [CP][RB]
     float *sedl_r = sedl_l + CP * 4;                                          // [CP][RB+1] (pitch 8)
     const bool has_left = TILED && P.tile_left != 0, has_right = TILED && P.tile_right != 0;
+    const bool fh = (P.flip_h >> g_) & 1u, fw = (P.flip_w >> g_) & 1u;  // scan direction of this group
+    const int ush = (P.u_shared & 1) ? g_ * P.dpg : 0;                    // u indexed by channel - ush
+    const int gsh = (P.u_shared & 2) ? g_ * P.dpg : 0;                    // dout indexed by channel - gsh
     uint64_t *bars = reinterpret_cast<uint64_t *>(sedl_r + CP * 8);
     unsigned char *raw = reinterpret_cast<unsigned char *>(bars + 2);
     const int stage_bytes = CP * W * (RB * es + RB * eso + (RB + 2) * es);
@@ -203,9 +206,9 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         a1.x = fmaf(Dv, gv.x, a1.x); a1.y = fmaf(Dv, gv.y, a1.y);
                         a1.z = fmaf(Dv, gv.z, a1.z); a1.w = fmaf(Dv, gv.w, a1.w);
                         a2.x *= sv.x; a2.y *= sv.y; a2.z *= sv.z; a2.w *= sv.w;
-                        const int64_t o = (((int64_t)b * P.dim + sd) * H + (pr0 + rr)) * P.Wout + c;
-                        st4(P.du, o, P.io_dt, P.vec & VEC_DU, W - c, a1);
-                        st4(P.ddelta, o, P.io_dt, P.vec & VEC_DU, W - c, a2);
+                        const int64_t o = ((int64_t)b * P.dim + sd) * H * P.Wout;
+                        st4d(P.du, o, P.Wout, pr0 + rr, c, H, W, fh, fw, P.io_dt, P.vec & VEC_DU, a1);
+                        st4d(P.ddelta, o, P.Wout, pr0 + rr, c, H, W, fh, fw, P.io_dt, P.vec & VEC_DU, a2);
                         // columns past the image carry g = 0 and ddl = 0
                         dDp = gv.x * uv.x + gv.y * uv.y + gv.z * uv.z + gv.w * uv.w;
                         dbp = a2.x + a2.y + a2.z + a2.w;
@@ -232,12 +235,12 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         gv = lds4(raw_g, (sc * RB + rr) * W + c, P.out_dt);
                         xv = lds4(raw_dl, (sc * (RB + 2) + (r - lo)) * W + c, P.io_dt);
                     } else {
-                        uv = ld4(P.u, (int64_t)b * P.u_bs + (int64_t)sd * P.u_ds + (int64_t)r * P.u_hs + c, P.io_dt,
-                                 P.vec & VEC_U, W - c);
-                        gv = ld4(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + (int64_t)r * P.o_hs + c,
-                                 P.out_dt, P.vec & VEC_OUT, W - c);
-                        xv = ld4(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)r * P.dl_hs + c,
-                                 P.io_dt, P.vec & VEC_DELTA, W - c);
+                        uv = ld4d(P.u, (int64_t)b * P.u_bs + (int64_t)(sd - ush) * P.u_ds, P.u_hs, r, c, H, W, fh, fw,
+                                  P.io_dt, P.vec & VEC_U);
+                        gv = ld4d(P.out, (int64_t)b * P.o_bs + (int64_t)(sd - gsh) * P.o_ds, P.o_hs, r, c, H, W, fh, fw,
+                                  P.out_dt, P.vec & VEC_OUT);
+                        xv = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, r, c, H, W, fh, fw,
+                                  P.io_dt, P.vec & VEC_DELTA);
                     }
                     soft4(xv, sv, P.bias ? __ldg(P.bias + sdd) : 0.f, P.softplus, W - c);
                 }
@@ -257,8 +260,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         if (bulk)
                             x = lds4(raw_dl, (sc * (RB + 2) + (r - lo)) * W + c, P.io_dt);
                         else
-                            x = ld4(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)r * P.dl_hs + c,
-                                    P.io_dt, P.vec & VEC_DELTA, W - c);
+                            x = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, r, c, H, W, fh, fw,
+                                     P.io_dt, P.vec & VEC_DELTA);
                         soft4(x, unused, P.bias ? __ldg(P.bias + sdd) : 0.f, P.softplus, W - c);
                     }
                     *reinterpret_cast<float4 *>(sdl + sc * CS6 + rr * Wp + pos4<L>(t)) = x;
@@ -275,7 +278,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                     saB[o] = bc(0.f); saC[o] = bc(0.f);
                     (void)scg;
                     if (c < W && rr < pnr && 2 * spp < N) {
-                        const int64_t og = ((((int64_t)b * P.G + g_) * N + 2 * spp) * H + (pr0 + rr)) * P.Wout + c;
+                        const int64_t og = ((((int64_t)b * P.G + g_) * N + 2 * spp) * H + (fh ? H - 1 - (pr0 + rr) : pr0 + rr)) * P.Wout +
+                                           (fw ? W - 1 - c : c);
                         atomicAdd(P.dB + og, vb.x);
                         atomicAdd(P.dC + og, vc.x);
                         if (2 * spp + 1 < N) {
@@ -285,7 +289,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                     }
                 }
             }
-            if (nr > 0 && pass == 0) stage_BC<L>(P, b, g_, r0, nr, sB, sC);
+            if (nr > 0 && pass == 0) stage_BC<L>(P, b, g_, r0, nr, sB, sC, fh, fw);
             if (nr > 0 && (has_left || has_right)) {
                 for (int it = tid; it < CP * NPp * (RB + 1); it += nthr) {
                     const int k = it % (RB + 1), q = (it / (RB + 1)) % NPp, sc = it / ((RB + 1) * NPp);
@@ -545,7 +549,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                                 *qb = add2(*qb, dBv);
                                 *qc = add2(*qc, dCv);
                             } else if (ch_ok && j * STRIP + i < W) {
-                                const int64_t og = ((((int64_t)b * P.G + g_) * N + n0) * H + (r0 + rr)) * P.Wout + j * STRIP + i;
+                                const int64_t og = ((((int64_t)b * P.G + g_) * N + n0) * H + (fh ? H - 1 - (r0 + rr) : r0 + rr)) * P.Wout +
+                                                   (fw ? W - 1 - (j * STRIP + i) : j * STRIP + i);
                                 atomicAdd(P.dB + og, dBv.x);
                                 atomicAdd(P.dC + og, dCv.x);
                                 if (n1 < N) {
@@ -582,7 +587,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                                     *qc = add2(*qc, sc2);
                                 } else if (j * STRIP + col < W) {
                                     const int64_t og =
-                                        ((((int64_t)b * P.G + g_) * N + n0) * H + (r0 + rr)) * P.Wout + j * STRIP + col;
+                                        ((((int64_t)b * P.G + g_) * N + n0) * H + (fh ? H - 1 - (r0 + rr) : r0 + rr)) * P.Wout +
+                                        (fw ? W - 1 - (j * STRIP + col) : j * STRIP + col);
                                     atomicAdd(P.dB + og, sb.x);
                                     atomicAdd(P.dC + og, sc2.x);
                                     if (n1 < N) {

@@ -53,6 +53,12 @@ struct Dev {
     int nck;    // row blocks per image: ceil(H/RB)
     int acc_dbc; // backward: 1 = dB/dC accumulated over the CTA's passes in shared memory,
                  //           0 = added to global memory row by row (wide rows: tiles do not fit)
+    // Scan directions: bit g of flip_h / flip_w set = group g walks the image rows bottom-up /
+    // the columns right-to-left.  Tensors stay in image coordinates; the flips are index maps
+    // applied when tiles are staged and results written.  u_shared: u and dout have dim/G
+    // channels shared by all groups (the four corner directions read the same image).
+    unsigned flip_h, flip_w;
+    int u_shared;
     int vec;    // bit i set: tensor i may be accessed 4 elements at a time
     int bulk;   // 1: row blocks of u, delta (and dout) are fetched with bulk asynchronous copies
                 //    (rows are 16-byte multiples, planes contiguous and aligned); 0: plain loads
@@ -217,6 +223,34 @@ __device__ __forceinline__ float4 lds4(const unsigned char *raw, int idx, int dt
     const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&v.x));
     const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
     return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// Direction-aware access to 4 consecutive SCAN columns c..c+3 of scan row r of an image plane
+// (element offset `plane`, row pitch `hs`): rows are mirrored when fh, columns when fw.
+__device__ __forceinline__ float4 ld4d(const void *p, int64_t plane, int64_t hs, int r, int c, int H, int W, bool fh,
+                                       bool fw, int dt, bool vec) {
+    const int64_t row = plane + (int64_t)(fh ? H - 1 - r : r) * hs;
+    if (!fw) return ld4(p, row + c, dt, vec, W - c);
+    const int nv = W - c;
+    if (nv >= 4) {
+        const float4 v = ld4(p, row + (W - 4 - c), dt, vec, 4);
+        return make_float4(v.w, v.z, v.y, v.x);
+    }
+    float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (nv > 0) q.x = ld_elem(p, row + W - 1 - c, dt);
+    if (nv > 1) q.y = ld_elem(p, row + W - 2 - c, dt);
+    if (nv > 2) q.z = ld_elem(p, row + W - 3 - c, dt);
+    return q;
+}
+__device__ __forceinline__ void st4d(void *p, int64_t plane, int64_t hs, int r, int c, int H, int W, bool fh, bool fw,
+                                     int dt, bool vec, float4 v) {
+    const int64_t row = plane + (int64_t)(fh ? H - 1 - r : r) * hs;
+    if (!fw) { st4(p, row + c, dt, vec, W - c, v); return; }
+    const int nv = W - c;
+    if (nv >= 4) { st4(p, row + (W - 4 - c), dt, vec, 4, make_float4(v.w, v.z, v.y, v.x)); return; }
+    if (nv > 0) st_elem(p, row + W - 1 - c, dt, v.x);
+    if (nv > 1) st_elem(p, row + W - 2 - c, dt, v.y);
+    if (nv > 2) st_elem(p, row + W - 3 - c, dt, v.z);
 }
 
 // softplus with the reference's threshold (fwd kernel :221-224).
@@ -450,7 +484,8 @@ __device__ __forceinline__ void row_forward(int j, const float (&dl)[STRIP], con
 // ---- staging shared by both kernels ---------------------------------------------
 // B and C of one row block for every state pair: sB/sC[NPp][RB][Wp] float2.
 template <int L>
-__device__ __forceinline__ void stage_BC(const Dev &P, int b, int g, int r0, int nr, float2 *sB, float2 *sC) {
+__device__ __forceinline__ void stage_BC(const Dev &P, int b, int g, int r0, int nr, float2 *sB, float2 *sC,
+                                         bool fh, bool fw) {
     constexpr int Wp = L * STRIP, T4 = Wp / 4;
     const int items = P.NPp * RB * T4;
     const int nthr = blockDim.x;
@@ -459,14 +494,13 @@ __device__ __forceinline__ void stage_BC(const Dev &P, int b, int g, int r0, int
         const int c = 4 * t, n0 = 2 * sp;
         float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0, c0 = b0, c1 = b0;
         if (rr < nr && n0 < P.N) {
-            const int r = r0 + rr, nv = P.W - c;
-            const int64_t ob = (int64_t)b * P.B_bs + (int64_t)g * P.B_gs + (int64_t)r * P.B_hs + c;
-            const int64_t oc = (int64_t)b * P.C_bs + (int64_t)g * P.C_gs + (int64_t)r * P.C_hs + c;
-            b0 = ld4(P.B, ob + (int64_t)n0 * P.B_ns, P.io_dt, P.vec & VEC_B, nv);
-            c0 = ld4(P.C, oc + (int64_t)n0 * P.C_ns, P.io_dt, P.vec & VEC_C, nv);
+            const int r = r0 + rr;
+            const int64_t ob = (int64_t)b * P.B_bs + (int64_t)g * P.B_gs, oc = (int64_t)b * P.C_bs + (int64_t)g * P.C_gs;
+            b0 = ld4d(P.B, ob + (int64_t)n0 * P.B_ns, P.B_hs, r, c, P.H, P.W, fh, fw, P.io_dt, P.vec & VEC_B);
+            c0 = ld4d(P.C, oc + (int64_t)n0 * P.C_ns, P.C_hs, r, c, P.H, P.W, fh, fw, P.io_dt, P.vec & VEC_C);
             if (n0 + 1 < P.N) {
-                b1 = ld4(P.B, ob + (int64_t)(n0 + 1) * P.B_ns, P.io_dt, P.vec & VEC_B, nv);
-                c1 = ld4(P.C, oc + (int64_t)(n0 + 1) * P.C_ns, P.io_dt, P.vec & VEC_C, nv);
+                b1 = ld4d(P.B, ob + (int64_t)(n0 + 1) * P.B_ns, P.B_hs, r, c, P.H, P.W, fh, fw, P.io_dt, P.vec & VEC_B);
+                c1 = ld4d(P.C, oc + (int64_t)(n0 + 1) * P.C_ns, P.C_hs, r, c, P.H, P.W, fh, fw, P.io_dt, P.vec & VEC_C);
             }
         }
         const int base = (sp * RB + rr) * Wp + pos2<L>(c);  // columns c, c+1; c+2, c+3 follow 2L float2 later

@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
     const int cp = cg * CW + cl;  // channel slot inside a pass
     const int tile = blockIdx.x % P.ntiles, bg = blockIdx.x / P.ntiles;
     const int g = bg % P.G, b = bg / P.G;
+    const bool fh = (P.flip_h >> g) & 1u, fw = (P.flip_w >> g) & 1u;  // scan direction of this group
+    const int ush = (P.u_shared & 1) ? g * P.dpg : 0;                        // u is indexed by channel - ush
     const int dbase = g * P.dpg + tile * P.CT;
     const int nch = min(P.CT, (g + 1) * P.dpg - dbase);  // valid channels of this CTA
     const int H = P.H, W = P.W, N = P.N;
@@ -159,16 +161,16 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                         acc.x = fmaf(Dv, uv.x, acc.x); acc.y = fmaf(Dv, uv.y, acc.y);
                         acc.z = fmaf(Dv, uv.z, acc.z); acc.w = fmaf(Dv, uv.w, acc.w);
                     }
-                    st4(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + (int64_t)(pr0 + rr) * P.o_hs + c,
-                        P.out_dt, P.vec & VEC_OUT, W - c, acc);
+                    st4d(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds, P.o_hs, pr0 + rr, c, H, W, fh, fw, P.out_dt,
+                         P.vec & VEC_OUT, acc);
                 }
                 float4 uv = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (rr < nr && ch0 + sc < nch) {
                     if (bulk) {
                         if (c < W) uv = lds4(raw_u, (sc * RB + rr) * W + c, P.io_dt);
                     } else {
-                        uv = ld4(P.u, (int64_t)b * P.u_bs + (int64_t)(dbase + ch0 + sc) * P.u_ds +
-                                          (int64_t)(r0 + rr) * P.u_hs + c, P.io_dt, P.vec & VEC_U, W - c);
+                        uv = ld4d(P.u, (int64_t)b * P.u_bs + (int64_t)(dbase + ch0 + sc - ush) * P.u_ds, P.u_hs, r0 + rr, c,
+                                  H, W, fh, fw, P.io_dt, P.vec & VEC_U);
                     }
                 }
                 *reinterpret_cast<float4 *>(su + o4) = uv;
@@ -184,8 +186,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                         if (bulk)
                             x = lds4(raw_dl, (sc * (RB + 1) + (r - lo)) * W + c, P.io_dt);
                         else
-                            x = ld4(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)r * P.dl_hs + c,
-                                    P.io_dt, P.vec & VEC_DELTA, W - c);
+                            x = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, r, c, H, W, fh, fw,
+                                     P.io_dt, P.vec & VEC_DELTA);
                         const float bv = P.bias ? __ldg(P.bias + sdd) : 0.f;
                         x.x += bv; x.y += bv; x.z += bv; x.w += bv;
                         if (P.softplus) {
@@ -196,7 +198,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                     }
                     *reinterpret_cast<float4 *>(sdl + sc * CS5 + rr * Wp + pos4<L>(t)) = x;
                 }
-                if (pass == 0) stage_BC<L>(P, b, g, r0, nr, sB, sC);
+                if (pass == 0) stage_BC<L>(P, b, g, r0, nr, sB, sC, fh, fw);
                 if (has_left) {  // column left of this tile: h, s written by the tile to the left; delta
                     for (int it = tid; it < CP * NPp * (RB + 1); it += nthr) {
                         const int k = it % (RB + 1), q = (it / (RB + 1)) % NPp, sc = it / ((RB + 1) * NPp);
