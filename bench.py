@@ -144,11 +144,12 @@ def run_reference(args, shape, name):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default=DEFAULT_CONFIG)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-chunks", type=int, default=4, help="batch chunks of the host-buffer pipeline")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling captures only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -258,27 +259,23 @@ def main():
     del du, dd, dB, dC, scratch
 
     # ---- end to end: host buffers in, host buffers out, copies inside the timed region ----
+    # cs2d.fwd_bwd_from_host is the call a user with host-resident tensors makes: it pipelines
+    # batch chunks over copy-in / kernel / copy-out streams.
     big = ("u", "delta", "B", "C", "dout")
     h2d = sum(host[k].numel() * host[k].element_size() for k in big)
-    o, g = step(d)
-    outs = [o, g[0], g[1], g[3], g[4], g[2], g[5], g[6]]
-    hout = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outs]
-    d2h = sum(t.numel() * t.element_size() for t in outs)
-    del o, g, outs
+    hout = cs2d.alloc_host_outputs(host["u"], host["B"], d["A"], True, True)
+    d2h = sum(t.numel() * t.element_size() for t in hout.values())
+    params = {"A": d["A"], "D": d["D"], "delta_bias": d["delta_bias"]}
 
     def e2e_step():
-        t = dict(d)
-        for k in big:
-            t[k] = host[k].to(dev, non_blocking=True)
-        o, g = step(t)
-        for hb, src in zip(hout, [o, g[0], g[1], g[3], g[4], g[2], g[5], g[6]]):
-            hb.copy_(src, non_blocking=True)
+        cs2d.fwd_bwd_from_host(host, params, hout, True, False, chunks=args.e2e_chunks, allreduce=world > 1)
 
     e2e_step()
+    torch.cuda.synchronize()
     e2e_steps = max(2, min(args.steps, 5))
     e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
     e2e = {"value": el_step / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "ms_per_step": e2e_ms}
+           "ms_per_step": e2e_ms, "chunks": args.e2e_chunks}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
