@@ -153,6 +153,10 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling captures only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference" or int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        # the CPU arm uses every host core; torchrun exports OMP_NUM_THREADS=1, which must be undone
+        # before any OpenMP runtime is loaded
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
 
     from cs2d.synthetic import CONFIGS, algorithmic_bytes, elements, make_inputs
     B, K, D, N, H, W, dtype = CONFIGS[args.config]
