@@ -36,3 +36,17 @@ def test_cross_scan_forward_and_gradients(shape, dtype):
         s = 10.0 if k in ("A", "D", "delta_bias", "w") else 1.0
         check_close("d" + k, dev[k].grad.float().cpu().numpy(), ref[k].grad.numpy(), rtol * s, atol * s)
     assert cs2d.device_status() == 0
+
+
+def test_module_trains_all_parameters():
+    from cs2d.nn import CrossScan2D
+    torch.manual_seed(1)
+    m = CrossScan2D(d_inner=4, d_state=4).cuda()
+    u = torch.randn(2, 4, 6, 10, device="cuda")
+    delta = torch.randn(2, 16, 6, 10, device="cuda")
+    Bm, Cm = torch.randn(2, 4, 4, 6, 10, device="cuda"), torch.randn(2, 4, 4, 6, 10, device="cuda")
+    y = m(u, delta, Bm, Cm)
+    assert y.shape == u.shape
+    y.square().mean().backward()
+    for name, p in m.named_parameters():
+        assert p.grad is not None and torch.isfinite(p.grad).all() and p.grad.abs().sum() > 0, name
