@@ -206,3 +206,37 @@ def test_full_size_sample_against_oracle(full):
         go = O.bwd(u, dl, A, Bm, Cm, Dv, bias, do, True)
         check_close("du", _np(g[0][b:b + 1, ch]), go["du"], 1e-4, 1e-5)
         check_close("ddelta", _np(g[1][b:b + 1, ch]), go["ddelta"], 1e-4, 1e-5)
+
+
+# ---- every benchmark configuration at its own feature-map shape (batch reduced to 1) --------------
+from cs2d.synthetic import CONFIGS  # noqa: E402
+
+
+@pytest.mark.parametrize("name", [n for n in CONFIGS if not n.startswith(("c1", "c2"))])
+def test_benchmark_config_shapes_against_oracle(name):
+    _, K, D, N, H, W, dtype = CONFIGS[name]
+    inp = make_inputs(1, K, D, N, H, W, dtype=dtype, seed=3)
+    d = _dev(inp)
+    out, g, _ = _run(d)
+    rtol, atol = TOL[str(dtype).replace("torch.", "")]
+    f = lambda t: t.float().cpu()
+    # three channels of the first and of the last direction through the float64 oracle; B/C
+    # gradients are sums over all D channels of a group, so they are checked on a group that is
+    # fed only those channels (a second, smaller call)
+    for k in (0, K - 1):
+        ch = slice(k * D, k * D + 3)
+        u, dl, do = f(d["u"][:, ch]), f(d["delta"][:, ch]), f(d["dout"][:, ch])
+        Bm, Cm = f(d["B"][:, k:k + 1]), f(d["C"][:, k:k + 1])
+        A, Dv, bias = f(d["A"][ch]), f(d["D"][ch]), f(d["delta_bias"][ch])
+        yo = O.fwd(u, dl, A, Bm, Cm, Dv, bias, True)
+        go = O.bwd(u, dl, A, Bm, Cm, Dv, bias, do, True)
+        check_close("out", _np(out[:, ch]), yo, rtol, atol)
+        check_close("du", _np(g[0][:, ch]), go["du"], rtol, atol)
+        check_close("ddelta", _np(g[1][:, ch]), go["ddelta"], rtol, atol)
+        check_close("dA", _np(g[2][ch]), go["dA"], rtol * 10, atol * 10)
+        sub = {kk: (v[:, ch].contiguous() if kk in ("u", "delta", "dout") else v) for kk, v in d.items()}
+        sub.update(A=d["A"][ch].contiguous(), D=d["D"][ch].contiguous(), delta_bias=d["delta_bias"][ch].contiguous(),
+                   B=d["B"][:, k:k + 1].contiguous(), C=d["C"][:, k:k + 1].contiguous())
+        _, g3, _ = _run(sub)
+        check_close("dB", _np(g3[3]), go["dB"], rtol, atol)
+        check_close("dC", _np(g3[4]), go["dC"], rtol, atol)
