@@ -141,6 +141,19 @@ int cs2d_bwd_dir(const cs2d_problem *p, const cs2d_dirs *dirs, const void *dout,
                  void *stream);
 
 /*
+ * Forward that no backward will follow (inference, evaluation).  Same results as
+ * cs2d_fwd / cs2d_fwd_dir (dirs may be NULL), but instead of the saved-state
+ * buffer it takes a scratch buffer of cs2d_fwd_only_scratch_bytes(p) bytes
+ * (16-byte aligned, contents undefined before and after): one rolling row of h
+ * per channel and state pair instead of one per four image rows.  The reference
+ * always writes its three side tensors (selective_scan_oflex.cpp:251-258,
+ * selective_scan_fwd_kernel_oflex.cuh:289-295); it has no such mode.
+ */
+size_t cs2d_fwd_only_scratch_bytes(const cs2d_problem *p);
+int cs2d_fwd_only(const cs2d_problem *p, const cs2d_dirs *dirs, void *out, int64_t out_bs, int64_t out_ds,
+                  int64_t out_hs, void *scratch, void *stream);
+
+/*
  * Backward without any allocation on the caller's side: identical to cs2d_bwd
  * except that the scratch buffer is a fixed device array inside the library
  * (CS2D_NOALLOC_SCRATCH_BYTES per GPU, held from library load to process exit).

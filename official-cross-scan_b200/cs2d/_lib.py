@@ -58,6 +58,8 @@ def lib():
         L.cs2d_saved_bytes.argtypes = [ctypes.POINTER(Problem)]
         L.cs2d_bwd_scratch_bytes.restype = ctypes.c_size_t
         L.cs2d_bwd_scratch_bytes.argtypes = [ctypes.POINTER(Problem)]
+        L.cs2d_fwd_only_scratch_bytes.restype = ctypes.c_size_t
+        L.cs2d_fwd_only_scratch_bytes.argtypes = [ctypes.POINTER(Problem)]
         L.cs2d_fwd.restype = ctypes.c_int
         L.cs2d_fwd.argtypes = [ctypes.POINTER(Problem), vp, i64, i64, i64, vp, vp]
         L.cs2d_bwd.restype = ctypes.c_int
@@ -65,6 +67,8 @@ def lib():
         dp = ctypes.POINTER(Dirs)
         L.cs2d_fwd_dir.restype = ctypes.c_int
         L.cs2d_fwd_dir.argtypes = [ctypes.POINTER(Problem), dp, vp, i64, i64, i64, vp, vp]
+        L.cs2d_fwd_only.restype = ctypes.c_int
+        L.cs2d_fwd_only.argtypes = [ctypes.POINTER(Problem), dp, vp, i64, i64, i64, vp, vp]
         L.cs2d_bwd_dir.restype = ctypes.c_int
         L.cs2d_bwd_dir.argtypes = [ctypes.POINTER(Problem), dp, vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                                    vp]

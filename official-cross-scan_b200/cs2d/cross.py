@@ -59,24 +59,26 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
-def _dir_forward(u, delta, A, B, C, D, delta_bias, delta_softplus):
-    """One launch for all directions; returns per-direction outputs (b, K*d, h, w) fp32 and the saved state."""
+def _dir_forward(u, delta, A, B, C, D, delta_bias, delta_softplus, keep_state=True):
+    """One launch for all directions; returns per-direction outputs (b, K*d, h, w) fp32 and the saved state
+    (``None`` when ``keep_state`` is false: the forward then only holds one rolling row of state)."""
     L = _lib.lib()
     K, dim = B.size(1), A.size(0)
     p = ops._problem(u, delta, A, B, C, D, delta_bias, None, delta_softplus, torch.float32, "cross_scan_fwd",
                      shared_u_dim=dim)
     rows, cols = _masks(K)
     dirs = _lib.Dirs(rows, cols, 1)
-    nbytes = L.cs2d_saved_bytes(ctypes.byref(p))
+    nbytes = (L.cs2d_saved_bytes if keep_state else L.cs2d_fwd_only_scratch_bytes)(ctypes.byref(p))
     if nbytes == 0:
         raise RuntimeError(f"cs2d forward: {_lib.last_error()}")
     with torch.cuda.device(u.device):
         out = torch.empty(u.size(0), dim, u.size(2), u.size(3), dtype=torch.float32, device=u.device)
         saved = torch.empty(nbytes // 4, dtype=torch.float32, device=u.device)
-        rc = L.cs2d_fwd_dir(ctypes.byref(p), ctypes.byref(dirs), _ptr(out), out.stride(0), out.stride(1),
-                            out.stride(2), _ptr(saved), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        rc = (L.cs2d_fwd_dir if keep_state else L.cs2d_fwd_only)(
+            ctypes.byref(p), ctypes.byref(dirs), _ptr(out), out.stride(0), out.stride(1), out.stride(2), _ptr(saved),
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     ops._raise_on(rc, "forward")
-    return out, saved
+    return out, (saved if keep_state else None)
 
 
 def _dir_backward(u, delta, A, B, C, D, delta_bias, g, saved, delta_softplus):
@@ -153,4 +155,14 @@ class CrossScan2D(torch.autograd.Function):
 
 def cross_scan_2d(u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplus=True):
     """Differentiable four-corner CrossScan; see the module docstring for shapes."""
+    needs_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad
+                                                 for t in (u, delta, A, B, C, w, D, delta_bias))
+    if not needs_grad and u.size(-1) <= _MAX_DIRECT_COLS:  # evaluation: no saved state
+        b, d, h, wd = u.shape
+        K = B.size(1)
+        if delta.size(1) != K * d or A.size(0) != K * d or tuple(w.shape) != (K, d):
+            raise RuntimeError("expected delta (b, K*D, h, w), A (K*D, n), w (K, D)")
+        out, _ = _dir_forward(u.contiguous(), delta.contiguous(), A, B.contiguous(), C.contiguous(), D, delta_bias,
+                              delta_softplus, keep_state=False)
+        return (out.view(b, K, d, h, wd) * w.float()[None, :, :, None, None]).sum(1).to(u.dtype)
     return CrossScan2D.apply(u, delta, A, B, C, w, D, delta_bias, delta_softplus)

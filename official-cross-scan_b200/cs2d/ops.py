@@ -118,6 +118,29 @@ def fwd(u, delta, A, B, C, D_=None, delta_bias_=None, delta_softplus=False, out_
     return [out, x, x_v, x_sd]
 
 
+def fwd_only(u, delta, A, B, C, D_=None, delta_bias_=None, delta_softplus=False, out_float=False, A_decay_=None):
+    """Forward that no backward will follow: returns ``out`` alone.
+
+    Same kernels and results as ``fwd``; the state between row blocks lives in one
+    rolling row per channel and state pair instead of the checkpoint buffer (a
+    quarter of all h values), so evaluation needs a fraction of the memory.
+    """
+    L = _lib.lib()
+    out_dtype = torch.float32 if out_float else u.dtype
+    p = _problem(u, delta, A, B, C, D_, delta_bias_, A_decay_, delta_softplus, out_dtype, "selective_scan_fwd")
+    nbytes = L.cs2d_fwd_only_scratch_bytes(ctypes.byref(p))
+    if nbytes == 0:
+        raise RuntimeError(f"cs2d forward: {_lib.last_error()}")
+    with torch.cuda.device(u.device):
+        out = torch.empty(tuple(u.shape), dtype=out_dtype, device=u.device)
+        scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=u.device)
+        stream = torch.cuda.current_stream(u.device).cuda_stream
+        rc = L.cs2d_fwd_only(ctypes.byref(p), None, _ptr(out), out.stride(0), out.stride(1), out.stride(2),
+                             _ptr(scratch), ctypes.c_void_p(stream))
+    _raise_on(rc, "forward")
+    return out
+
+
 def param_grad_layout(dim, dstate, has_D, has_bias, has_decay):
     """Offsets of the per-channel parameter gradients inside one flat fp32 buffer.
 
@@ -220,5 +243,12 @@ class SelectiveScan2D(torch.autograd.Function):
 
 def selective_scan_2d(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=False, out_float=False,
                       A_decay=None):
-    """Differentiable 2D-CrossScan selective scan (one scan orientation; see ``fwd``)."""
+    """Differentiable 2D-CrossScan selective scan (one scan orientation; see ``fwd``).
+
+    When nothing can ask for a gradient (``torch.no_grad()`` or no input requires one) the
+    forward keeps no saved state (``fwd_only``).
+    """
+    if not (torch.is_grad_enabled() and any(t is not None and t.requires_grad
+                                            for t in (u, delta, A, B, C, D, delta_bias, A_decay))):
+        return fwd_only(u, delta, A, B, C, D, delta_bias, delta_softplus, out_float, A_decay)
     return SelectiveScan2D.apply(u, delta, A, B, C, D, delta_bias, delta_softplus, out_float, A_decay)

@@ -155,6 +155,7 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     if (vec_ok(p->B, es, p->ncols, {p->B_bs, p->B_gs, p->B_ns, p->B_hs})) d.vec |= VEC_B;
     if (vec_ok(p->C, es, p->ncols, {p->C_bs, p->C_gs, p->C_ns, p->C_hs})) d.vec |= VEC_C;
     d.adj = nullptr;
+    d.ck_roll = 0;
     d.status = nullptr;
     d.tile_left = d.tile_right = 0; d.Wout = p->ncols;
     d.flip_h = d.flip_w = 0; d.u_shared = 0;
@@ -209,7 +210,9 @@ static size_t edge_bytes(const cs2d_problem *p, int NPp) {
     return (size_t)p->batch * p->dim * NPp * p->nrows * sizeof(float4);
 }
 
-static size_t layout_bytes(const cs2d_problem *p, bool backward) {
+// backward: adjoint rows; otherwise the forward's state rows - all checkpoints, or (rolling) one
+// row per channel and state pair for a forward that no backward follows
+static size_t layout_bytes(const cs2d_problem *p, bool backward, bool rolling = false) {
     if (validate(p) != CS2D_OK) return 0;
     const int nt = n_tiles(p->ncols);
     size_t total = 0;
@@ -217,7 +220,7 @@ static size_t layout_bytes(const cs2d_problem *p, bool backward) {
     for (int t = 0; t < nt; ++t) {
         TileView tv;
         if (tile_view(p, t, backward, false, &tv) != CS2D_OK) return 0;
-        total += backward ? tv.adj_bytes : tv.saved_bytes;
+        total += backward || rolling ? tv.adj_bytes : tv.saved_bytes;
         NPp = tv.g.NPp;
     }
     return total + (size_t)(nt - 1) * edge_bytes(p, NPp);
@@ -226,6 +229,8 @@ static size_t layout_bytes(const cs2d_problem *p, bool backward) {
 size_t cs2d_saved_bytes(const cs2d_problem *p) { return layout_bytes(p, false); }
 
 size_t cs2d_bwd_scratch_bytes(const cs2d_problem *p) { return layout_bytes(p, true); }
+
+size_t cs2d_fwd_only_scratch_bytes(const cs2d_problem *p) { return layout_bytes(p, false, true); }
 
 static int check_dirs(const cs2d_problem *p, const cs2d_dirs *o) {
     if (!o || (!o->flip_rows_mask && !o->flip_cols_mask && !o->shared_input)) return CS2D_OK;
@@ -237,7 +242,7 @@ static int check_dirs(const cs2d_problem *p, const cs2d_dirs *o) {
 }
 
 static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_t out_bs, int64_t out_ds,
-                    int64_t out_hs, void *saved, void *stream) {
+                    int64_t out_hs, void *saved, void *stream, bool rolling = false) {
     int rc = validate(p);
     if (rc) return rc;
     if ((rc = check_dirs(p, o))) return rc;
@@ -252,7 +257,7 @@ static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_
     for (int t = 0; t < nt; ++t) {
         TileView tv;
         if ((rc = tile_view(p, t, false, false, &tv))) return rc;
-        ck_total += tv.saved_bytes;
+        ck_total += rolling ? tv.adj_bytes : tv.saved_bytes;
     }
     size_t ck_off = 0;
     for (int t = 0; t < nt; ++t) {
@@ -265,7 +270,8 @@ static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_
         d.out = const_cast<char *>(at(out, tv.c0, eso)); d.o_bs = out_bs; d.o_ds = out_ds; d.o_hs = out_hs;
         if (vec_ok(d.out, eso, tv.q.ncols, {out_bs, out_ds, out_hs})) d.vec |= VEC_OUT;
         d.saved = reinterpret_cast<float2 *>(reinterpret_cast<char *>(saved) + ck_off);
-        ck_off += tv.saved_bytes;
+        ck_off += rolling ? tv.adj_bytes : tv.saved_bytes;
+        d.ck_roll = rolling;
         d.status = status;
         d.tile_left = t > 0; d.tile_right = t + 1 < nt; d.Wout = p->ncols;
         const size_t eb = edge_bytes(p, tv.g.NPp);
@@ -283,6 +289,11 @@ static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_
 int cs2d_fwd(const cs2d_problem *p, void *out, int64_t out_bs, int64_t out_ds, int64_t out_hs, void *saved,
              void *stream) {
     return fwd_impl(p, nullptr, out, out_bs, out_ds, out_hs, saved, stream);
+}
+
+int cs2d_fwd_only(const cs2d_problem *p, const cs2d_dirs *dirs, void *out, int64_t out_bs, int64_t out_ds,
+                  int64_t out_hs, void *scratch, void *stream) {
+    return fwd_impl(p, dirs, out, out_bs, out_ds, out_hs, scratch, stream, true);
 }
 
 int cs2d_fwd_dir(const cs2d_problem *p, const cs2d_dirs *dirs, void *out, int64_t out_bs, int64_t out_ds,

@@ -69,6 +69,7 @@ struct Dev {
     int64_t B_bs, B_gs, B_ns, B_hs, C_bs, C_gs, C_ns, C_hs;
     void *out; int64_t o_bs, o_ds, o_hs;  // forward: out; backward: dout
     float2 *saved;                         // [batch][dim][nck][NPp][L*8] checkpoints of h
+    int ck_roll;                           // forward without backward: one rolling row [batch][dim][1][NPp][L*8]
     // Column tiling of rows wider than 256 columns: this launch covers one tile (all
     // tensor pointers are already moved to the tile's first column).  The values that
     // cross a tile boundary travel through global edge buffers [batch][dim][NPp][H] float4

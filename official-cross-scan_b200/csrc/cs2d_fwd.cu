@@ -78,6 +78,9 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
 
     const int nblk = P.nck;
     const int steps = nblk * P.npass;
+    // rows of the state buffer per (batch, channel): every block's last h row when a backward
+    // will follow, one rolling row otherwise
+    const int ckn = P.ck_roll ? 1 : nblk;
 
     // Bulk asynchronous staging: the raw row blocks of u and delta of step k+1 are
     // copied global -> shared by the copy engine while step k computes; an mbarrier
@@ -121,7 +124,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
             const bool ok = nr > 0 && r0 > 0 && pair_on && ch0 + cp < nch;
             const int dq = dbase + min(ch0 + cp, nch - 1);
             const float4 *pk = reinterpret_cast<const float4 *>(
-                P.saved + ((((int64_t)b * P.dim + dq) * P.nck + (blk - 1)) * NPp + pp) * Wp + j * STRIP);
+                P.saved + ((((int64_t)b * P.dim + dq) * ckn + (P.ck_roll ? 0 : blk - 1)) * NPp + pp) * Wp + j * STRIP);
 #pragma unroll
             for (int k = 0; k < STRIP / 2; ++k) ck_pre[k] = ok ? pk[k] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
@@ -233,7 +236,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
             const float2 A2 = f2(__ldg(P.A + d * P.A_ds + n0 * P.A_ns) * LOG2E,
                                  n1 < N ? __ldg(P.A + d * P.A_ds + n1 * P.A_ns) * LOG2E : 0.f);
             float2 h_up[STRIP], a_up[STRIP];
-            float2 *ck = P.saved + ((((int64_t)b * P.dim + d) * P.nck + blk) * NPp + pp) * Wp + j * STRIP;
+            float2 *ck = P.saved + ((((int64_t)b * P.dim + d) * ckn + (P.ck_roll ? 0 : blk)) * NPp + pp) * Wp + j * STRIP;
             if (r0 > 0) {
                 float dlt[STRIP];
                 unpack8(sdl + cp * CS5, L4, j, dlt);

@@ -53,6 +53,9 @@ def test_sizes_without_gpu():
     per = 2 * 8 * 8 * 8  # batch x dim x pair slots x bytes per float2
     assert L.cs2d_saved_bytes(ctypes.byref(pw)) == per * 14 * (256 + 128) + 2 * 8 * 8 * 56 * 16
     assert L.cs2d_bwd_scratch_bytes(ctypes.byref(pw)) == per * (256 + 128) + 2 * 8 * 8 * 56 * 16
+    # a forward that no backward follows keeps one rolling row instead of 14 checkpoints
+    assert L.cs2d_fwd_only_scratch_bytes(ctypes.byref(p)) == 2 * 8 * 8 * 64 * 8
+    assert L.cs2d_fwd_only_scratch_bytes(ctypes.byref(pw)) == per * (256 + 128) + 2 * 8 * 8 * 56 * 16
 
 
 @pytest.mark.parametrize("over,msg", [

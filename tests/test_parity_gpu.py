@@ -240,3 +240,18 @@ def test_benchmark_config_shapes_against_oracle(name):
         _, g3, _ = _run(sub)
         check_close("dB", _np(g3[3]), go["dB"], rtol, atol)
         check_close("dC", _np(g3[4]), go["dC"], rtol, atol)
+
+
+@pytest.mark.parametrize("shape,dtype", [((2, 4, 6, 16, 21, 40), torch.float32), ((1, 2, 5, 3, 13, 300), torch.float32),
+                                         ((2, 4, 40, 16, 14, 14), torch.bfloat16), ((2, 2, 3, 1, 9, 9), torch.float16)])
+def test_forward_only_equals_forward(shape, dtype):
+    """The forward that keeps no saved state (rolling row) returns bit-identical results."""
+    inp = make_inputs(*shape, dtype=dtype, seed=6)
+    dev = {k: (v.cuda() if v is not None else None) for k, v in inp.items()}
+    args = (dev["u"], dev["delta"], dev["A"], dev["B"], dev["C"], dev["D"], dev["delta_bias"], True, False, None)
+    full = cs2d.fwd(*args)[0]
+    only = cs2d.fwd_only(*args)
+    assert torch.equal(full, only)
+    with torch.no_grad():
+        assert torch.equal(cs2d.selective_scan_2d(*args), full)
+    assert cs2d.device_status() == 0
