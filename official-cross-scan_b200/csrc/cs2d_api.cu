@@ -11,8 +11,8 @@
 namespace cs2d {
 cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st);
 cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st);
-size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk);
-size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk);
+size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk, int CT, bool tiled);
+size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk, bool tiled);
 static __device__ int g_cs2d_status = 0;  // see ERR_* in cs2d_common.cuh
 
 // Device address of the status word on the current device (looked up once per device).
@@ -38,11 +38,13 @@ static int fail(int code, const char *fmt, ...) {
 
 struct Geometry { int L, NPp, CG, CP, CT, npass, ntiles, grid, nck, acc, bulk; };
 
-static const size_t kMaxSmem = 227 * 1024;
+static const size_t kMaxSmem = 227 * 1024;   // largest dynamic shared memory of one CTA
+static const size_t kSmSmem = 228 * 1024;    // shared memory of one SM; every resident CTA also reserves 1 KB
+static const size_t kCtaReserve = 1024;
 static const int kSMs = 148;
 
 // Lanes per row, state-pair slots, channels per pass and per CTA, and the grid.
-static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, Geometry *g) {
+static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, Geometry *g) {
     const int W = p->ncols, es = p->io_dtype == CS2D_F32 ? 4 : 2, eso = p->out_dtype == CS2D_F32 ? 4 : 2;
     const int strips = (p->ncols + STRIP - 1) / STRIP;
     int L = 1;
@@ -55,8 +57,8 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, Geometry *g)
     // Channel groups per pass: fill the CTA up to 8 warps, but keep the staged
     // per-channel tiles small enough that the shared memory fits.
     int CG = MAX_WARPS / NPp;
-    while (CG > 1 && (backward ? bwd_smem_bytes(L, CG, NPp, CG * (32 / L), false, W, es, eso, false)
-                               : 2 * fwd_smem_bytes(L, CG, NPp, W, es, false)) > kMaxSmem)
+    while (CG > 1 && (backward ? bwd_smem_bytes(L, CG, NPp, CG * (32 / L), false, W, es, eso, false, tiled) > kMaxSmem
+                               : 2 * (fwd_smem_bytes(L, CG, NPp, W, es, false, CG * (32 / L), tiled) + kCtaReserve) > kSmSmem))
         CG >>= 1;
     const int CP = CG * (32 / L);
     const int pmax = (dpg + CP - 1) / CP;  // passes that cover a whole group
@@ -80,15 +82,16 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, Geometry *g)
     g->bulk = bulk_ok ? 1 : 0;
     if (backward) {
         // drop, in this order, the bulk staging buffers, then the dB/dC accumulators, then passes
-        if (bwd_smem_bytes(L, CG, NPp, npass * CP, true, W, es, eso, g->bulk) > kMaxSmem) g->bulk = 0;
-        if (bwd_smem_bytes(L, CG, NPp, npass * CP, true, W, es, eso, false) > kMaxSmem) g->acc = 0;
-        while (npass > 1 && bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false) > kMaxSmem) --npass;
-        if (bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false) > kMaxSmem)
+        if (bwd_smem_bytes(L, CG, NPp, npass * CP, true, W, es, eso, g->bulk, tiled) > kMaxSmem) g->bulk = 0;
+        if (bwd_smem_bytes(L, CG, NPp, npass * CP, true, W, es, eso, false, tiled) > kMaxSmem) g->acc = 0;
+        while (npass > 1 && bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false, tiled) > kMaxSmem) --npass;
+        if (bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false, tiled) > kMaxSmem)
             return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d with dstate=%d needs more shared memory than one SM has",
                         p->ncols, p->dstate);
     } else {
-        if (2 * fwd_smem_bytes(L, CG, NPp, W, es, g->bulk) > kMaxSmem) g->bulk = 0;  // keep two CTAs per SM
-        if (fwd_smem_bytes(L, CG, NPp, W, es, false) > kMaxSmem)
+        // keep two CTAs per SM
+        if (2 * (fwd_smem_bytes(L, CG, NPp, W, es, g->bulk, npass * CP, tiled) + kCtaReserve) > kSmSmem) g->bulk = 0;
+        if (fwd_smem_bytes(L, CG, NPp, W, es, false, npass * CP, tiled) > kMaxSmem)
             return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d with dstate=%d needs more shared memory than one SM has",
                         p->ncols, p->dstate);
     }
@@ -198,7 +201,7 @@ static int tile_view(const cs2d_problem *p, int t, bool backward, bool bulk_ok, 
     tv->q.delta = at(p->delta, tv->c0, es);
     tv->q.B = at(p->B, tv->c0, es);
     tv->q.C = at(p->C, tv->c0, es);
-    int rc = plan(&tv->q, backward, bulk_ok, &tv->g);
+    int rc = plan(&tv->q, backward, bulk_ok, n_tiles(p->ncols) > 1, &tv->g);
     if (rc) return rc;
     const size_t per = (size_t)p->batch * p->dim * tv->g.NPp * (tv->g.L * STRIP) * sizeof(float2);
     tv->saved_bytes = per * tv->g.nck;

@@ -44,9 +44,12 @@ struct BwdSmem {
     static __host__ __device__ constexpr int aB(int CP, int NPp, int nw) { return C(CP, NPp, nw) + NPp * RB * Wp * 2; }  // [warps][RB][Wp] float2
     static __host__ __device__ constexpr int aC(int CP, int NPp, int nw, bool acc) { return aB(CP, NPp, nw) + (acc ? nw * RB * Wp * 2 : 0); }
     static __host__ __device__ constexpr int dA(int CP, int NPp, int nw, bool acc) { return aC(CP, NPp, nw, acc) + (acc ? nw * RB * Wp * 2 : 0); }
-    // dA: [CT][2*NPp], red: [CT][2], decay: [warps]
+    // dD / ddelta_bias partial sums: one slot per (channel, segment of the channel's RB*T4 write-out
+    // items that one warp reduces), so that every slot has a single owner and needs no atomics
+    static constexpr int SEG = RB * (Wp / 4) < 32 ? RB * (Wp / 4) : 32, NSEG = RB * (Wp / 4) / SEG;
+    // dA: [CT][2*NPp], red: [CT][NSEG][2], decay: [warps], par: [CT][2] (D, delta_bias of the CTA's channels)
     static __host__ __device__ constexpr int total(int CP, int NPp, int CT, int nw, bool acc) {
-        return dA(CP, NPp, nw, acc) + CT * 2 * NPp + CT * 2 + nw;
+        return dA(CP, NPp, nw, acc) + CT * 2 * NPp + CT * NSEG * 2 + nw + CT * 2;
     }
 };
 
@@ -71,7 +74,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
     float2 *saC = reinterpret_cast<float2 *>(smem + S::aC(CP, NPp, nw, acc_on));
     float *sdA = smem + S::dA(CP, NPp, nw, acc_on);
     float *sred = sdA + CT * 2 * NPp;
-    float *sdecay = sred + CT * 2;
+    float *sdecay = sred + CT * S::NSEG * 2;
+    float *spar = sdecay + nw;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int j = lane & (L - 1), cl = lane / L;
@@ -91,7 +95,11 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
     for (int i = tid; i < nw * CW * CS4; i += nthr) { spdu[i] = 0.f; spdd[i] = 0.f; }
     if (acc_on)
         for (int i = tid; i < nw * RB * Wp; i += nthr) { saB[i] = bc(0.f); saC[i] = bc(0.f); }
-    for (int i = tid; i < CT * 2 * NPp + CT * 2 + nw; i += nthr) sdA[i] = 0.f;
+    for (int i = tid; i < CT * 2 * NPp + CT * S::NSEG * 2 + nw; i += nthr) sdA[i] = 0.f;
+    for (int i = tid; i < nch; i += nthr) {  // D and delta_bias of this CTA's channels
+        spar[2 * i] = P.D ? __ldg(P.D + dbase + i) : 0.f;
+        spar[2 * i + 1] = P.bias ? __ldg(P.bias + (dbase + i) / P.drep) : 0.f;
+    }
     float2 ddecay_acc = bc(0.f);
 
     const int nblk = P.nck, npass = P.npass;
@@ -107,17 +115,18 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
     // the softplus'd delta of those two columns
     const int tot4 = (S::total(CP, NPp, CT, nw, acc_on) + 3) & ~3;
     float4 *sedge = reinterpret_cast<float4 *>(smem + tot4);
-    float4 *sadj = sedge + CP * NPp * (RB + 1);
-    float *sedl_l = reinterpret_cast<float *>(sadj + CP * NPp * (RB + 1));   // [CP][RB]
-    float *sedl_r = sedl_l + CP * 4;                                          // [CP][RB+1] (pitch 8)
+    // (the four edge areas only exist in the kernels that handle column tiles)
+    float4 *sadj = sedge + (TILED ? CP * NPp * (RB + 1) : 0);
+    float *sedl_l = reinterpret_cast<float *>(sadj + (TILED ? CP * NPp * (RB + 1) : 0));   // [CP][RB]
+    float *sedl_r = sedl_l + (TILED ? CP * 4 : 0);                                          // [CP][RB+1] (pitch 8)
     const bool has_left = TILED && P.tile_left != 0, has_right = TILED && P.tile_right != 0;
     const bool fh = (P.flip_h >> g_) & 1u, fw = (P.flip_w >> g_) & 1u;  // scan direction of this group
     const int ush = (P.u_shared & 1) ? g_ * P.dpg : 0;                    // u indexed by channel - ush
     const int gsh = (P.u_shared & 2) ? g_ * P.dpg : 0;                    // dout indexed by channel - gsh
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sedl_r + CP * 8);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sedl_r + (TILED ? CP * 8 : 0));
     unsigned char *raw = reinterpret_cast<unsigned char *>(bars + 2);
     const int stage_bytes = CP * W * (RB * es + RB * eso + (RB + 2) * es);
-    auto issue = [&](int k) {
+    auto issue = [&](int k) {  // called by every lane of warp 0: one copy per lane and round
         const int kblk = nblk - 1 - k / npass, kpass = k % npass;
         const int kr0 = kblk * RB, knr = min(RB, H - kr0), kch0 = kpass * CP;
         const int lo = max(kr0 - 1, 0), hi = min(kr0 + knr + 1, H);
@@ -125,25 +134,30 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
         uint64_t *bar = bars + (k & 1);
         unsigned char *ru = raw + (size_t)(k & 1) * stage_bytes, *rg = ru + (size_t)CP * RB * W * es;
         unsigned char *rd = rg + (size_t)CP * RB * W * eso;
-        mbar_expect_tx(bar, (uint32_t)(nv * W * (knr * es + knr * eso + (hi - lo) * es)));
-        for (int sc = 0; sc < nv; ++sc) {
-            const int sd = dbase + kch0 + sc, sdd = sd / P.drep;
-            const char *srcu = reinterpret_cast<const char *>(P.u) +
-                               ((int64_t)b * P.u_bs + (int64_t)sd * P.u_ds + (int64_t)kr0 * W) * es;
-            const char *srcg = reinterpret_cast<const char *>(P.out) +
-                               ((int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + (int64_t)kr0 * W) * eso;
-            const char *srcd = reinterpret_cast<const char *>(P.delta) +
-                               ((int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)lo * W) * es;
-            bulk_g2s(ru + (size_t)sc * RB * W * es, srcu, (uint32_t)(knr * W * es), bar);
-            bulk_g2s(rg + (size_t)sc * RB * W * eso, srcg, (uint32_t)(knr * W * eso), bar);
-            bulk_g2s(rd + (size_t)sc * (RB + 2) * W * es, srcd, (uint32_t)((hi - lo) * W * es), bar);
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)(nv * W * (knr * es + knr * eso + (hi - lo) * es)));
+        __syncwarp();
+        for (int i = lane; i < 3 * nv; i += 32) {
+            const int sc = i / 3, kind = i - 3 * sc;
+            const int sd = dbase + kch0 + sc;
+            if (kind == 0) {
+                bulk_g2s(ru + (size_t)sc * RB * W * es,
+                         reinterpret_cast<const char *>(P.u) + ((int64_t)b * P.u_bs + (int64_t)sd * P.u_ds + (int64_t)kr0 * W) * es,
+                         (uint32_t)(knr * W * es), bar);
+            } else if (kind == 1) {
+                bulk_g2s(rg + (size_t)sc * RB * W * eso,
+                         reinterpret_cast<const char *>(P.out) + ((int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + (int64_t)kr0 * W) * eso,
+                         (uint32_t)(knr * W * eso), bar);
+            } else {
+                bulk_g2s(rd + (size_t)sc * (RB + 2) * W * es,
+                         reinterpret_cast<const char *>(P.delta) +
+                             ((int64_t)b * P.dl_bs + (int64_t)(sd / P.drep) * P.dl_ds + (int64_t)lo * W) * es,
+                         (uint32_t)((hi - lo) * W * es), bar);
+            }
         }
     };
-    if (bulk) {
-        if (tid == 0) { mbar_init(bars, 1); mbar_init(bars + 1, 1); mbar_init_fence(); }
-        __syncthreads();
-        if (tid == 0 && steps > 0) issue(0);
-    }
+    if (bulk && tid == 0) { mbar_init(bars, 1); mbar_init(bars + 1, 1); mbar_init_fence(); }
+    __syncthreads();  // barriers initialised, parameter copies and zeroed tiles visible
+    if (bulk && warp == 0 && steps > 0) issue(0);
     for (int step = 0; step <= steps; ++step) {
         const int blk = nblk - 1 - step / npass, pass = step % npass;  // bottom-up
         const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
@@ -169,7 +183,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
         }
         // ---- phase A: write out the previous step, stage this one -------------------
         if (bulk) {
-            if (tid == 0 && step + 1 < steps) issue(step + 1);   // lands while this step computes
+            if (warp == 0 && step + 1 < steps) issue(step + 1);   // lands while this step computes
             bool ok = nr == 0 || mbar_wait_bounded(bars + (step & 1), (step >> 1) & 1);
             if (__syncthreads_or(!ok)) {  // give up: flag it, drain the other stage, leave
                 if (tid == 0) atomicOr(P.status, ERR_BULK_COPY_TIMEOUT);
@@ -202,7 +216,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         const float4 gv = *reinterpret_cast<const float4 *>(sg + o4);
                         const float4 uv = *reinterpret_cast<const float4 *>(su + o4);
                         const float4 sv = *reinterpret_cast<const float4 *>(ssig + o4);
-                        const float Dv = P.D ? __ldg(P.D + sd) : 0.f;
+                        const float Dv = spar[2 * (pch0 + sc)];
                         a1.x = fmaf(Dv, gv.x, a1.x); a1.y = fmaf(Dv, gv.y, a1.y);
                         a1.z = fmaf(Dv, gv.z, a1.z); a1.w = fmaf(Dv, gv.w, a1.w);
                         a2.x *= sv.x; a2.y *= sv.y; a2.z *= sv.z; a2.w *= sv.w;
@@ -214,15 +228,16 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         dbp = a2.x + a2.y + a2.z + a2.w;
                     }
                     // the RB*T4 items of a channel are consecutive: segmented warp sum
-                    constexpr int SEG = RB * T4 < 32 ? RB * T4 : 32;
+                    constexpr int SEG = S::SEG;
 #pragma unroll
                     for (int off = SEG / 2; off; off >>= 1) {
                         dDp += __shfl_xor_sync(0xffffffffu, dDp, off);
                         dbp += __shfl_xor_sync(0xffffffffu, dbp, off);
                     }
-                    if ((lane & (SEG - 1)) == 0 && pch0 + sc < nch) {
-                        atomicAdd(sred + 2 * (pch0 + sc), dDp);
-                        atomicAdd(sred + 2 * (pch0 + sc) + 1, dbp);
+                    if ((lane & (SEG - 1)) == 0 && pch0 + sc < nch) {  // the slot's only writer
+                        float *q = sred + ((pch0 + sc) * S::NSEG + (it % (RB * T4)) / SEG) * 2;
+                        q[0] += dDp;
+                        q[1] += dbp;
                     }
                 }
                 // stage this step's u, dout, delta (row rr) for the same item: the thread that
@@ -242,29 +257,30 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                         xv = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, r, c, H, W, fh, fw,
                                   P.io_dt, P.vec & VEC_DELTA);
                     }
-                    soft4(xv, sv, P.bias ? __ldg(P.bias + sdd) : 0.f, P.softplus, W - c);
+                    soft4(xv, sv, spar[2 * (ch0 + sc) + 1], P.softplus, W - c);
                 }
                 *reinterpret_cast<float4 *>(su + o4) = uv;
                 *reinterpret_cast<float4 *>(sg + o4) = gv;
                 *reinterpret_cast<float4 *>(ssig + o4) = sv;
                 *reinterpret_cast<float4 *>(sdl + sc * CS6 + (rr + 1) * Wp + pos4<L>(t)) = xv;
             }
-            if (nr > 0) {  // delta of the rows just above and just below the block
-                const int itemsH = CP * 2 * T4;
+            if (nr > 0) {  // delta of the rows just above and just below the block, one column per item
+                const int itemsH = CP * 2 * Wp;
                 for (int it = tid; it < itemsH; it += nthr) {
-                    const int t = it % T4, which = (it / T4) & 1, sc = it / (T4 * 2);
-                    const int c = 4 * t, rr = which ? RB + 1 : 0, r = r0 + rr - 1;
-                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f), unused = x;
+                    const int c = it % Wp, which = (it / Wp) & 1, sc = it / (Wp * 2);
+                    const int rr = which ? RB + 1 : 0, r = r0 + rr - 1;
+                    float x = 0.f;
                     if (r >= 0 && r < H && rr - 1 <= nr && ch0 + sc < nch && c < W) {
                         const int sdd = (dbase + ch0 + sc) / P.drep;
                         if (bulk)
-                            x = lds4(raw_dl, (sc * (RB + 2) + (r - lo)) * W + c, P.io_dt);
+                            x = lds1(raw_dl, (sc * (RB + 2) + (r - lo)) * W + c, P.io_dt);
                         else
-                            x = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, r, c, H, W, fh, fw,
-                                     P.io_dt, P.vec & VEC_DELTA);
-                        soft4(x, unused, P.bias ? __ldg(P.bias + sdd) : 0.f, P.softplus, W - c);
+                            x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds +
+                                                     (int64_t)(fh ? H - 1 - r : r) * P.dl_hs + (fw ? W - 1 - c : c), P.io_dt);
+                        x += spar[2 * (ch0 + sc) + 1];
+                        if (P.softplus) x = softplus20(x);
                     }
-                    *reinterpret_cast<float4 *>(sdl + sc * CS6 + rr * Wp + pos4<L>(t)) = x;
+                    sdl[sc * CS6 + rr * Wp + pos1<L>(c)] = x;
                 }
             }
             // a row block is complete when its last pass has been written out
@@ -637,8 +653,10 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
     }
     for (int i = tid; i < nch * 2; i += nthr) {
         const int sd = dbase + i / 2;
-        if ((i & 1) == 0) { if (P.dD) atomicAdd(P.dD + sd, sred[i]); }
-        else if (P.dbias) atomicAdd(P.dbias + sd, sred[i]);
+        float v = 0.f;
+        for (int q = 0; q < S::NSEG; ++q) v += sred[((i / 2) * S::NSEG + q) * 2 + (i & 1)];
+        if ((i & 1) == 0) { if (P.dD) atomicAdd(P.dD + sd, v); }
+        else if (P.dbias) atomicAdd(P.dbias + sd, v);
     }
     if (want_decay && tid == 0) {
         float v = 0.f;
@@ -647,10 +665,10 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
     }
 }
 
-size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk) {
+size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk, bool tiled) {
     const int nw = CG * NPp;
     const int CPh = CG * (32 / L);
-    const size_t extra = (size_t)(2 * CPh * NPp * (RB + 1) * 4 + CPh * 12) * 4 + 16 +
+    const size_t extra = (size_t)(tiled ? 2 * CPh * NPp * (RB + 1) * 4 + CPh * 12 : 0) * 4 + 16 +
                          (bulk ? 2 * (size_t)CPh * W * (RB * es + RB * eso + (RB + 2) * es) : 0);
     const int CP = CG * (32 / L);
     switch (L) {
@@ -680,7 +698,7 @@ static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) 
 cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st) {
     const bool spec = P.NPp == 8 && P.CG == 1, tiled = P.tile_left || P.tile_right;
     const size_t smem = bwd_smem_bytes(L, P.CG, P.NPp, P.CT, P.acc_dbc != 0, P.W, P.io_dt == CS2D_F32 ? 4 : 2,
-                                       P.out_dt == CS2D_F32 ? 4 : 2, P.bulk != 0);
+                                       P.out_dt == CS2D_F32 ? 4 : 2, P.bulk != 0, tiled);
     switch (L) {
         case 1: return tiled ? (spec ? launch<1, 8, true>(P, grid, smem, st) : launch<1, 0, true>(P, grid, smem, st))
                              : (spec ? launch<1, 8, false>(P, grid, smem, st) : launch<1, 0, false>(P, grid, smem, st));

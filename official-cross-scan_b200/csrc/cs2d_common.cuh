@@ -226,6 +226,13 @@ __device__ __forceinline__ float4 lds4(const unsigned char *raw, int idx, int dt
     return make_float4(a.x, a.y, b.x, b.y);
 }
 
+// one element of a raw (input dtype) shared-memory row as a float
+__device__ __forceinline__ float lds1(const unsigned char *raw, int idx, int dt) {
+    if (dt == CS2D_F32) return reinterpret_cast<const float *>(raw)[idx];
+    if (dt == CS2D_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(raw)[idx]);
+    return __half2float(reinterpret_cast<const __half *>(raw)[idx]);
+}
+
 // Direction-aware access to 4 consecutive SCAN columns c..c+3 of scan row r of an image plane
 // (element offset `plane`, row pitch `hs`): rows are mirrored when fh, columns when fw.
 __device__ __forceinline__ float4 ld4d(const void *p, int64_t plane, int64_t hs, int r, int c, int H, int W, bool fh,
@@ -265,8 +272,9 @@ __device__ __forceinline__ void soft4(float4 &x, float4 &sig, float bias, int so
     for (int e = 0; e < 4; ++e) {
         sg[e] = 1.f;
         if (softplus && xs[e] <= 20.f) {
-            sg[e] = 1.f / (1.f + __expf(-xs[e]));
-            xs[e] = log1pf(__expf(xs[e]));
+            const float t = __expf(xs[e]);       // <= e^20: 1 + t stays finite and exact enough
+            sg[e] = __fdividef(t, 1.f + t);      // sigmoid(x) = e^x / (1 + e^x)
+            xs[e] = log1pf(t);
         }
         if (e >= nvalid) { xs[e] = 0.f; sg[e] = 0.f; }
     }
@@ -288,6 +296,9 @@ __host__ __device__ constexpr int chan_stride(int rows) {
 // float offset of the float4 holding columns 4t..4t+3 of a row
 template <int L>
 __device__ __forceinline__ int pos4(int t) { return (t & 1) * (4 * L) + 4 * (t >> 1); }
+// float offset of column c of a row
+template <int L>
+__device__ __forceinline__ int pos1(int c) { return pos4<L>(c >> 2) + (c & 3); }
 // Pair tiles are [slot][row][Wp] float2; the 8 columns of strip j are four
 // float4 (two columns x two states) at float2 offsets k*2L + 2j, k = 0..3.
 template <int L>

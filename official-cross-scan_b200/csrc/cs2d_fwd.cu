@@ -31,10 +31,21 @@ struct FwdSmem {
     // (u: RB rows, delta: RB+1 rows per channel, in the input dtype)
     // left-edge values of a column tile: [CP][NPp][RB+1] float4 (h, s of rows r0-1..r0+RB-1)
     // and the softplus'd delta of the column left of the tile [CP][RB] (padded to 4 floats)
+    // (both only exist in the kernels that handle column tiles)
     static __host__ __device__ constexpr int edge(int CP, int NPp, int nw) { return total(CP, NPp, nw); }
-    static __host__ __device__ constexpr int edl(int CP, int NPp, int nw) { return edge(CP, NPp, nw) + CP * NPp * (RB + 1) * 4; }
-    static __host__ __device__ constexpr int bars(int CP, int NPp, int nw) { return edl(CP, NPp, nw) + CP * 4; }
-    static __host__ __device__ constexpr int raw(int CP, int NPp, int nw) { return bars(CP, NPp, nw) + 4; }
+    static __host__ __device__ constexpr int edl(int CP, int NPp, int nw, bool tiled) {
+        return edge(CP, NPp, nw) + (tiled ? CP * NPp * (RB + 1) * 4 : 0);
+    }
+    // D and delta_bias of the CTA's CT channels: [CT][2], padded to 16 bytes
+    static __host__ __device__ constexpr int par(int CP, int NPp, int nw, bool tiled) {
+        return edl(CP, NPp, nw, tiled) + (tiled ? CP * 4 : 0);
+    }
+    static __host__ __device__ constexpr int bars(int CP, int NPp, int nw, bool tiled, int CT) {
+        return par(CP, NPp, nw, tiled) + ((2 * CT + 3) & ~3);
+    }
+    static __host__ __device__ constexpr int raw(int CP, int NPp, int nw, bool tiled, int CT) {
+        return bars(CP, NPp, nw, tiled, CT) + 4;
+    }
     static __host__ __device__ constexpr int stage_bytes(int CP, int W, int es) { return CP * (2 * RB + 1) * W * es; }
 };
 
@@ -54,7 +65,8 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
     float2 *sB = reinterpret_cast<float2 *>(smem + S::B(CP, nw));
     float2 *sC = sB + NPp * RB * Wp;
     float4 *sedge = reinterpret_cast<float4 *>(smem + S::edge(CP, NPp, nw));
-    float *sedl = smem + S::edl(CP, NPp, nw);
+    float *sedl = smem + S::edl(CP, NPp, nw, TILED);
+    float *spar = smem + S::par(CP, NPp, nw, TILED);
     const bool has_left = TILED && P.tile_left != 0;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -75,6 +87,10 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
 
     // the partial tiles of idle pair slots are summed too: keep them zero
     for (int i = tid; i < nw * CW * CS4; i += nthr) sy[i] = 0.f;
+    for (int i = tid; i < nch; i += nthr) {  // D and delta_bias of this CTA's channels
+        spar[2 * i] = P.D ? __ldg(P.D + dbase + i) : 0.f;
+        spar[2 * i + 1] = P.bias ? __ldg(P.bias + (dbase + i) / P.drep) : 0.f;
+    }
 
     const int nblk = P.nck;
     const int steps = nblk * P.npass;
@@ -87,32 +103,35 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
     // per stage counts the bytes.  One thread issues, everybody waits (bounded).
     const bool bulk = P.bulk != 0;
     const int es = P.io_dt == CS2D_F32 ? 4 : 2;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::bars(CP, NPp, nw));
-    unsigned char *raw = reinterpret_cast<unsigned char *>(smem + S::raw(CP, NPp, nw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::bars(CP, NPp, nw, TILED, P.CT));
+    unsigned char *raw = reinterpret_cast<unsigned char *>(smem + S::raw(CP, NPp, nw, TILED, P.CT));
     const int stage_bytes = S::stage_bytes(CP, W, es);
-    auto issue = [&](int k) {
+    auto issue = [&](int k) {  // called by every lane of warp 0: one copy per lane and round
         const int kblk = k / P.npass, kpass = k % P.npass;
         const int kr0 = kblk * RB, knr = min(RB, H - kr0), kch0 = kpass * CP;
         const int lo = max(kr0 - 1, 0), nrows_dl = kr0 + knr - lo;
         const int nv = max(0, min(CP, nch - kch0));
         uint64_t *bar = bars + (k & 1);
         unsigned char *ru = raw + (size_t)(k & 1) * stage_bytes, *rd = ru + (size_t)CP * RB * W * es;
-        mbar_expect_tx(bar, (uint32_t)(nv * (knr + nrows_dl) * W * es));
-        for (int sc = 0; sc < nv; ++sc) {
-            const int sd = dbase + kch0 + sc, sdd = sd / P.drep;
-            const char *srcu = reinterpret_cast<const char *>(P.u) +
-                               ((int64_t)b * P.u_bs + (int64_t)sd * P.u_ds + (int64_t)kr0 * W) * es;
-            const char *srcd = reinterpret_cast<const char *>(P.delta) +
-                               ((int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + (int64_t)lo * W) * es;
-            bulk_g2s(ru + (size_t)sc * RB * W * es, srcu, (uint32_t)(knr * W * es), bar);
-            bulk_g2s(rd + (size_t)sc * (RB + 1) * W * es, srcd, (uint32_t)(nrows_dl * W * es), bar);
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)(nv * (knr + nrows_dl) * W * es));
+        __syncwarp();
+        for (int i = lane; i < 2 * nv; i += 32) {
+            const int sc = i >> 1, sd = dbase + kch0 + sc;
+            if ((i & 1) == 0) {
+                bulk_g2s(ru + (size_t)sc * RB * W * es,
+                         reinterpret_cast<const char *>(P.u) + ((int64_t)b * P.u_bs + (int64_t)sd * P.u_ds + (int64_t)kr0 * W) * es,
+                         (uint32_t)(knr * W * es), bar);
+            } else {
+                bulk_g2s(rd + (size_t)sc * (RB + 1) * W * es,
+                         reinterpret_cast<const char *>(P.delta) +
+                             ((int64_t)b * P.dl_bs + (int64_t)(sd / P.drep) * P.dl_ds + (int64_t)lo * W) * es,
+                         (uint32_t)(nrows_dl * W * es), bar);
+            }
         }
     };
-    if (bulk) {
-        if (tid == 0) { mbar_init(bars, 1); mbar_init(bars + 1, 1); mbar_init_fence(); }
-        __syncthreads();
-        if (tid == 0 && steps > 0) issue(0);
-    }
+    if (bulk && tid == 0) { mbar_init(bars, 1); mbar_init(bars + 1, 1); mbar_init_fence(); }
+    __syncthreads();  // barriers initialised, parameter copies and zeroed tiles visible
+    if (bulk && warp == 0 && steps > 0) issue(0);
     for (int step = 0; step <= steps; ++step) {
         const int blk = step / P.npass, pass = step % P.npass;
         const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
@@ -130,7 +149,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
         }
         // ---- phase A: write out the previous step, stage this one -------------------
         if (bulk) {
-            if (tid == 0 && step + 1 < steps) issue(step + 1);   // lands while this step computes
+            if (warp == 0 && step + 1 < steps) issue(step + 1);   // lands while this step computes
             bool ok = nr == 0 || mbar_wait_bounded(bars + (step & 1), (step >> 1) & 1);
             if (__syncthreads_or(!ok)) {  // give up: flag it, drain the other stage, leave
                 if (tid == 0) atomicOr(P.status, ERR_BULK_COPY_TIMEOUT);
@@ -159,7 +178,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                     }
                     if (P.D) {
-                        const float Dv = __ldg(P.D + sd);
+                        const float Dv = spar[2 * (pch0 + sc)];
                         const float4 uv = *reinterpret_cast<const float4 *>(su + o4);
                         acc.x = fmaf(Dv, uv.x, acc.x); acc.y = fmaf(Dv, uv.y, acc.y);
                         acc.z = fmaf(Dv, uv.z, acc.z); acc.w = fmaf(Dv, uv.w, acc.w);
@@ -167,39 +186,46 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                     st4d(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds, P.o_hs, pr0 + rr, c, H, W, fh, fw, P.out_dt,
                          P.vec & VEC_OUT, acc);
                 }
-                float4 uv = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (rr < nr && ch0 + sc < nch) {
+                // this step's u and delta of row rr for the same item
+                float4 uv = make_float4(0.f, 0.f, 0.f, 0.f), x = uv;
+                if (rr < nr && ch0 + sc < nch && c < W) {
+                    const int sdd = (dbase + ch0 + sc) / P.drep;
                     if (bulk) {
-                        if (c < W) uv = lds4(raw_u, (sc * RB + rr) * W + c, P.io_dt);
+                        uv = lds4(raw_u, (sc * RB + rr) * W + c, P.io_dt);
+                        x = lds4(raw_dl, (sc * (RB + 1) + (r0 + rr - lo)) * W + c, P.io_dt);
                     } else {
                         uv = ld4d(P.u, (int64_t)b * P.u_bs + (int64_t)(dbase + ch0 + sc - ush) * P.u_ds, P.u_hs, r0 + rr, c,
                                   H, W, fh, fw, P.io_dt, P.vec & VEC_U);
+                        x = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, r0 + rr, c, H, W, fh, fw,
+                                 P.io_dt, P.vec & VEC_DELTA);
                     }
+                    const float bv = spar[2 * (ch0 + sc) + 1];
+                    x.x += bv; x.y += bv; x.z += bv; x.w += bv;
+                    if (P.softplus) {
+                        x.x = softplus20(x.x); x.y = softplus20(x.y); x.z = softplus20(x.z); x.w = softplus20(x.w);
+                    }
+                    const int nv = W - c;  // columns past the image keep dl = 0
+                    if (nv < 4) { x.w = 0.f; if (nv < 3) x.z = 0.f; if (nv < 2) x.y = 0.f; }
                 }
                 *reinterpret_cast<float4 *>(su + o4) = uv;
+                *reinterpret_cast<float4 *>(sdl + sc * CS5 + (rr + 1) * Wp + pos4<L>(t)) = x;
             }
             if (nr > 0) {
-                const int items5 = CP * (RB + 1) * T4;
-                for (int it = tid; it < items5; it += nthr) {
-                    const int t = it % T4, rr = (it / T4) % (RB + 1), sc = it / (T4 * (RB + 1));
-                    const int c = 4 * t, r = r0 + rr - 1;
-                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (r >= 0 && rr - 1 < nr && ch0 + sc < nch && c < W) {
+                // delta of the row above the block, one column per item so that all warps share it
+                for (int it = tid; it < CP * Wp; it += nthr) {
+                    const int c = it % Wp, sc = it / Wp, r = r0 - 1;
+                    float x = 0.f;
+                    if (r >= 0 && ch0 + sc < nch && c < W) {
                         const int sdd = (dbase + ch0 + sc) / P.drep;
                         if (bulk)
-                            x = lds4(raw_dl, (sc * (RB + 1) + (r - lo)) * W + c, P.io_dt);
+                            x = lds1(raw_dl, sc * (RB + 1) * W + c, P.io_dt);
                         else
-                            x = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, r, c, H, W, fh, fw,
-                                     P.io_dt, P.vec & VEC_DELTA);
-                        const float bv = P.bias ? __ldg(P.bias + sdd) : 0.f;
-                        x.x += bv; x.y += bv; x.z += bv; x.w += bv;
-                        if (P.softplus) {
-                            x.x = softplus20(x.x); x.y = softplus20(x.y); x.z = softplus20(x.z); x.w = softplus20(x.w);
-                        }
-                        const int nv = W - c;  // columns past the image keep dl = 0
-                        if (nv < 4) { x.w = 0.f; if (nv < 3) x.z = 0.f; if (nv < 2) x.y = 0.f; }
+                            x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds +
+                                                     (int64_t)(fh ? H - 1 - r : r) * P.dl_hs + (fw ? W - 1 - c : c), P.io_dt);
+                        x += spar[2 * (ch0 + sc) + 1];
+                        if (P.softplus) x = softplus20(x);
                     }
-                    *reinterpret_cast<float4 *>(sdl + sc * CS5 + rr * Wp + pos4<L>(t)) = x;
+                    sdl[sc * CS5 + pos1<L>(c)] = x;
                 }
                 if (pass == 0) stage_BC<L>(P, b, g, r0, nr, sB, sC, fh, fw);
                 if (has_left) {  // column left of this tile: h, s written by the tile to the left; delta
@@ -295,10 +321,10 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
     }
 }
 
-size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk) {
+size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk, int CT, bool tiled) {
     const int nw = CG * NPp;
     const int CPh = CG * (32 / L);
-    const size_t extra = (size_t)(CPh * NPp * (RB + 1) * 4 + CPh * 4) * 4 + 16 +
+    const size_t extra = (size_t)((tiled ? CPh * NPp * (RB + 1) * 4 + CPh * 4 : 0) + ((2 * CT + 3) & ~3)) * 4 + 16 +
                          (bulk ? 2 * (size_t)CPh * (2 * RB + 1) * W * es : 0);
     const int CP = CG * (32 / L);
     switch (L) {
@@ -327,7 +353,7 @@ static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) 
 
 cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st) {
     const bool spec = P.NPp == 8 && P.CG == 1, tiled = P.tile_left || P.tile_right;
-    const size_t smem = fwd_smem_bytes(L, P.CG, P.NPp, P.W, P.io_dt == CS2D_F32 ? 4 : 2, P.bulk != 0);
+    const size_t smem = fwd_smem_bytes(L, P.CG, P.NPp, P.W, P.io_dt == CS2D_F32 ? 4 : 2, P.bulk != 0, P.CT, tiled);
     switch (L) {
         case 1: return tiled ? (spec ? launch<1, 8, true>(P, grid, smem, st) : launch<1, 0, true>(P, grid, smem, st))
                              : (spec ? launch<1, 8, false>(P, grid, smem, st) : launch<1, 0, false>(P, grid, smem, st));
