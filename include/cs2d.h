@@ -178,7 +178,8 @@ int cs2d_bwd_noalloc(const cs2d_problem *p, const void *dout, int64_t dout_bs, i
 /*
  * Reads and clears the device-side status word of the current device
  * (synchronises with the device).  0 = no kernel reported a problem; nonzero =
- * a kernel gave up on a bounded wait for one of its asynchronous copies and
+ * a kernel gave up on a bounded wait (bit 0: for one of its asynchronous copies,
+ * bit 1: for the tiles its staging warps hand to its compute warps) and
  * returned early, so the outputs of the calls since the last check are invalid
  * (cs2d_last_error() then describes it).  Negative: the query itself failed.
  * The reference has no counterpart; its kernels contain no waits.

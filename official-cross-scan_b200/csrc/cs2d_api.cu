@@ -1,6 +1,7 @@
 // extern "C" boundary of the cs2d library: validation, launch geometry, errors.
 // Mirrors the checks of the reference host binding
 // (src/cusoflex/selective_scan_oflex.cpp:188-245 and :298-391) on raw pointers.
+#include <cstdlib>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -12,7 +13,7 @@ namespace cs2d {
 cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st);
 cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st);
 size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk, int CT, bool tiled);
-size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk, bool tiled);
+size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk, bool tiled, bool ws);
 static __device__ int g_cs2d_status = 0;  // see ERR_* in cs2d_common.cuh
 
 // Device address of the status word on the current device (looked up once per device).
@@ -36,7 +37,7 @@ static int fail(int code, const char *fmt, ...) {
     return code;
 }
 
-struct Geometry { int L, NPp, CG, CP, CT, npass, ntiles, grid, nck, acc, bulk; };
+struct Geometry { int L, NPp, CG, CP, CT, npass, ntiles, grid, nck, acc, bulk, ws; };
 
 static const size_t kMaxSmem = 227 * 1024;   // largest dynamic shared memory of one CTA
 static const size_t kSmSmem = 228 * 1024;    // shared memory of one SM; every resident CTA also reserves 1 KB
@@ -57,7 +58,7 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, 
     // Channel groups per pass: fill the CTA up to 8 warps, but keep the staged
     // per-channel tiles small enough that the shared memory fits.
     int CG = MAX_WARPS / NPp;
-    while (CG > 1 && (backward ? bwd_smem_bytes(L, CG, NPp, CG * (32 / L), false, W, es, eso, false, tiled) > kMaxSmem
+    while (CG > 1 && (backward ? bwd_smem_bytes(L, CG, NPp, CG * (32 / L), false, W, es, eso, false, tiled, false) > kMaxSmem
                                : 2 * (fwd_smem_bytes(L, CG, NPp, W, es, false, CG * (32 / L), tiled) + kCtaReserve) > kSmSmem))
         CG >>= 1;
     const int CP = CG * (32 / L);
@@ -79,15 +80,24 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, 
         if (cost < best - 1e-9) { best = cost; npass = np; }
     }
     g->acc = 1;
+    g->ws = 0;
     g->bulk = bulk_ok ? 1 : 0;
     if (backward) {
         // drop, in this order, the bulk staging buffers, then the dB/dC accumulators, then passes
-        if (bwd_smem_bytes(L, CG, NPp, npass * CP, true, W, es, eso, g->bulk, tiled) > kMaxSmem) g->bulk = 0;
-        if (bwd_smem_bytes(L, CG, NPp, npass * CP, true, W, es, eso, false, tiled) > kMaxSmem) g->acc = 0;
-        while (npass > 1 && bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false, tiled) > kMaxSmem) --npass;
-        if (bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false, tiled) > kMaxSmem)
+        if (bwd_smem_bytes(L, CG, NPp, npass * CP, true, W, es, eso, g->bulk, tiled, false) > kMaxSmem) g->bulk = 0;
+        if (bwd_smem_bytes(L, CG, NPp, npass * CP, true, W, es, eso, false, tiled, false) > kMaxSmem) g->acc = 0;
+        while (npass > 1 && bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false, tiled, false) > kMaxSmem) --npass;
+        if (bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false, tiled, false) > kMaxSmem)
             return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d with dstate=%d needs more shared memory than one SM has",
                         p->ncols, p->dstate);
+        // The common geometry (8 state-pair slots, one channel group, one column tile) runs
+        // warp-specialised when the second tile set fits: staging warps replace the bulk copies.
+        static const bool ws_off = [] { const char *e = getenv("CS2D_BWD_WS"); return e && e[0] == '0'; }();
+        if (!ws_off && NPp == 8 && CG == 1 && !tiled &&
+            bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false, false, true) <= kMaxSmem) {
+            g->ws = 1;
+            g->bulk = 0;
+        }
     } else {
         // keep two CTAs per SM
         if (2 * (fwd_smem_bytes(L, CG, NPp, W, es, g->bulk, npass * CP, tiled) + kCtaReserve) > kSmSmem) g->bulk = 0;
@@ -143,7 +153,7 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     d.batch = p->batch; d.dim = p->dim; d.H = p->nrows; d.W = p->ncols; d.N = p->dstate; d.G = p->n_groups;
     d.ddim = p->delta_dim; d.io_dt = p->io_dtype; d.out_dt = p->out_dtype; d.softplus = p->delta_softplus;
     d.dpg = p->dim / p->n_groups; d.drep = p->dim / p->delta_dim;
-    d.acc_dbc = g.acc; d.bulk = g.bulk; d.NPp = g.NPp; d.CG = g.CG; d.CT = g.CT; d.npass = g.npass; d.ntiles = g.ntiles; d.nck = g.nck;
+    d.acc_dbc = g.acc; d.bulk = g.bulk; d.ws = g.ws; d.NPp = g.NPp; d.CG = g.CG; d.CT = g.CT; d.npass = g.npass; d.ntiles = g.ntiles; d.nck = g.nck;
     d.u = p->u; d.delta = p->delta; d.B = p->B; d.C = p->C; d.A = p->A; d.D = p->D; d.bias = p->delta_bias;
     d.decay = p->A_decay;
     d.u_bs = p->u_bs; d.u_ds = p->u_ds; d.u_hs = p->u_hs;
@@ -437,7 +447,8 @@ int cs2d_device_status(void) {
     if (cudaMemcpyFromSymbol(&v, g_cs2d_status, sizeof(int)) != cudaSuccess) return CS2D_ERR_CUDA;
     if (v != 0) {
         cudaMemcpyToSymbol(g_cs2d_status, &zero, sizeof(int));
-        fail(CS2D_ERR_CUDA, "a kernel gave up waiting for a bulk copy (status %d); its outputs are invalid", v);
+        fail(CS2D_ERR_CUDA, "a kernel gave up on a bounded wait (status %d: %s%s); its outputs are invalid", v,
+             (v & ERR_BULK_COPY_TIMEOUT) ? "bulk copy " : "", (v & ERR_STAGE_TIMEOUT) ? "staging warps" : "");
     }
     return v;
 }

@@ -44,6 +44,8 @@ struct BwdSmem {
     static __host__ __device__ constexpr int aB(int CP, int NPp, int nw) { return C(CP, NPp, nw) + NPp * RB * Wp * 2; }  // [warps][RB][Wp] float2
     static __host__ __device__ constexpr int aC(int CP, int NPp, int nw, bool acc) { return aB(CP, NPp, nw) + (acc ? nw * RB * Wp * 2 : 0); }
     static __host__ __device__ constexpr int dA(int CP, int NPp, int nw, bool acc) { return aC(CP, NPp, nw, acc) + (acc ? nw * RB * Wp * 2 : 0); }
+    // one set of staged per-channel tiles (u, dout, sigmoid, delta), rounded to 16 bytes
+    static __host__ __device__ constexpr int set_floats(int CP) { return (dl(CP) + CP * CS6 + 3) & ~3; }
     // dD / ddelta_bias partial sums: one slot per (channel, segment of the channel's RB*T4 write-out
     // items that one warp reduces), so that every slot has a single owner and needs no atomics
     static constexpr int SEG = RB * (Wp / 4) < 32 ? RB * (Wp / 4) : 32, NSEG = RB * (Wp / 4) / SEG;
@@ -56,14 +58,23 @@ struct BwdSmem {
 // NPC = 8 specialises the common geometry (8 state-pair slots, one channel group, 8 warps) so
 // that every shared-memory offset is a compile-time constant; NPC = 0 reads it from P.
 // TILED compiles the column-tile edge handling in; the common single-tile launch leaves it out.
-template <int L, int NPC, bool TILED>
-__global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
+// WS (with NPC = 8, not TILED) is the warp-specialised form: warps 0-7 compute as before and
+// write out the previous step, warps 8-11 load and transform (softplus, sigmoid) the tiles of
+// the NEXT step into a second tile set meanwhile, so that the staging - global-memory latency
+// and the transcendental chains - no longer sits between two compute phases.  The two groups
+// meet on mbarriers (tile set full / tile set free), every wait bounded.  The staging warps
+// give most of their registers to the compute warps (setmaxnreg).
+constexpr int WS_COMPUTE = 256, WS_STAGE = 128, WS_REGS_COMPUTE = 232, WS_REGS_STAGE = 40;
+template <int L, int NPC, bool TILED, bool WS>
+__global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) bwd_kernel(const Dev P) {
+    static_assert(!WS || (NPC == 8 && !TILED), "the warp-specialised form covers the common geometry only");
     using S = BwdSmem<L>;
     constexpr int Wp = S::Wp, CW = S::CW, T4 = Wp / 4, CS4 = S::CS4, CS6 = S::CS6, L4 = 4 * L, L2 = 2 * L;
     constexpr int NU = CW >= 8 ? 1 : 8 / CW;  // columns of a strip owned by a lane after the channel sum
     extern __shared__ __align__(16) float smem[];
     const int NPp = NPC ? NPC : P.NPp, CG = NPC ? MAX_WARPS / NPC : P.CG, CP = CG * CW, CT = P.CT;
     const int nw = NPp * CG, nthr = nw * 32;
+    // staged tiles of the step being computed; WS alternates between two sets
     float *su = smem + S::u(CP), *sg = smem + S::g(CP), *ssig = smem + S::sig(CP), *sdl = smem + S::dl(CP);
     float *spdu = smem + S::pdu(CP), *spdd = smem + S::pdd(CP, nw);
     float2 *str = reinterpret_cast<float2 *>(smem + S::tr(CP, nw));
@@ -155,9 +166,93 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
             }
         }
     };
-    if (bulk && tid == 0) { mbar_init(bars, 1); mbar_init(bars + 1, 1); mbar_init_fence(); }
+    // WS: second tile set and the full / free mbarriers of the two sets
+    float *set1 = reinterpret_cast<float *>(bars + 4);
+    uint64_t *full = bars, *freeb = bars + 2;
+    if (WS) {
+        if (tid == 0) {
+            mbar_init(full, WS_STAGE); mbar_init(full + 1, WS_STAGE);
+            mbar_init(freeb, WS_COMPUTE); mbar_init(freeb + 1, WS_COMPUTE);
+            mbar_init_fence();
+        }
+    } else if (bulk && tid == 0) {
+        mbar_init(bars, 1); mbar_init(bars + 1, 1); mbar_init_fence();
+    }
     __syncthreads();  // barriers initialised, parameter copies and zeroed tiles visible
-    if (bulk && warp == 0 && steps > 0) issue(0);
+    if (!WS && bulk && warp == 0 && steps > 0) issue(0);
+
+    // loads and transforms the tiles of step k (row block kblk, channels kch0..) into the set at `base`
+    auto stage_step = [&](int k, float *base, const unsigned char *raw_k, int t0, int nt) {
+        float *tu = base + S::u(CP), *tg = base + S::g(CP), *tsig = base + S::sig(CP), *tdl = base + S::dl(CP);
+        const int kblk = nblk - 1 - k / npass, kch0 = (k % npass) * CP;
+        const int kr0 = kblk * RB, knr = k < steps ? min(RB, H - kr0) : 0;
+        const int lo = max(kr0 - 1, 0);
+        const unsigned char *raw_u = raw_k, *raw_g = raw_u + (size_t)CP * RB * W * es;
+        const unsigned char *raw_dl = raw_g + (size_t)CP * RB * W * eso;
+        for (int it = t0; it < CP * RB * T4; it += nt) {
+            const int t = it % T4, rr = (it / T4) % RB, sc = it / (T4 * RB);
+            const int c = 4 * t, o4 = sc * CS4 + rr * Wp + pos4<L>(t);
+            float4 uv = make_float4(0.f, 0.f, 0.f, 0.f), gv = uv, xv = uv, sv = uv;
+            if (rr < knr && kch0 + sc < nch && c < W) {
+                const int sd = dbase + kch0 + sc, r = kr0 + rr, sdd = sd / P.drep;
+                if (!WS && bulk) {
+                    uv = lds4(raw_u, (sc * RB + rr) * W + c, P.io_dt);
+                    gv = lds4(raw_g, (sc * RB + rr) * W + c, P.out_dt);
+                    xv = lds4(raw_dl, (sc * (RB + 2) + (r - lo)) * W + c, P.io_dt);
+                } else {
+                    uv = ld4d(P.u, (int64_t)b * P.u_bs + (int64_t)(sd - ush) * P.u_ds, P.u_hs, r, c, H, W, fh, fw,
+                              P.io_dt, P.vec & VEC_U);
+                    gv = ld4d(P.out, (int64_t)b * P.o_bs + (int64_t)(sd - gsh) * P.o_ds, P.o_hs, r, c, H, W, fh, fw,
+                              P.out_dt, P.vec & VEC_OUT);
+                    xv = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, r, c, H, W, fh, fw,
+                              P.io_dt, P.vec & VEC_DELTA);
+                }
+                soft4(xv, sv, spar[2 * (kch0 + sc) + 1], P.softplus, W - c);
+            }
+            *reinterpret_cast<float4 *>(tu + o4) = uv;
+            *reinterpret_cast<float4 *>(tg + o4) = gv;
+            *reinterpret_cast<float4 *>(tsig + o4) = sv;
+            *reinterpret_cast<float4 *>(tdl + sc * CS6 + (rr + 1) * Wp + pos4<L>(t)) = xv;
+        }
+        if (knr > 0) {  // delta of the rows just above and just below the block, one column per item
+            for (int it = t0; it < CP * 2 * Wp; it += nt) {
+                const int c = it % Wp, which = (it / Wp) & 1, sc = it / (Wp * 2);
+                const int rr = which ? RB + 1 : 0, r = kr0 + rr - 1;
+                float x = 0.f;
+                if (r >= 0 && r < H && rr - 1 <= knr && kch0 + sc < nch && c < W) {
+                    const int sdd = (dbase + kch0 + sc) / P.drep;
+                    if (!WS && bulk)
+                        x = lds1(raw_dl, (sc * (RB + 2) + (r - lo)) * W + c, P.io_dt);
+                    else
+                        x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds +
+                                                 (int64_t)(fh ? H - 1 - r : r) * P.dl_hs + (fw ? W - 1 - c : c), P.io_dt);
+                    x += spar[2 * (kch0 + sc) + 1];
+                    if (P.softplus) x = softplus20(x);
+                }
+                tdl[sc * CS6 + rr * Wp + pos1<L>(c)] = x;
+            }
+        }
+    };
+
+    if constexpr (WS) {
+        if (warp >= WS_COMPUTE / 32) {  // ---- staging warps ----
+            asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WS_REGS_STAGE));
+            for (int k = 0; k < steps; ++k) {
+                const int set = k & 1;
+                if (k >= 2 && !mbar_wait_bounded(freeb + set, ((k >> 1) - 1) & 1)) {
+                    atomicOr(P.status, ERR_STAGE_TIMEOUT);  // the compute warps give up on `full` in turn
+                    return;
+                }
+                stage_step(k, set ? set1 : smem, nullptr, tid - WS_COMPUTE, WS_STAGE);
+                mbar_arrive(full + set);  // release: the tile writes above are visible to the waiters
+            }
+            return;
+        }
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(WS_REGS_COMPUTE));
+    }
+    auto cta_sync = [&]() {
+        if constexpr (WS) group_sync(1, WS_COMPUTE); else __syncthreads();
+    };
     for (int step = 0; step <= steps; ++step) {
         const int blk = nblk - 1 - step / npass, pass = step % npass;  // bottom-up
         const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
@@ -182,7 +277,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
             }
         }
         // ---- phase A: write out the previous step, stage this one -------------------
-        if (bulk) {
+        if (!WS && bulk) {
             if (warp == 0 && step + 1 < steps) issue(step + 1);   // lands while this step computes
             bool ok = nr == 0 || mbar_wait_bounded(bars + (step & 1), (step >> 1) & 1);
             if (__syncthreads_or(!ok)) {  // give up: flag it, drain the other stage, leave
@@ -192,96 +287,59 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
             }
         }
         {
-            const unsigned char *raw_u = raw + (size_t)(step & 1) * stage_bytes;
-            const unsigned char *raw_g = raw_u + (size_t)CP * RB * W * es;
-            const unsigned char *raw_dl = raw_g + (size_t)CP * RB * W * eso;
-            const int lo = max(r0 - 1, 0);
-            const int items = CP * RB * T4;
+            // tiles of the previous step (being written out) and of this one
+            float *prev = WS && (pstep & 1) ? set1 : smem, *cur = WS && (step & 1) ? set1 : smem;
+            const float *psu = prev + S::u(CP), *psg = prev + S::g(CP), *pssig = prev + S::sig(CP);
+            su = cur + S::u(CP); sg = cur + S::g(CP); ssig = cur + S::sig(CP); sdl = cur + S::dl(CP);
+            const int items = pnr > 0 ? CP * RB * T4 : 0;
             for (int it = tid; it < items; it += nthr) {
                 const int t = it % T4, rr = (it / T4) % RB, sc = it / (T4 * RB);
                 const int c = 4 * t, o4 = sc * CS4 + rr * Wp + pos4<L>(t);
-                if (pnr > 0) {  // uniform
-                    float dDp = 0.f, dbp = 0.f;
-                    if (rr < pnr && pch0 + sc < nch) {
-                        const int sd = dbase + pch0 + sc;
-                        const int scg = sc / CW, scl = sc % CW;
-                        float4 a1 = make_float4(0.f, 0.f, 0.f, 0.f), a2 = a1;
-                        for (int q = 0; q < NPp; ++q) {
-                            const int o = ((scg * NPp + q) * CW + scl) * CS4 + rr * Wp + pos4<L>(t);
-                            const float4 v1 = *reinterpret_cast<const float4 *>(spdu + o);
-                            const float4 v2 = *reinterpret_cast<const float4 *>(spdd + o);
-                            a1.x += v1.x; a1.y += v1.y; a1.z += v1.z; a1.w += v1.w;
-                            a2.x += v2.x; a2.y += v2.y; a2.z += v2.z; a2.w += v2.w;
-                        }
-                        const float4 gv = *reinterpret_cast<const float4 *>(sg + o4);
-                        const float4 uv = *reinterpret_cast<const float4 *>(su + o4);
-                        const float4 sv = *reinterpret_cast<const float4 *>(ssig + o4);
-                        const float Dv = spar[2 * (pch0 + sc)];
-                        a1.x = fmaf(Dv, gv.x, a1.x); a1.y = fmaf(Dv, gv.y, a1.y);
-                        a1.z = fmaf(Dv, gv.z, a1.z); a1.w = fmaf(Dv, gv.w, a1.w);
-                        a2.x *= sv.x; a2.y *= sv.y; a2.z *= sv.z; a2.w *= sv.w;
-                        const int64_t o = ((int64_t)b * P.dim + sd) * H * P.Wout;
-                        st4d(P.du, o, P.Wout, pr0 + rr, c, H, W, fh, fw, P.io_dt, P.vec & VEC_DU, a1);
-                        st4d(P.ddelta, o, P.Wout, pr0 + rr, c, H, W, fh, fw, P.io_dt, P.vec & VEC_DU, a2);
-                        // columns past the image carry g = 0 and ddl = 0
-                        dDp = gv.x * uv.x + gv.y * uv.y + gv.z * uv.z + gv.w * uv.w;
-                        dbp = a2.x + a2.y + a2.z + a2.w;
+                float dDp = 0.f, dbp = 0.f;
+                if (rr < pnr && pch0 + sc < nch) {
+                    const int sd = dbase + pch0 + sc;
+                    const int scg = sc / CW, scl = sc % CW;
+                    float4 a1 = make_float4(0.f, 0.f, 0.f, 0.f), a2 = a1;
+                    for (int q = 0; q < NPp; ++q) {
+                        const int o = ((scg * NPp + q) * CW + scl) * CS4 + rr * Wp + pos4<L>(t);
+                        const float4 v1 = *reinterpret_cast<const float4 *>(spdu + o);
+                        const float4 v2 = *reinterpret_cast<const float4 *>(spdd + o);
+                        a1.x += v1.x; a1.y += v1.y; a1.z += v1.z; a1.w += v1.w;
+                        a2.x += v2.x; a2.y += v2.y; a2.z += v2.z; a2.w += v2.w;
                     }
-                    // the RB*T4 items of a channel are consecutive: segmented warp sum
-                    constexpr int SEG = S::SEG;
+                    const float4 gv = *reinterpret_cast<const float4 *>(psg + o4);
+                    const float4 uv = *reinterpret_cast<const float4 *>(psu + o4);
+                    const float4 sv = *reinterpret_cast<const float4 *>(pssig + o4);
+                    const float Dv = spar[2 * (pch0 + sc)];
+                    a1.x = fmaf(Dv, gv.x, a1.x); a1.y = fmaf(Dv, gv.y, a1.y);
+                    a1.z = fmaf(Dv, gv.z, a1.z); a1.w = fmaf(Dv, gv.w, a1.w);
+                    a2.x *= sv.x; a2.y *= sv.y; a2.z *= sv.z; a2.w *= sv.w;
+                    const int64_t o = ((int64_t)b * P.dim + sd) * H * P.Wout;
+                    st4d(P.du, o, P.Wout, pr0 + rr, c, H, W, fh, fw, P.io_dt, P.vec & VEC_DU, a1);
+                    st4d(P.ddelta, o, P.Wout, pr0 + rr, c, H, W, fh, fw, P.io_dt, P.vec & VEC_DU, a2);
+                    // columns past the image carry g = 0 and ddl = 0
+                    dDp = gv.x * uv.x + gv.y * uv.y + gv.z * uv.z + gv.w * uv.w;
+                    dbp = a2.x + a2.y + a2.z + a2.w;
+                }
+                // the RB*T4 items of a channel are consecutive: segmented warp sum
+                constexpr int SEG = S::SEG;
 #pragma unroll
-                    for (int off = SEG / 2; off; off >>= 1) {
-                        dDp += __shfl_xor_sync(0xffffffffu, dDp, off);
-                        dbp += __shfl_xor_sync(0xffffffffu, dbp, off);
-                    }
-                    if ((lane & (SEG - 1)) == 0 && pch0 + sc < nch) {  // the slot's only writer
-                        float *q = sred + ((pch0 + sc) * S::NSEG + (it % (RB * T4)) / SEG) * 2;
-                        q[0] += dDp;
-                        q[1] += dbp;
-                    }
+                for (int off = SEG / 2; off; off >>= 1) {
+                    dDp += __shfl_xor_sync(0xffffffffu, dDp, off);
+                    dbp += __shfl_xor_sync(0xffffffffu, dbp, off);
                 }
-                // stage this step's u, dout, delta (row rr) for the same item: the thread that
-                // read the old tile entries above is the one that replaces them
-                float4 uv = make_float4(0.f, 0.f, 0.f, 0.f), gv = uv, xv = uv, sv = uv;
-                if (rr < nr && ch0 + sc < nch && c < W) {
-                    const int sd = dbase + ch0 + sc, r = r0 + rr, sdd = sd / P.drep;
-                    if (bulk) {
-                        uv = lds4(raw_u, (sc * RB + rr) * W + c, P.io_dt);
-                        gv = lds4(raw_g, (sc * RB + rr) * W + c, P.out_dt);
-                        xv = lds4(raw_dl, (sc * (RB + 2) + (r - lo)) * W + c, P.io_dt);
-                    } else {
-                        uv = ld4d(P.u, (int64_t)b * P.u_bs + (int64_t)(sd - ush) * P.u_ds, P.u_hs, r, c, H, W, fh, fw,
-                                  P.io_dt, P.vec & VEC_U);
-                        gv = ld4d(P.out, (int64_t)b * P.o_bs + (int64_t)(sd - gsh) * P.o_ds, P.o_hs, r, c, H, W, fh, fw,
-                                  P.out_dt, P.vec & VEC_OUT);
-                        xv = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, r, c, H, W, fh, fw,
-                                  P.io_dt, P.vec & VEC_DELTA);
-                    }
-                    soft4(xv, sv, spar[2 * (ch0 + sc) + 1], P.softplus, W - c);
+                if ((lane & (SEG - 1)) == 0 && pch0 + sc < nch) {  // the slot's only writer
+                    float *q = sred + ((pch0 + sc) * S::NSEG + (it % (RB * T4)) / SEG) * 2;
+                    q[0] += dDp;
+                    q[1] += dbp;
                 }
-                *reinterpret_cast<float4 *>(su + o4) = uv;
-                *reinterpret_cast<float4 *>(sg + o4) = gv;
-                *reinterpret_cast<float4 *>(ssig + o4) = sv;
-                *reinterpret_cast<float4 *>(sdl + sc * CS6 + (rr + 1) * Wp + pos4<L>(t)) = xv;
             }
-            if (nr > 0) {  // delta of the rows just above and just below the block, one column per item
-                const int itemsH = CP * 2 * Wp;
-                for (int it = tid; it < itemsH; it += nthr) {
-                    const int c = it % Wp, which = (it / Wp) & 1, sc = it / (Wp * 2);
-                    const int rr = which ? RB + 1 : 0, r = r0 + rr - 1;
-                    float x = 0.f;
-                    if (r >= 0 && r < H && rr - 1 <= nr && ch0 + sc < nch && c < W) {
-                        const int sdd = (dbase + ch0 + sc) / P.drep;
-                        if (bulk)
-                            x = lds1(raw_dl, (sc * (RB + 2) + (r - lo)) * W + c, P.io_dt);
-                        else
-                            x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds +
-                                                     (int64_t)(fh ? H - 1 - r : r) * P.dl_hs + (fw ? W - 1 - c : c), P.io_dt);
-                        x += spar[2 * (ch0 + sc) + 1];
-                        if (P.softplus) x = softplus20(x);
-                    }
-                    sdl[sc * CS6 + rr * Wp + pos1<L>(c)] = x;
-                }
+            if constexpr (WS) {
+                // the previous step's tile set may be refilled by the staging warps from here on
+                if (step > 0) mbar_arrive(freeb + (pstep & 1));
+            } else {
+                // every thread replaces the tile entries it has just read (same item mapping)
+                stage_step(step, smem, raw + (size_t)(step & 1) * stage_bytes, tid, nthr);
             }
             // a row block is complete when its last pass has been written out
             if (acc_on && pnr > 0 && ppass == npass - 1) {
@@ -305,7 +363,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                     }
                 }
             }
-            if (nr > 0 && pass == 0) stage_BC<L>(P, b, g_, r0, nr, sB, sC, fh, fw);
+            if (nr > 0 && pass == 0) stage_BC<L>(P, b, g_, r0, nr, sB, sC, fh, fw, tid, nthr);
             if (nr > 0 && (has_left || has_right)) {
                 for (int it = tid; it < CP * NPp * (RB + 1); it += nthr) {
                     const int k = it % (RB + 1), q = (it / (RB + 1)) % NPp, sc = it / ((RB + 1) * NPp);
@@ -339,7 +397,14 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                 }
             }
         }
-        __syncthreads();
+        if constexpr (WS) {  // this step's tiles have to be complete
+            const bool ok = nr == 0 || mbar_wait_bounded(full + (step & 1), (step >> 1) & 1);
+            if (group_or(2, WS_COMPUTE, !ok)) {  // the staging warps stopped (they flagged why): leave together
+                if (tid == 0) atomicOr(P.status, ERR_STAGE_TIMEOUT);
+                return;
+            }
+        }
+        cta_sync();
         if (nr == 0) break;
 
         // ---- compute ---------------------------------------------------------------------
@@ -635,7 +700,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
                 q[0] += dAacc.x; q[1] += dAacc.y;
             }
         }
-        __syncthreads();
+        cta_sync();
     }
 
     // ---- per-channel parameter gradients ---------------------------------------
@@ -646,7 +711,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
         for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
         if (lane == 0) sdecay[warp] = v;
     }
-    __syncthreads();
+    cta_sync();
     for (int i = tid; i < nch * 2 * NPp; i += nthr) {
         const int sc = i / (2 * NPp), n = i % (2 * NPp);
         if (n < N) atomicAdd(P.dA + (int64_t)(dbase + sc) * N + n, sdA[i]);
@@ -665,53 +730,62 @@ __global__ void __launch_bounds__(MAX_THREADS, 1) bwd_kernel(const Dev P) {
     }
 }
 
-size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk, bool tiled) {
+template <int L>
+static size_t smem_floats(int CP, int NPp, int CT, int nw, bool acc, bool ws) {
+    return (size_t)((BwdSmem<L>::total(CP, NPp, CT, nw, acc) + 3) & ~3) + (ws ? BwdSmem<L>::set_floats(CP) : 0);
+}
+
+size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk, bool tiled, bool ws) {
     const int nw = CG * NPp;
-    const int CPh = CG * (32 / L);
-    const size_t extra = (size_t)(tiled ? 2 * CPh * NPp * (RB + 1) * 4 + CPh * 12 : 0) * 4 + 16 +
-                         (bulk ? 2 * (size_t)CPh * W * (RB * es + RB * eso + (RB + 2) * es) : 0);
     const int CP = CG * (32 / L);
+    // after the tiles: tile-edge areas (tiled kernels), the mbarriers, then either the raw row
+    // blocks of the bulk copies (two stages) or, warp-specialised, the second tile set
+    const size_t extra = (size_t)(tiled ? 2 * CP * NPp * (RB + 1) * 4 + CP * 12 : 0) * 4 + (ws ? 32 : 16) +
+                         (bulk && !ws ? 2 * (size_t)CP * W * (RB * es + RB * eso + (RB + 2) * es) : 0);
     switch (L) {
-        case 1: return (size_t)((BwdSmem<1>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
-        case 2: return (size_t)((BwdSmem<2>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
-        case 4: return (size_t)((BwdSmem<4>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
-        case 8: return (size_t)((BwdSmem<8>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
-        case 16: return (size_t)((BwdSmem<16>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
-        default: return (size_t)((BwdSmem<32>::total(CP, NPp, CT, nw, acc) + 3) & ~3) * 4 + extra;
+        case 1: return smem_floats<1>(CP, NPp, CT, nw, acc, ws) * 4 + extra;
+        case 2: return smem_floats<2>(CP, NPp, CT, nw, acc, ws) * 4 + extra;
+        case 4: return smem_floats<4>(CP, NPp, CT, nw, acc, ws) * 4 + extra;
+        case 8: return smem_floats<8>(CP, NPp, CT, nw, acc, ws) * 4 + extra;
+        case 16: return smem_floats<16>(CP, NPp, CT, nw, acc, ws) * 4 + extra;
+        default: return smem_floats<32>(CP, NPp, CT, nw, acc, ws) * 4 + extra;
     }
 }
 
-template <int L, int NPC, bool TILED>
+template <int L, int NPC, bool TILED, bool WS>
 static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) {
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(bwd_kernel<L, NPC, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(bwd_kernel<L, NPC, TILED, WS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    bwd_kernel<L, NPC, TILED><<<grid, 32 * P.CG * P.NPp, smem, st>>>(P);
+    bwd_kernel<L, NPC, TILED, WS><<<grid, WS ? WS_COMPUTE + WS_STAGE : 32 * P.CG * P.NPp, smem, st>>>(P);
     return cudaGetLastError();
 }
 
-cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st) {
+template <int L>
+static cudaError_t launch_L(const Dev &P, int grid, size_t smem, cudaStream_t st) {
     const bool spec = P.NPp == 8 && P.CG == 1, tiled = P.tile_left || P.tile_right;
+    if (P.ws) return launch<L, 8, false, true>(P, grid, smem, st);
+    return tiled ? (spec ? launch<L, 8, true, false>(P, grid, smem, st) : launch<L, 0, true, false>(P, grid, smem, st))
+                 : (spec ? launch<L, 8, false, false>(P, grid, smem, st) : launch<L, 0, false, false>(P, grid, smem, st));
+}
+
+cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st) {
+    const bool tiled = P.tile_left || P.tile_right;
+    if (P.ws && (P.NPp != 8 || P.CG != 1 || tiled)) return cudaErrorInvalidValue;
     const size_t smem = bwd_smem_bytes(L, P.CG, P.NPp, P.CT, P.acc_dbc != 0, P.W, P.io_dt == CS2D_F32 ? 4 : 2,
-                                       P.out_dt == CS2D_F32 ? 4 : 2, P.bulk != 0, tiled);
+                                       P.out_dt == CS2D_F32 ? 4 : 2, P.bulk != 0, tiled, P.ws != 0);
     switch (L) {
-        case 1: return tiled ? (spec ? launch<1, 8, true>(P, grid, smem, st) : launch<1, 0, true>(P, grid, smem, st))
-                             : (spec ? launch<1, 8, false>(P, grid, smem, st) : launch<1, 0, false>(P, grid, smem, st));
-        case 2: return tiled ? (spec ? launch<2, 8, true>(P, grid, smem, st) : launch<2, 0, true>(P, grid, smem, st))
-                             : (spec ? launch<2, 8, false>(P, grid, smem, st) : launch<2, 0, false>(P, grid, smem, st));
-        case 4: return tiled ? (spec ? launch<4, 8, true>(P, grid, smem, st) : launch<4, 0, true>(P, grid, smem, st))
-                             : (spec ? launch<4, 8, false>(P, grid, smem, st) : launch<4, 0, false>(P, grid, smem, st));
-        case 8: return tiled ? (spec ? launch<8, 8, true>(P, grid, smem, st) : launch<8, 0, true>(P, grid, smem, st))
-                             : (spec ? launch<8, 8, false>(P, grid, smem, st) : launch<8, 0, false>(P, grid, smem, st));
-        case 16: return tiled ? (spec ? launch<16, 8, true>(P, grid, smem, st) : launch<16, 0, true>(P, grid, smem, st))
-                             : (spec ? launch<16, 8, false>(P, grid, smem, st) : launch<16, 0, false>(P, grid, smem, st));
-        case 32: return tiled ? (spec ? launch<32, 8, true>(P, grid, smem, st) : launch<32, 0, true>(P, grid, smem, st))
-                             : (spec ? launch<32, 8, false>(P, grid, smem, st) : launch<32, 0, false>(P, grid, smem, st));
+        case 1: return launch_L<1>(P, grid, smem, st);
+        case 2: return launch_L<2>(P, grid, smem, st);
+        case 4: return launch_L<4>(P, grid, smem, st);
+        case 8: return launch_L<8>(P, grid, smem, st);
+        case 16: return launch_L<16>(P, grid, smem, st);
+        case 32: return launch_L<32>(P, grid, smem, st);
     }
     return cudaErrorInvalidValue;
 }

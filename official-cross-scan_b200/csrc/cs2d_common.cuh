@@ -60,6 +60,7 @@ struct Dev {
     unsigned flip_h, flip_w;
     int u_shared;
     int vec;    // bit i set: tensor i may be accessed 4 elements at a time
+    int ws;     // backward: 1 = warp-specialised kernel (8 compute warps + 4 staging warps)
     int bulk;   // 1: row blocks of u, delta (and dout) are fetched with bulk asynchronous copies
                 //    (rows are 16-byte multiples, planes contiguous and aligned); 0: plain loads
     int *status; // device status word (see ERR_*)
@@ -89,7 +90,7 @@ enum { VEC_U = 1, VEC_DELTA = 2, VEC_B = 4, VEC_C = 8, VEC_OUT = 16, VEC_DU = 32
 // Device-side status word of the library (0 = fine).  A kernel that gives up on a
 // bounded wait records why here instead of spinning; the host reads and clears it
 // through cs2d_device_status().
-enum { ERR_BULK_COPY_TIMEOUT = 1 };
+enum { ERR_BULK_COPY_TIMEOUT = 1, ERR_STAGE_TIMEOUT = 2 };
 
 // ---- packed fp32x2 helpers -------------------------------------------------
 __device__ __forceinline__ float2 f2(float x, float y) { return make_float2(x, y); }
@@ -193,6 +194,21 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
                      smem_addr(dst)),
                  "l"(src), "r"(bytes), "r"(smem_addr(bar))
                  : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+// Barrier / OR-reduction among `n` threads of the CTA (a multiple of 32) on hardware barrier `id`
+// (1..15; 0 is __syncthreads).  Used where only some of the CTA's warps take part.
+__device__ __forceinline__ void group_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+__device__ __forceinline__ bool group_or(int id, int n, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, %2, %3, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)pred), "r"(id), "r"(n)
+        : "memory");
+    return r != 0;
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
@@ -497,11 +513,10 @@ __device__ __forceinline__ void row_forward(int j, const float (&dl)[STRIP], con
 // B and C of one row block for every state pair: sB/sC[NPp][RB][Wp] float2.
 template <int L>
 __device__ __forceinline__ void stage_BC(const Dev &P, int b, int g, int r0, int nr, float2 *sB, float2 *sC,
-                                         bool fh, bool fw) {
+                                         bool fh, bool fw, int tid, int nthr) {
     constexpr int Wp = L * STRIP, T4 = Wp / 4;
     const int items = P.NPp * RB * T4;
-    const int nthr = blockDim.x;
-    for (int it = threadIdx.x; it < items; it += nthr) {
+    for (int it = tid; it < items; it += nthr) {
         const int t = it % T4, rr = (it / T4) % RB, sp = it / (T4 * RB);
         const int c = 4 * t, n0 = 2 * sp;
         float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0, c0 = b0, c1 = b0;

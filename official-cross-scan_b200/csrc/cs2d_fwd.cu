@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                     }
                     sdl[sc * CS5 + pos1<L>(c)] = x;
                 }
-                if (pass == 0) stage_BC<L>(P, b, g, r0, nr, sB, sC, fh, fw);
+                if (pass == 0) stage_BC<L>(P, b, g, r0, nr, sB, sC, fh, fw, tid, nthr);
                 if (has_left) {  // column left of this tile: h, s written by the tile to the left; delta
                     for (int it = tid; it < CP * NPp * (RB + 1); it += nthr) {
                         const int k = it % (RB + 1), q = (it / (RB + 1)) % NPp, sc = it / ((RB + 1) * NPp);
