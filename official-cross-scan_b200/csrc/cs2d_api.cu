@@ -12,7 +12,7 @@
 namespace cs2d {
 cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st);
 cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st);
-size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk, int CT, bool tiled);
+size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk, int CT, bool tiled, bool ws);
 size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk, bool tiled, bool ws);
 static __device__ int g_cs2d_status = 0;  // see ERR_* in cs2d_common.cuh
 
@@ -59,7 +59,7 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, 
     // per-channel tiles small enough that the shared memory fits.
     int CG = MAX_WARPS / NPp;
     while (CG > 1 && (backward ? bwd_smem_bytes(L, CG, NPp, CG * (32 / L), false, W, es, eso, false, tiled, false) > kMaxSmem
-                               : 2 * (fwd_smem_bytes(L, CG, NPp, W, es, false, CG * (32 / L), tiled) + kCtaReserve) > kSmSmem))
+                               : 2 * (fwd_smem_bytes(L, CG, NPp, W, es, false, CG * (32 / L), tiled, false) + kCtaReserve) > kSmSmem))
         CG >>= 1;
     const int CP = CG * (32 / L);
     const int pmax = (dpg + CP - 1) / CP;  // passes that cover a whole group
@@ -100,10 +100,17 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, 
         }
     } else {
         // keep two CTAs per SM
-        if (2 * (fwd_smem_bytes(L, CG, NPp, W, es, g->bulk, npass * CP, tiled) + kCtaReserve) > kSmSmem) g->bulk = 0;
-        if (fwd_smem_bytes(L, CG, NPp, W, es, false, npass * CP, tiled) > kMaxSmem)
+        if (2 * (fwd_smem_bytes(L, CG, NPp, W, es, g->bulk, npass * CP, tiled, false) + kCtaReserve) > kSmSmem) g->bulk = 0;
+        if (fwd_smem_bytes(L, CG, NPp, W, es, false, npass * CP, tiled, false) > kMaxSmem)
             return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d with dstate=%d needs more shared memory than one SM has",
                         p->ncols, p->dstate);
+        // warp-specialised like the backward, as long as two CTAs still share an SM
+        static const bool fws_off = [] { const char *e = getenv("CS2D_FWD_WS"); return e && e[0] == '0'; }();
+        if (!fws_off && NPp == 8 && CG == 1 && !tiled &&
+            2 * (fwd_smem_bytes(L, CG, NPp, W, es, false, npass * CP, false, true) + kCtaReserve) <= kSmSmem) {
+            g->ws = 1;
+            g->bulk = 0;
+        }
     }
     g->L = L; g->NPp = NPp; g->CG = CG; g->CP = CP; g->npass = npass; g->CT = npass * CP;
     g->ntiles = (dpg + g->CT - 1) / g->CT;

@@ -47,13 +47,22 @@ struct FwdSmem {
         return bars(CP, NPp, nw, tiled, CT) + 4;
     }
     static __host__ __device__ constexpr int stage_bytes(int CP, int W, int es) { return CP * (2 * RB + 1) * W * es; }
+    // one set of staged per-channel tiles (u, delta), rounded to 16 bytes
+    static __host__ __device__ constexpr int set_floats(int CP) { return (y(CP) + 3) & ~3; }
 };
 
 // NPC = 8 specialises the common geometry (8 state-pair slots, one channel group, 8 warps) so
 // that every shared-memory offset is a compile-time constant; NPC = 0 reads it from P.
 // TILED compiles the column-tile edge handling in; the common single-tile launch leaves it out.
-template <int L, int NPC, bool TILED>
-__global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
+// WS (with NPC = 8, not TILED) is the warp-specialised form: warps 0-7 compute and write out the
+// previous step, warps 8-11 load and transform (softplus) the tiles of the NEXT step into a
+// second tile set meanwhile; the groups meet on mbarriers (tile set full / free), every wait
+// bounded, and the staging warps give registers to the compute warps (setmaxnreg).  Two such
+// CTAs share an SM: 2 * (256 * 104 + 128 * 32) registers.
+constexpr int FWS_COMPUTE = 256, FWS_STAGE = 128, FWS_REGS_COMPUTE = 104, FWS_REGS_STAGE = 32;
+template <int L, int NPC, bool TILED, bool WS>
+__global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2) fwd_kernel(const Dev P) {
+    static_assert(!WS || (NPC == 8 && !TILED), "the warp-specialised form covers the common geometry only");
     using S = FwdSmem<L>;
     constexpr int Wp = S::Wp, CW = S::CW, T4 = Wp / 4, CS4 = S::CS4, CS5 = S::CS5, L4 = 4 * L, L2 = 2 * L;
     extern __shared__ __align__(16) float smem[];
@@ -129,9 +138,93 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
             }
         }
     };
-    if (bulk && tid == 0) { mbar_init(bars, 1); mbar_init(bars + 1, 1); mbar_init_fence(); }
+    // WS: second tile set and the full / free mbarriers of the two sets
+    float *set1 = reinterpret_cast<float *>(bars + 4);
+    uint64_t *full = bars, *freeb = bars + 2;
+    if (WS) {
+        if (tid == 0) {
+            mbar_init(full, FWS_STAGE); mbar_init(full + 1, FWS_STAGE);
+            mbar_init(freeb, FWS_COMPUTE); mbar_init(freeb + 1, FWS_COMPUTE);
+            mbar_init_fence();
+        }
+    } else if (bulk && tid == 0) {
+        mbar_init(bars, 1); mbar_init(bars + 1, 1); mbar_init_fence();
+    }
     __syncthreads();  // barriers initialised, parameter copies and zeroed tiles visible
-    if (bulk && warp == 0 && steps > 0) issue(0);
+    if (!WS && bulk && warp == 0 && steps > 0) issue(0);
+
+    // loads and transforms u and delta of step k into the tile set at `base`
+    auto stage_step = [&](int k, float *base, const unsigned char *raw_k, int t0, int nt) {
+        float *tu = base + S::u(CP), *tdl = base + S::dl(CP);
+        const int kblk = k / P.npass, kch0 = (k % P.npass) * CP;
+        const int kr0 = kblk * RB, knr = k < steps ? min(RB, H - kr0) : 0;
+        const int lo = max(kr0 - 1, 0);
+        const unsigned char *raw_u = raw_k, *raw_dl = raw_u + (size_t)CP * RB * W * es;
+        for (int it = t0; it < CP * RB * T4; it += nt) {
+            const int t = it % T4, rr = (it / T4) % RB, sc = it / (T4 * RB);
+            const int c = 4 * t, o4 = sc * CS4 + rr * Wp + pos4<L>(t);
+            float4 uv = make_float4(0.f, 0.f, 0.f, 0.f), x = uv;
+            if (rr < knr && kch0 + sc < nch && c < W) {
+                const int sdd = (dbase + kch0 + sc) / P.drep;
+                if (!WS && bulk) {
+                    uv = lds4(raw_u, (sc * RB + rr) * W + c, P.io_dt);
+                    x = lds4(raw_dl, (sc * (RB + 1) + (kr0 + rr - lo)) * W + c, P.io_dt);
+                } else {
+                    uv = ld4d(P.u, (int64_t)b * P.u_bs + (int64_t)(dbase + kch0 + sc - ush) * P.u_ds, P.u_hs, kr0 + rr, c,
+                              H, W, fh, fw, P.io_dt, P.vec & VEC_U);
+                    x = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, kr0 + rr, c, H, W, fh, fw,
+                             P.io_dt, P.vec & VEC_DELTA);
+                }
+                const float bv = spar[2 * (kch0 + sc) + 1];
+                x.x += bv; x.y += bv; x.z += bv; x.w += bv;
+                if (P.softplus) {
+                    x.x = softplus20(x.x); x.y = softplus20(x.y); x.z = softplus20(x.z); x.w = softplus20(x.w);
+                }
+                const int nv = W - c;  // columns past the image keep dl = 0
+                if (nv < 4) { x.w = 0.f; if (nv < 3) x.z = 0.f; if (nv < 2) x.y = 0.f; }
+            }
+            *reinterpret_cast<float4 *>(tu + o4) = uv;
+            *reinterpret_cast<float4 *>(tdl + sc * CS5 + (rr + 1) * Wp + pos4<L>(t)) = x;
+        }
+        if (knr > 0) {
+            // delta of the row above the block, one column per item so that all warps share it
+            for (int it = t0; it < CP * Wp; it += nt) {
+                const int c = it % Wp, sc = it / Wp, r = kr0 - 1;
+                float x = 0.f;
+                if (r >= 0 && kch0 + sc < nch && c < W) {
+                    const int sdd = (dbase + kch0 + sc) / P.drep;
+                    if (!WS && bulk)
+                        x = lds1(raw_dl, sc * (RB + 1) * W + c, P.io_dt);
+                    else
+                        x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds +
+                                                 (int64_t)(fh ? H - 1 - r : r) * P.dl_hs + (fw ? W - 1 - c : c), P.io_dt);
+                    x += spar[2 * (kch0 + sc) + 1];
+                    if (P.softplus) x = softplus20(x);
+                }
+                tdl[sc * CS5 + pos1<L>(c)] = x;
+            }
+        }
+    };
+
+    if constexpr (WS) {
+        if (warp >= FWS_COMPUTE / 32) {  // ---- staging warps ----
+            asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FWS_REGS_STAGE));
+            for (int k = 0; k < steps; ++k) {
+                const int set = k & 1;
+                if (k >= 2 && !mbar_wait_bounded(freeb + set, ((k >> 1) - 1) & 1)) {
+                    atomicOr(P.status, ERR_STAGE_TIMEOUT);  // the compute warps give up on `full` in turn
+                    return;
+                }
+                stage_step(k, set ? set1 : smem, nullptr, tid - FWS_COMPUTE, FWS_STAGE);
+                mbar_arrive(full + set);  // release: the tile writes above are visible to the waiters
+            }
+            return;
+        }
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FWS_REGS_COMPUTE));
+    }
+    auto cta_sync = [&]() {
+        if constexpr (WS) group_sync(1, FWS_COMPUTE); else __syncthreads();
+    };
     for (int step = 0; step <= steps; ++step) {
         const int blk = step / P.npass, pass = step % P.npass;
         const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
@@ -148,7 +241,7 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
             for (int k = 0; k < STRIP / 2; ++k) ck_pre[k] = ok ? pk[k] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         // ---- phase A: write out the previous step, stage this one -------------------
-        if (bulk) {
+        if (!WS && bulk) {
             if (warp == 0 && step + 1 < steps) issue(step + 1);   // lands while this step computes
             bool ok = nr == 0 || mbar_wait_bounded(bars + (step & 1), (step >> 1) & 1);
             if (__syncthreads_or(!ok)) {  // give up: flag it, drain the other stage, leave
@@ -158,17 +251,18 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
             }
         }
         {
-            const unsigned char *raw_u = raw + (size_t)(step & 1) * stage_bytes;
-            const unsigned char *raw_dl = raw_u + (size_t)CP * RB * W * es;
-            const int lo = max(r0 - 1, 0);
             const int pstep = step - 1;
             const int pblk = pstep / P.npass, ppass = pstep % P.npass;
             const int pr0 = pblk * RB, pnr = step > 0 ? min(RB, H - pr0) : 0, pch0 = ppass * CP;
-            const int items = CP * RB * T4;
+            // tiles of the previous step (its u is needed for D*u) and of this one
+            float *prev = WS && (pstep & 1) ? set1 : smem, *cur = WS && (step & 1) ? set1 : smem;
+            const float *psu = prev + S::u(CP);
+            su = cur + S::u(CP); sdl = cur + S::dl(CP);
+            const int items = pnr > 0 ? CP * RB * T4 : 0;
             for (int it = tid; it < items; it += nthr) {
                 const int t = it % T4, rr = (it / T4) % RB, sc = it / (T4 * RB);
                 const int c = 4 * t, o4 = sc * CS4 + rr * Wp + pos4<L>(t);
-                if (pnr > 0 && rr < pnr && pch0 + sc < nch) {
+                if (rr < pnr && pch0 + sc < nch) {
                     const int sd = dbase + pch0 + sc;
                     const int scg = sc / CW, scl = sc % CW;
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -179,54 +273,22 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                     }
                     if (P.D) {
                         const float Dv = spar[2 * (pch0 + sc)];
-                        const float4 uv = *reinterpret_cast<const float4 *>(su + o4);
+                        const float4 uv = *reinterpret_cast<const float4 *>(psu + o4);
                         acc.x = fmaf(Dv, uv.x, acc.x); acc.y = fmaf(Dv, uv.y, acc.y);
                         acc.z = fmaf(Dv, uv.z, acc.z); acc.w = fmaf(Dv, uv.w, acc.w);
                     }
                     st4d(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds, P.o_hs, pr0 + rr, c, H, W, fh, fw, P.out_dt,
                          P.vec & VEC_OUT, acc);
                 }
-                // this step's u and delta of row rr for the same item
-                float4 uv = make_float4(0.f, 0.f, 0.f, 0.f), x = uv;
-                if (rr < nr && ch0 + sc < nch && c < W) {
-                    const int sdd = (dbase + ch0 + sc) / P.drep;
-                    if (bulk) {
-                        uv = lds4(raw_u, (sc * RB + rr) * W + c, P.io_dt);
-                        x = lds4(raw_dl, (sc * (RB + 1) + (r0 + rr - lo)) * W + c, P.io_dt);
-                    } else {
-                        uv = ld4d(P.u, (int64_t)b * P.u_bs + (int64_t)(dbase + ch0 + sc - ush) * P.u_ds, P.u_hs, r0 + rr, c,
-                                  H, W, fh, fw, P.io_dt, P.vec & VEC_U);
-                        x = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, r0 + rr, c, H, W, fh, fw,
-                                 P.io_dt, P.vec & VEC_DELTA);
-                    }
-                    const float bv = spar[2 * (ch0 + sc) + 1];
-                    x.x += bv; x.y += bv; x.z += bv; x.w += bv;
-                    if (P.softplus) {
-                        x.x = softplus20(x.x); x.y = softplus20(x.y); x.z = softplus20(x.z); x.w = softplus20(x.w);
-                    }
-                    const int nv = W - c;  // columns past the image keep dl = 0
-                    if (nv < 4) { x.w = 0.f; if (nv < 3) x.z = 0.f; if (nv < 2) x.y = 0.f; }
-                }
-                *reinterpret_cast<float4 *>(su + o4) = uv;
-                *reinterpret_cast<float4 *>(sdl + sc * CS5 + (rr + 1) * Wp + pos4<L>(t)) = x;
+            }
+            if constexpr (WS) {
+                // the previous step's tile set may be refilled by the staging warps from here on
+                if (step > 0) mbar_arrive(freeb + (pstep & 1));
+            } else {
+                // every thread replaces the tile entries it has just read (same item mapping)
+                stage_step(step, smem, raw + (size_t)(step & 1) * stage_bytes, tid, nthr);
             }
             if (nr > 0) {
-                // delta of the row above the block, one column per item so that all warps share it
-                for (int it = tid; it < CP * Wp; it += nthr) {
-                    const int c = it % Wp, sc = it / Wp, r = r0 - 1;
-                    float x = 0.f;
-                    if (r >= 0 && ch0 + sc < nch && c < W) {
-                        const int sdd = (dbase + ch0 + sc) / P.drep;
-                        if (bulk)
-                            x = lds1(raw_dl, sc * (RB + 1) * W + c, P.io_dt);
-                        else
-                            x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds +
-                                                     (int64_t)(fh ? H - 1 - r : r) * P.dl_hs + (fw ? W - 1 - c : c), P.io_dt);
-                        x += spar[2 * (ch0 + sc) + 1];
-                        if (P.softplus) x = softplus20(x);
-                    }
-                    sdl[sc * CS5 + pos1<L>(c)] = x;
-                }
                 if (pass == 0) stage_BC<L>(P, b, g, r0, nr, sB, sC, fh, fw, tid, nthr);
                 if (has_left) {  // column left of this tile: h, s written by the tile to the left; delta
                     for (int it = tid; it < CP * NPp * (RB + 1); it += nthr) {
@@ -252,7 +314,14 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                 }
             }
         }
-        __syncthreads();
+        if constexpr (WS) {  // this step's tiles have to be complete
+            const bool ok = nr == 0 || mbar_wait_bounded(full + (step & 1), (step >> 1) & 1);
+            if (group_or(2, FWS_COMPUTE, !ok)) {  // the staging warps stopped (they flagged why): leave together
+                if (tid == 0) atomicOr(P.status, ERR_STAGE_TIMEOUT);
+                return;
+            }
+        }
+        cta_sync();
         if (nr == 0) break;
 
         // ---- compute: RB rows of CP channels ----------------------------------------
@@ -317,56 +386,65 @@ __global__ void __launch_bounds__(MAX_THREADS, 2) fwd_kernel(const Dev P) {
                     pk[k] = make_float4(h_up[2 * k].x, h_up[2 * k].y, h_up[2 * k + 1].x, h_up[2 * k + 1].y);
             }
         }
-        __syncthreads();
+        cta_sync();
     }
 }
 
-size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk, int CT, bool tiled) {
+template <int L>
+static size_t smem_floats(int CP, int NPp, int nw, bool ws) {
+    return (size_t)FwdSmem<L>::total(CP, NPp, nw) + (ws ? FwdSmem<L>::set_floats(CP) : 0);
+}
+
+size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk, int CT, bool tiled, bool ws) {
     const int nw = CG * NPp;
-    const int CPh = CG * (32 / L);
-    const size_t extra = (size_t)((tiled ? CPh * NPp * (RB + 1) * 4 + CPh * 4 : 0) + ((2 * CT + 3) & ~3)) * 4 + 16 +
-                         (bulk ? 2 * (size_t)CPh * (2 * RB + 1) * W * es : 0);
     const int CP = CG * (32 / L);
+    // after the tiles: tile-edge areas (tiled kernels), the parameter copies, the mbarriers, then
+    // either the raw row blocks of the bulk copies (two stages) or, warp-specialised, the second tile set
+    const size_t extra = (size_t)((tiled ? CP * NPp * (RB + 1) * 4 + CP * 4 : 0) + ((2 * CT + 3) & ~3)) * 4 + (ws ? 32 : 16) +
+                         (bulk && !ws ? 2 * (size_t)CP * (2 * RB + 1) * W * es : 0);
     switch (L) {
-        case 1: return (size_t)FwdSmem<1>::total(CP, NPp, nw) * 4 + extra;
-        case 2: return (size_t)FwdSmem<2>::total(CP, NPp, nw) * 4 + extra;
-        case 4: return (size_t)FwdSmem<4>::total(CP, NPp, nw) * 4 + extra;
-        case 8: return (size_t)FwdSmem<8>::total(CP, NPp, nw) * 4 + extra;
-        case 16: return (size_t)FwdSmem<16>::total(CP, NPp, nw) * 4 + extra;
-        default: return (size_t)FwdSmem<32>::total(CP, NPp, nw) * 4 + extra;
+        case 1: return smem_floats<1>(CP, NPp, nw, ws) * 4 + extra;
+        case 2: return smem_floats<2>(CP, NPp, nw, ws) * 4 + extra;
+        case 4: return smem_floats<4>(CP, NPp, nw, ws) * 4 + extra;
+        case 8: return smem_floats<8>(CP, NPp, nw, ws) * 4 + extra;
+        case 16: return smem_floats<16>(CP, NPp, nw, ws) * 4 + extra;
+        default: return smem_floats<32>(CP, NPp, nw, ws) * 4 + extra;
     }
 }
 
-template <int L, int NPC, bool TILED>
+template <int L, int NPC, bool TILED, bool WS>
 static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) {
     static bool attr_done[64] = {};  // per template instance and device
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(fwd_kernel<L, NPC, TILED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(fwd_kernel<L, NPC, TILED, WS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    fwd_kernel<L, NPC, TILED><<<grid, 32 * P.CG * P.NPp, smem, st>>>(P);
+    fwd_kernel<L, NPC, TILED, WS><<<grid, WS ? FWS_COMPUTE + FWS_STAGE : 32 * P.CG * P.NPp, smem, st>>>(P);
     return cudaGetLastError();
 }
 
-cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st) {
+template <int L>
+static cudaError_t launch_L(const Dev &P, int grid, size_t smem, cudaStream_t st) {
     const bool spec = P.NPp == 8 && P.CG == 1, tiled = P.tile_left || P.tile_right;
-    const size_t smem = fwd_smem_bytes(L, P.CG, P.NPp, P.W, P.io_dt == CS2D_F32 ? 4 : 2, P.bulk != 0, P.CT, tiled);
+    if (P.ws) return launch<L, 8, false, true>(P, grid, smem, st);
+    return tiled ? (spec ? launch<L, 8, true, false>(P, grid, smem, st) : launch<L, 0, true, false>(P, grid, smem, st))
+                 : (spec ? launch<L, 8, false, false>(P, grid, smem, st) : launch<L, 0, false, false>(P, grid, smem, st));
+}
+
+cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st) {
+    const bool tiled = P.tile_left || P.tile_right;
+    if (P.ws && (P.NPp != 8 || P.CG != 1 || tiled)) return cudaErrorInvalidValue;
+    const size_t smem = fwd_smem_bytes(L, P.CG, P.NPp, P.W, P.io_dt == CS2D_F32 ? 4 : 2, P.bulk != 0, P.CT, tiled, P.ws != 0);
     switch (L) {
-        case 1: return tiled ? (spec ? launch<1, 8, true>(P, grid, smem, st) : launch<1, 0, true>(P, grid, smem, st))
-                             : (spec ? launch<1, 8, false>(P, grid, smem, st) : launch<1, 0, false>(P, grid, smem, st));
-        case 2: return tiled ? (spec ? launch<2, 8, true>(P, grid, smem, st) : launch<2, 0, true>(P, grid, smem, st))
-                             : (spec ? launch<2, 8, false>(P, grid, smem, st) : launch<2, 0, false>(P, grid, smem, st));
-        case 4: return tiled ? (spec ? launch<4, 8, true>(P, grid, smem, st) : launch<4, 0, true>(P, grid, smem, st))
-                             : (spec ? launch<4, 8, false>(P, grid, smem, st) : launch<4, 0, false>(P, grid, smem, st));
-        case 8: return tiled ? (spec ? launch<8, 8, true>(P, grid, smem, st) : launch<8, 0, true>(P, grid, smem, st))
-                             : (spec ? launch<8, 8, false>(P, grid, smem, st) : launch<8, 0, false>(P, grid, smem, st));
-        case 16: return tiled ? (spec ? launch<16, 8, true>(P, grid, smem, st) : launch<16, 0, true>(P, grid, smem, st))
-                             : (spec ? launch<16, 8, false>(P, grid, smem, st) : launch<16, 0, false>(P, grid, smem, st));
-        case 32: return tiled ? (spec ? launch<32, 8, true>(P, grid, smem, st) : launch<32, 0, true>(P, grid, smem, st))
-                             : (spec ? launch<32, 8, false>(P, grid, smem, st) : launch<32, 0, false>(P, grid, smem, st));
+        case 1: return launch_L<1>(P, grid, smem, st);
+        case 2: return launch_L<2>(P, grid, smem, st);
+        case 4: return launch_L<4>(P, grid, smem, st);
+        case 8: return launch_L<8>(P, grid, smem, st);
+        case 16: return launch_L<16>(P, grid, smem, st);
+        case 32: return launch_L<32>(P, grid, smem, st);
     }
     return cudaErrorInvalidValue;
 }
