@@ -263,9 +263,12 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
         // The checkpoint row above this block and the adjoint row below it are private
         // to this thread; fetch them now so that they arrive while phase A runs.
         float4 ck_pre[STRIP / 2], adj_pre[STRIP / 2];
+        float2 Araw = bc(0.f);  // this thread's two A values, fetched with them
         {
             const bool ok = nr > 0 && pair_on && ch0 + cp < nch;
             const int dq = dbase + min(ch0 + cp, nch - 1);
+            if (nr > 0 && pair_on)
+                Araw = f2(__ldg(P.A + dq * P.A_ds + n0 * P.A_ns), n1 < N ? __ldg(P.A + dq * P.A_ds + n1 * P.A_ns) : 0.f);
             const float4 *pk = reinterpret_cast<const float4 *>(
                 P.saved + ((((int64_t)b * P.dim + dq) * P.nck + (blk - 1)) * NPp + pp) * Wp + j * STRIP);
             const float4 *pa = reinterpret_cast<const float4 *>(
@@ -411,8 +414,6 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
         if (pair_on) {
             const bool ch_ok = ch0 + cp < nch;
             const int d = dbase + min(ch0 + cp, nch - 1);
-            const float2 Araw = f2(__ldg(P.A + d * P.A_ds + n0 * P.A_ns),
-                                   n1 < N ? __ldg(P.A + d * P.A_ds + n1 * P.A_ns) : 0.f);
             const float2 A2 = mul2(Araw, bc(LOG2E));
             const float *dlc = sdl + cp * CS6;
             // The recomputed h rows are parked in this thread's own slots of the partial

@@ -232,9 +232,13 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
         // The checkpoint row above this block is private to this thread (it wrote it
         // when it last had the channel); fetch it now so it arrives during phase A.
         float4 ck_pre[STRIP / 2];
+        float2 A2 = bc(0.f);  // this thread's two A values (times log2 e), fetched with it
         {
             const bool ok = nr > 0 && r0 > 0 && pair_on && ch0 + cp < nch;
             const int dq = dbase + min(ch0 + cp, nch - 1);
+            if (nr > 0 && pair_on)
+                A2 = f2(__ldg(P.A + dq * P.A_ds + n0 * P.A_ns) * LOG2E,
+                        n1 < N ? __ldg(P.A + dq * P.A_ds + n1 * P.A_ns) * LOG2E : 0.f);
             const float4 *pk = reinterpret_cast<const float4 *>(
                 P.saved + ((((int64_t)b * P.dim + dq) * ckn + (P.ck_roll ? 0 : blk - 1)) * NPp + pp) * Wp + j * STRIP);
 #pragma unroll
@@ -328,8 +332,6 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
         if (pair_on) {
             const bool ch_ok = ch0 + cp < nch;
             const int d = dbase + min(ch0 + cp, nch - 1);
-            const float2 A2 = f2(__ldg(P.A + d * P.A_ds + n0 * P.A_ns) * LOG2E,
-                                 n1 < N ? __ldg(P.A + d * P.A_ds + n1 * P.A_ns) * LOG2E : 0.f);
             float2 h_up[STRIP], a_up[STRIP];
             float2 *ck = P.saved + ((((int64_t)b * P.dim + d) * ckn + (P.ck_roll ? 0 : blk)) * NPp + pp) * Wp + j * STRIP;
             if (r0 > 0) {
