@@ -141,6 +141,24 @@ int cs2d_bwd_dir(const cs2d_problem *p, const cs2d_dirs *dirs, const void *dout,
                  void *stream);
 
 /*
+ * Deterministic backward: bit-identical results from run to run.  cs2d_bwd (like
+ * the reference, selective_scan_bwd_kernel_oflex.cuh:608-609,770-771,886-901)
+ * adds the sums that cross CTAs - dB and dC over the channels of a group, dA, dD,
+ * ddelta_bias, dA_decay over the batch - with floating-point atomics, whose order
+ * varies.  Here every CTA stores its sums into slots of its own inside
+ * det_scratch (cs2d_bwd_det_scratch_bytes(p) bytes, 16-byte aligned, contents
+ * undefined before and after) and a second kernel adds them in a fixed order.
+ * Results are ADDED to dA, dB, dC, dD, ddelta_bias, dA_decay exactly as in
+ * cs2d_bwd (zero-fill them first).  dirs may be NULL.  Limits: ncols <= 256, and
+ * for ncols > 64 dstate > 8; otherwise CS2D_ERR_UNSUPPORTED
+ * (cs2d_bwd_det_scratch_bytes returns 0).
+ */
+size_t cs2d_bwd_det_scratch_bytes(const cs2d_problem *p);
+int cs2d_bwd_det(const cs2d_problem *p, const cs2d_dirs *dirs, const void *dout, int64_t dout_bs, int64_t dout_ds,
+                 int64_t dout_hs, const void *saved, void *scratch, void *det_scratch, void *du, void *ddelta,
+                 float *dA, float *dB, float *dC, float *dD, float *ddelta_bias, float *dA_decay, void *stream);
+
+/*
  * Forward that no backward will follow (inference, evaluation).  Same results as
  * cs2d_fwd / cs2d_fwd_dir (dirs may be NULL), but instead of the saved-state
  * buffer it takes a scratch buffer of cs2d_fwd_only_scratch_bytes(p) bytes

@@ -69,6 +69,11 @@ def lib():
         L.cs2d_fwd_dir.argtypes = [ctypes.POINTER(Problem), dp, vp, i64, i64, i64, vp, vp]
         L.cs2d_fwd_only.restype = ctypes.c_int
         L.cs2d_fwd_only.argtypes = [ctypes.POINTER(Problem), dp, vp, i64, i64, i64, vp, vp]
+        L.cs2d_bwd_det_scratch_bytes.restype = ctypes.c_size_t
+        L.cs2d_bwd_det_scratch_bytes.argtypes = [ctypes.POINTER(Problem)]
+        L.cs2d_bwd_det.restype = ctypes.c_int
+        L.cs2d_bwd_det.argtypes = [ctypes.POINTER(Problem), dp, vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
+                                   vp, vp]
         L.cs2d_bwd_dir.restype = ctypes.c_int
         L.cs2d_bwd_dir.argtypes = [ctypes.POINTER(Problem), dp, vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                                    vp]

@@ -159,7 +159,7 @@ def param_grad_layout(dim, dstate, has_D, has_bias, has_decay):
 
 
 def bwd(u, delta, A, B, C, D_, delta_bias_, dout, x_, x_v_, delta_softplus, A_decay_=None, x_sd_=None,
-        param_grads=None):
+        param_grads=None, deterministic=None):
     """Selective nd scan backward.
 
     Returns ``[du, ddelta, dA, dB, dC, dD, ddelta_bias, dA_decay]`` with ``None``
@@ -169,8 +169,14 @@ def bwd(u, delta, A, B, C, D_, delta_bias_, dout, x_, x_v_, delta_softplus, A_de
     flat fp32 CUDA tensor of ``param_grad_layout(...)[0]`` elements; dA, dD,
     ddelta_bias and dA_decay are then views into it, so that one collective can
     reduce them across ranks without packing copies.
+
+    ``deterministic`` (default: ``torch.are_deterministic_algorithms_enabled()``)
+    selects the backward without floating-point atomics (``cs2d_bwd_det``):
+    bit-identical gradients from run to run, for rows of at most 256 columns.
     """
     L = _lib.lib()
+    if deterministic is None:
+        deterministic = torch.are_deterministic_algorithms_enabled()
     _check(dout.is_cuda, "dout must be a CUDA tensor")
     _check(dout.dtype == u.dtype or dout.dtype == torch.float32, "dout must have the input dtype or float32")
     _check(_inner_ok(dout), "dout must be contiguous in the last dimension")
@@ -207,9 +213,18 @@ def bwd(u, delta, A, B, C, D_, delta_bias_, dout, x_, x_v_, delta_softplus, A_de
         dC = torch.zeros(tuple(C.shape), dtype=torch.float32, device=dev)
         scratch = torch.empty(L.cs2d_bwd_scratch_bytes(ctypes.byref(p)) // 4, dtype=torch.float32, device=dev)
         stream = torch.cuda.current_stream(dev).cuda_stream
-        rc = L.cs2d_bwd(ctypes.byref(p), _ptr(dout), dout.stride(0), dout.stride(1), dout.stride(2), _ptr(x_v_),
-                        _ptr(scratch), _ptr(du), _ptr(ddelta), _ptr(dA), _ptr(dB), _ptr(dC), _ptr(dD), _ptr(ddelta_bias),
-                        _ptr(dA_decay), ctypes.c_void_p(stream))
+        if deterministic:
+            nbytes_det = L.cs2d_bwd_det_scratch_bytes(ctypes.byref(p))
+            if nbytes_det == 0:
+                raise RuntimeError(f"cs2d backward has no deterministic implementation for this shape: {_lib.last_error()}")
+            det = torch.empty(nbytes_det // 4, dtype=torch.float32, device=dev)
+            rc = L.cs2d_bwd_det(ctypes.byref(p), None, _ptr(dout), dout.stride(0), dout.stride(1), dout.stride(2),
+                                _ptr(x_v_), _ptr(scratch), _ptr(det), _ptr(du), _ptr(ddelta), _ptr(dA), _ptr(dB), _ptr(dC),
+                                _ptr(dD), _ptr(ddelta_bias), _ptr(dA_decay), ctypes.c_void_p(stream))
+        else:
+            rc = L.cs2d_bwd(ctypes.byref(p), _ptr(dout), dout.stride(0), dout.stride(1), dout.stride(2), _ptr(x_v_),
+                            _ptr(scratch), _ptr(du), _ptr(ddelta), _ptr(dA), _ptr(dB), _ptr(dC), _ptr(dD),
+                            _ptr(ddelta_bias), _ptr(dA_decay), ctypes.c_void_p(stream))
     _raise_on(rc, "backward")
     if dim != delta_dim:
         rep = dim // delta_dim

@@ -175,6 +175,7 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     if (vec_ok(p->B, es, p->ncols, {p->B_bs, p->B_gs, p->B_ns, p->B_hs})) d.vec |= VEC_B;
     if (vec_ok(p->C, es, p->ncols, {p->C_bs, p->C_gs, p->C_ns, p->C_hs})) d.vec |= VEC_C;
     d.adj = nullptr;
+    d.det = 0; d.det_ts = 0;
     d.ck_roll = 0;
     d.status = nullptr;
     d.tile_left = d.tile_right = 0; d.Wout = p->ncols;
@@ -321,12 +322,57 @@ int cs2d_fwd_dir(const cs2d_problem *p, const cs2d_dirs *dirs, void *out, int64_
     return fwd_impl(p, dirs, out, out_bs, out_ds, out_hs, saved, stream);
 }
 
+// out[i] += part[i] + part[stride + i] + ... (count terms, in this order): the second step of the
+// deterministic backward
+__global__ void sum_slots(float *out, const float *part, int64_t n, int count, int64_t stride) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        float v = 0.f;
+        for (int t = 0; t < count; ++t) v += part[t * stride + i];
+        out[i] += v;
+    }
+}
+
+static cudaError_t launch_sum(float *out, const float *part, int64_t n, int count, int64_t stride, void *stream) {
+    if (!out || n <= 0) return cudaSuccess;
+    const int block = 256;
+    const int64_t want = (n + block - 1) / block;
+    sum_slots<<<(unsigned)(want < 8 * kSMs ? want : 8 * kSMs), block, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        out, part, n, count, stride);
+    g_launches.fetch_add(1);
+    return cudaGetLastError();
+}
+
+// layout of the deterministic backward's scratch, in floats
+struct DetLayout { int64_t nB, dB, dC, dA, dD, dbias, ddecay, total; int ntiles, grid, zero; };
+static int det_layout(const cs2d_problem *p, DetLayout *l) {
+    if (n_tiles(p->ncols) > 1)
+        return fail(CS2D_ERR_UNSUPPORTED, "the deterministic backward covers ncols <= %d", kTileCols);
+    TileView tv;
+    int rc = tile_view(p, 0, true, false, &tv);
+    if (rc) return rc;
+    // Without the dB/dC tiles in shared memory the CTA adds to its plane row by row, which has a
+    // single writer per element only when the CTA holds one channel group (see add_dbc).
+    if (!tv.g.acc && tv.g.CG != 1)
+        return fail(CS2D_ERR_UNSUPPORTED, "no deterministic backward for ncols=%d with dstate=%d "
+                                          "(dB/dC tiles do not fit in shared memory and several channel groups share a CTA)",
+                    p->ncols, p->dstate);
+    l->zero = !tv.g.acc;
+    l->ntiles = tv.g.ntiles; l->grid = tv.g.grid;
+    l->nB = (int64_t)p->batch * p->n_groups * p->dstate * p->nrows * p->ncols;
+    l->dB = 0; l->dC = l->dB + l->ntiles * l->nB; l->dA = l->dC + l->ntiles * l->nB;
+    l->dD = l->dA + (int64_t)p->batch * p->dim * p->dstate; l->dbias = l->dD + (int64_t)p->batch * p->dim;
+    l->ddecay = l->dbias + (int64_t)p->batch * p->dim; l->total = l->ddecay + l->grid;
+    return CS2D_OK;
+}
+
 static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout, int64_t dout_bs, int64_t dout_ds,
                     int64_t dout_hs, const void *saved, void *scratch, void *du, void *ddelta, float *dA, float *dB,
-                    float *dC, float *dD, float *ddelta_bias, float *dA_decay, void *stream) {
+                    float *dC, float *dD, float *ddelta_bias, float *dA_decay, void *stream, float *det = nullptr) {
     int rc = validate(p);
     if (rc) return rc;
     if ((rc = check_dirs(p, o))) return rc;
+    DetLayout dl = {};
+    if (det && (rc = det_layout(p, &dl))) return rc;
     const bool dirs = o && (o->flip_rows_mask || o->flip_cols_mask || o->shared_input);
     if (!dout || !saved || !scratch || !du || !ddelta || !dA || !dB || !dC)
         return fail(CS2D_ERR_INVALID, "dout, saved, scratch, du, ddelta, dA, dB, dC must be given");
@@ -372,11 +418,45 @@ static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout,
         d.adj_in = t + 1 < nt ? reinterpret_cast<const float4 *>(aedges + (size_t)t * eb) : nullptr;
         d.adj_out = t > 0 ? reinterpret_cast<float4 *>(aedges + (size_t)(t - 1) * eb) : nullptr;
         if (dirs) { d.flip_h = o->flip_rows_mask; d.flip_w = o->flip_cols_mask; d.u_shared = o->shared_input; }
+        if (det) {  // per-tile planes and per-batch slots instead of the results themselves
+            if (dl.zero && cudaMemsetAsync(det + dl.dB, 0, (size_t)(2 * dl.ntiles * dl.nB) * sizeof(float),
+                                           reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess)
+                return fail(CS2D_ERR_CUDA, "cannot clear the deterministic scratch");
+            d.det = 1; d.det_ts = dl.nB;
+            d.dB = det + dl.dB; d.dC = det + dl.dC; d.dA = det + dl.dA;
+            d.dD = dD ? det + dl.dD : nullptr; d.dbias = ddelta_bias ? det + dl.dbias : nullptr;
+            d.ddecay = dA_decay ? det + dl.ddecay : nullptr;
+        }
         cudaError_t e = launch_bwd(d, tv.g.L, tv.g.grid, reinterpret_cast<cudaStream_t>(stream));
         if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
         g_launches.fetch_add(1);
     }
+    if (det) {
+        const int64_t nA = (int64_t)p->dim * p->dstate;
+        cudaError_t e = launch_sum(dB, det + dl.dB, dl.nB, dl.ntiles, dl.nB, stream);
+        if (e == cudaSuccess) e = launch_sum(dC, det + dl.dC, dl.nB, dl.ntiles, dl.nB, stream);
+        if (e == cudaSuccess) e = launch_sum(dA, det + dl.dA, nA, p->batch, nA, stream);
+        if (e == cudaSuccess) e = launch_sum(dD, det + dl.dD, p->dim, p->batch, p->dim, stream);
+        if (e == cudaSuccess) e = launch_sum(ddelta_bias, det + dl.dbias, p->dim, p->batch, p->dim, stream);
+        if (e == cudaSuccess) e = launch_sum(dA_decay, det + dl.ddecay, 1, dl.grid, 1, stream);
+        if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "deterministic reduction failed: %s", cudaGetErrorString(e));
+    }
     return CS2D_OK;
+}
+
+size_t cs2d_bwd_det_scratch_bytes(const cs2d_problem *p) {
+    DetLayout dl = {};
+    if (validate(p) != CS2D_OK || det_layout(p, &dl) != CS2D_OK) return 0;
+    return (size_t)dl.total * sizeof(float);
+}
+
+int cs2d_bwd_det(const cs2d_problem *p, const cs2d_dirs *dirs, const void *dout, int64_t dout_bs, int64_t dout_ds,
+                 int64_t dout_hs, const void *saved, void *scratch, void *det_scratch, void *du, void *ddelta,
+                 float *dA, float *dB, float *dC, float *dD, float *ddelta_bias, float *dA_decay, void *stream) {
+    if (!det_scratch || (reinterpret_cast<uintptr_t>(det_scratch) & 15))
+        return fail(CS2D_ERR_INVALID, "det_scratch must be given and 16-byte aligned");
+    return bwd_impl(p, dirs, dout, dout_bs, dout_ds, dout_hs, saved, scratch, du, ddelta, dA, dB, dC, dD, ddelta_bias,
+                    dA_decay, stream, static_cast<float *>(det_scratch));
 }
 
 int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t dout_ds, int64_t dout_hs,

@@ -55,6 +55,23 @@ struct BwdSmem {
     }
 };
 
+// Row-by-row addition of one state pair's dB/dC values to global memory (shapes whose dB/dC
+// tiles do not fit in shared memory).  Deterministic mode: with one channel group per CTA the
+// lane that owns (pair, column) is the only writer of that element of the CTA's plane, pass
+// after pass, so a plain read-modify-write on the zero-filled plane replaces the atomics.
+__device__ __forceinline__ void add_dbc(const Dev &P, int tile, int64_t og, bool two, float2 vb, float2 vc) {
+    const int64_t ns = (int64_t)P.H * P.Wout;
+    if (P.det) {
+        float *qb = P.dB + (int64_t)tile * P.det_ts + og, *qc = P.dC + (int64_t)tile * P.det_ts + og;
+        qb[0] += vb.x; qc[0] += vc.x;
+        if (two) { qb[ns] += vb.y; qc[ns] += vc.y; }
+    } else {
+        atomicAdd(P.dB + og, vb.x);
+        atomicAdd(P.dC + og, vc.x);
+        if (two) { atomicAdd(P.dB + og + ns, vb.y); atomicAdd(P.dC + og + ns, vc.y); }
+    }
+}
+
 // NPC = 8 specialises the common geometry (8 state-pair slots, one channel group, 8 warps) so
 // that every shared-memory offset is a compile-time constant; NPC = 0 reads it from P.
 // TILED compiles the column-tile edge handling in; the common single-tile launch leaves it out.
@@ -357,11 +374,17 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                     if (c < W && rr < pnr && 2 * spp < N) {
                         const int64_t og = ((((int64_t)b * P.G + g_) * N + 2 * spp) * H + (fh ? H - 1 - (pr0 + rr) : pr0 + rr)) * P.Wout +
                                            (fw ? W - 1 - c : c);
-                        atomicAdd(P.dB + og, vb.x);
-                        atomicAdd(P.dC + og, vc.x);
-                        if (2 * spp + 1 < N) {
-                            atomicAdd(P.dB + og + (int64_t)H * P.Wout, vb.y);
-                            atomicAdd(P.dC + og + (int64_t)H * P.Wout, vc.y);
+                        if (P.det) {  // this channel tile's own plane: each element has one writer
+                            float *qb = P.dB + (int64_t)tile * P.det_ts + og, *qc = P.dC + (int64_t)tile * P.det_ts + og;
+                            qb[0] = vb.x; qc[0] = vc.x;
+                            if (2 * spp + 1 < N) { qb[(int64_t)H * P.Wout] = vb.y; qc[(int64_t)H * P.Wout] = vc.y; }
+                        } else {
+                            atomicAdd(P.dB + og, vb.x);
+                            atomicAdd(P.dC + og, vc.x);
+                            if (2 * spp + 1 < N) {
+                                atomicAdd(P.dB + og + (int64_t)H * P.Wout, vb.y);
+                                atomicAdd(P.dC + og + (int64_t)H * P.Wout, vc.y);
+                            }
                         }
                     }
                 }
@@ -633,12 +656,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                             } else if (ch_ok && j * STRIP + i < W) {
                                 const int64_t og = ((((int64_t)b * P.G + g_) * N + n0) * H + (fh ? H - 1 - (r0 + rr) : r0 + rr)) * P.Wout +
                                                    (fw ? W - 1 - (j * STRIP + i) : j * STRIP + i);
-                                atomicAdd(P.dB + og, dBv.x);
-                                atomicAdd(P.dC + og, dCv.x);
-                                if (n1 < N) {
-                                    atomicAdd(P.dB + og + (int64_t)H * P.Wout, dBv.y);
-                                    atomicAdd(P.dC + og + (int64_t)H * P.Wout, dCv.y);
-                                }
+                                add_dbc(P, tile, og, n1 < N, dBv, dCv);
                             }
                         } else {
                             const int o = i * 32 + ((lane + L * (i / NU)) & 31);
@@ -671,12 +689,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                                     const int64_t og =
                                         ((((int64_t)b * P.G + g_) * N + n0) * H + (fh ? H - 1 - (r0 + rr) : r0 + rr)) * P.Wout +
                                         (fw ? W - 1 - (j * STRIP + col) : j * STRIP + col);
-                                    atomicAdd(P.dB + og, sb.x);
-                                    atomicAdd(P.dC + og, sc2.x);
-                                    if (n1 < N) {
-                                        atomicAdd(P.dB + og + (int64_t)H * P.Wout, sb.y);
-                                        atomicAdd(P.dC + og + (int64_t)H * P.Wout, sc2.y);
-                                    }
+                                    add_dbc(P, tile, og, n1 < N, sb, sc2);
                                 }
                             }
                         }
@@ -713,21 +726,26 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
         if (lane == 0) sdecay[warp] = v;
     }
     cta_sync();
+    // deterministic mode: this batch entry's own slots instead of atomics onto the results
+    const int64_t slot = P.det ? (int64_t)b * P.dim : 0;
     for (int i = tid; i < nch * 2 * NPp; i += nthr) {
         const int sc = i / (2 * NPp), n = i % (2 * NPp);
-        if (n < N) atomicAdd(P.dA + (int64_t)(dbase + sc) * N + n, sdA[i]);
+        if (n < N) {
+            float *q = P.dA + (slot + dbase + sc) * N + n;
+            if (P.det) *q = sdA[i]; else atomicAdd(q, sdA[i]);
+        }
     }
     for (int i = tid; i < nch * 2; i += nthr) {
         const int sd = dbase + i / 2;
         float v = 0.f;
         for (int q = 0; q < S::NSEG; ++q) v += sred[((i / 2) * S::NSEG + q) * 2 + (i & 1)];
-        if ((i & 1) == 0) { if (P.dD) atomicAdd(P.dD + sd, v); }
-        else if (P.dbias) atomicAdd(P.dbias + sd, v);
+        float *q = (i & 1) == 0 ? P.dD : P.dbias;
+        if (q) { if (P.det) q[slot + sd] = v; else atomicAdd(q + sd, v); }
     }
     if (want_decay && tid == 0) {
         float v = 0.f;
         for (int w = 0; w < nw; ++w) v += sdecay[w];
-        atomicAdd(P.ddecay, v / decay);
+        if (P.det) P.ddecay[blockIdx.x] = v / decay; else atomicAdd(P.ddecay, v / decay);
     }
 }
 

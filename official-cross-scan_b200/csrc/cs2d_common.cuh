@@ -84,6 +84,12 @@ struct Dev {
     float2 *adj;                           // [batch][dim][NPp][L*8] adjoint row between blocks
     void *du, *ddelta;
     float *dA, *dB, *dC, *dD, *dbias, *ddecay;
+    // Deterministic mode: no global atomics.  Every CTA stores (does not add) its dB/dC sums
+    // into the plane of its channel tile (dB/dC then point at tile 0's plane, det_ts elements
+    // apart) and its per-channel sums into per-batch slots: dA [batch][dim][N], dD and dbias
+    // [batch][dim], ddecay [grid]; a second kernel adds the planes and slots up in a fixed order.
+    int det;
+    int64_t det_ts;
 };
 enum { VEC_U = 1, VEC_DELTA = 2, VEC_B = 4, VEC_C = 8, VEC_OUT = 16, VEC_DU = 32 };
 

@@ -53,6 +53,11 @@ def test_sizes_without_gpu():
     per = 2 * 8 * 8 * 8  # batch x dim x pair slots x bytes per float2
     assert L.cs2d_saved_bytes(ctypes.byref(pw)) == per * 14 * (256 + 128) + 2 * 8 * 8 * 56 * 16
     assert L.cs2d_bwd_scratch_bytes(ctypes.byref(pw)) == per * (256 + 128) + 2 * 8 * 8 * 56 * 16
+    # deterministic backward: per-channel-tile dB/dC planes + per-batch parameter slots + one slot per CTA
+    det = L.cs2d_bwd_det_scratch_bytes(ctypes.byref(p))
+    nB, slots = 2 * 4 * 16 * 56 * 56, 2 * 8 * (16 + 2)
+    assert det > 0 and (det // 4 - slots) % (2 * nB) in range(0, 2 * 8 * 4 + 1)
+    assert L.cs2d_bwd_det_scratch_bytes(ctypes.byref(pw)) == 0   # wider than one column tile
     # a forward that no backward follows keeps one rolling row instead of 14 checkpoints
     assert L.cs2d_fwd_only_scratch_bytes(ctypes.byref(p)) == 2 * 8 * 8 * 64 * 8
     assert L.cs2d_fwd_only_scratch_bytes(ctypes.byref(pw)) == per * (256 + 128) + 2 * 8 * 8 * 56 * 16

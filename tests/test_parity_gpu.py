@@ -255,3 +255,32 @@ def test_forward_only_equals_forward(shape, dtype):
     with torch.no_grad():
         assert torch.equal(cs2d.selective_scan_2d(*args), full)
     assert cs2d.device_status() == 0
+
+
+@pytest.mark.parametrize("shape,dtype,kw", [((4, 4, 48, 16, 21, 40), torch.float32, {}),
+                                            ((2, 4, 6, 5, 9, 60), torch.bfloat16, {"a_decay": 0.9}), ((2, 4, 5, 16, 9, 200), torch.float32, {}),
+                                            ((3, 2, 40, 1, 14, 14), torch.float32, {"delta_dim": 20})])
+def test_deterministic_backward_is_bit_reproducible(shape, dtype, kw):
+    """cs2d_bwd_det: same bits on every run, same values as the atomic backward within tolerance."""
+    inp = make_inputs(*shape, dtype=dtype, seed=8, **kw)
+    dev = {k: (v.cuda() if v is not None else None) for k, v in inp.items()}
+    o = cs2d.fwd(dev["u"], dev["delta"], dev["A"], dev["B"], dev["C"], dev["D"], dev["delta_bias"], True, False,
+                 dev["A_decay"])
+    run = lambda det: cs2d.bwd(dev["u"], dev["delta"], dev["A"], dev["B"], dev["C"], dev["D"], dev["delta_bias"],
+                               dev["dout"], o[1], o[2], True, dev["A_decay"], o[3], deterministic=det)
+    a, b2, c = run(True), run(True), run(False)
+    rtol, atol = TOL[str(dtype)[6:]]
+    for name, x, y, z in zip(("du", "ddelta", "dA", "dB", "dC", "dD", "ddelta_bias", "dA_decay"), a, b2, c):
+        assert (x is None) == (z is None), name
+        if x is None:
+            continue
+        assert torch.equal(x, y), f"{name} differs between two deterministic runs"
+        s = 10.0 if name in REDUCED else 1.0
+        check_close(name, x.float().cpu().numpy(), z.float().cpu().numpy(), rtol * s, atol * s * max(1.0, float(z.float().abs().max())))
+    with pytest.raises(RuntimeError, match="deterministic"):
+        wide = make_inputs(1, 1, 2, 2, 4, 300, seed=1)
+        wd = {k: (v.cuda() if v is not None else None) for k, v in wide.items()}
+        ow = cs2d.fwd(wd["u"], wd["delta"], wd["A"], wd["B"], wd["C"], wd["D"], wd["delta_bias"], True, False, None)
+        cs2d.bwd(wd["u"], wd["delta"], wd["A"], wd["B"], wd["C"], wd["D"], wd["delta_bias"], wd["dout"], ow[1], ow[2],
+                 True, None, ow[3], deterministic=True)
+    assert cs2d.device_status() == 0
