@@ -56,20 +56,16 @@ struct BwdSmem {
 };
 
 // Row-by-row addition of one state pair's dB/dC values to global memory (shapes whose dB/dC
-// tiles do not fit in shared memory).  Deterministic mode: with one channel group per CTA the
-// lane that owns (pair, column) is the only writer of that element of the CTA's plane, pass
-// after pass, so a plain read-modify-write on the zero-filled plane replaces the atomics.
+// tiles do not fit in shared memory).  Deterministic mode adds onto the CTA's own zero-filled
+// plane (det_ts elements per channel tile; 0 otherwise): with one channel group per CTA the lane
+// that owns (pair, column) is the only one that ever touches that element, pass after pass, so
+// the atomic adds arrive in program order.
 __device__ __forceinline__ void add_dbc(const Dev &P, int tile, int64_t og, bool two, float2 vb, float2 vc) {
     const int64_t ns = (int64_t)P.H * P.Wout;
-    if (P.det) {
-        float *qb = P.dB + (int64_t)tile * P.det_ts + og, *qc = P.dC + (int64_t)tile * P.det_ts + og;
-        qb[0] += vb.x; qc[0] += vc.x;
-        if (two) { qb[ns] += vb.y; qc[ns] += vc.y; }
-    } else {
-        atomicAdd(P.dB + og, vb.x);
-        atomicAdd(P.dC + og, vc.x);
-        if (two) { atomicAdd(P.dB + og + ns, vb.y); atomicAdd(P.dC + og + ns, vc.y); }
-    }
+    float *qb = P.dB + (int64_t)tile * P.det_ts + og, *qc = P.dC + (int64_t)tile * P.det_ts + og;
+    atomicAdd(qb, vb.x);
+    atomicAdd(qc, vc.x);
+    if (two) { atomicAdd(qb + ns, vb.y); atomicAdd(qc + ns, vc.y); }
 }
 
 // NPC = 8 specialises the common geometry (8 state-pair slots, one channel group, 8 warps) so
@@ -363,14 +359,15 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
             }
             // a row block is complete when its last pass has been written out
             if (acc_on && pnr > 0 && ppass == npass - 1) {
-                const int itemsB = nw * RB * Wp;  // one float2 (two states) per item
+                const int itemsB = NPp * RB * Wp;  // one float2 (two states) per item
                 for (int it = tid; it < itemsB; it += nthr) {
-                    const int c = it % Wp, rr = (it / Wp) % RB, w = it / (Wp * RB);
-                    const int spp = w % NPp, scg = w / NPp;
-                    const int o = (w * RB + rr) * Wp + pos2<L>(c);
-                    const float2 vb = saB[o], vc = saC[o];
-                    saB[o] = bc(0.f); saC[o] = bc(0.f);
-                    (void)scg;
+                    const int c = it % Wp, rr = (it / Wp) % RB, spp = it / (Wp * RB);
+                    float2 vb = bc(0.f), vc = bc(0.f);
+                    for (int scg = 0; scg < CG; ++scg) {  // the CTA's channel groups, in order
+                        const int o = ((scg * NPp + spp) * RB + rr) * Wp + pos2<L>(c);
+                        vb = add2(vb, saB[o]); vc = add2(vc, saC[o]);
+                        saB[o] = bc(0.f); saC[o] = bc(0.f);
+                    }
                     if (c < W && rr < pnr && 2 * spp < N) {
                         const int64_t og = ((((int64_t)b * P.G + g_) * N + 2 * spp) * H + (fh ? H - 1 - (pr0 + rr) : pr0 + rr)) * P.Wout +
                                            (fw ? W - 1 - c : c);
