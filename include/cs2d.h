@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define CS2D_ABI_VERSION 1
+#define CS2D_ABI_VERSION 2
 #define CS2D_MAX_DSTATE 16 /* reference: MAX_DSTATE, include/selective_scan_common.h:13 */
 
 typedef enum {
@@ -126,10 +126,26 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
  * reads u channel d - g*dim/n_groups, u_ds being the stride of those channels;
  * bit 1: the same for dout in the backward.  out, du, ddelta keep `dim` channels
  * (one result per direction).  Not yet combined with ncols > 256.
+ *
+ * Direction merge (merge_w != NULL): the weighted sum over the directions happens
+ * inside the kernels.  merge_w holds one fp32 weight per channel (dim values:
+ * direction-major, w[g][d]).
+ *   forward:  `out` is an fp32 image (batch, dim/n_groups, nrows, ncols) that the
+ *             caller zero-fills (p->out_dtype = CS2D_F32); the kernel ADDS
+ *             sum_g w[g][d] * y_g[d] onto it - no per-direction outputs exist.
+ *   backward: `dout` is the gradient of that image (dim/n_groups channels, set
+ *             shared_input bit 1); `du` is an fp32 image (batch, dim/n_groups, nrows,
+ *             ncols), zero-filled, onto which sum_g w*du_g is ADDED; ddelta, dA, dB, dC,
+ *             dD, ddelta_bias come out scaled by w as the chain rule asks; merge_dw
+ *             (dim fp32 values, zero-filled, may be NULL) receives dw[g][d] = sum dy*y_g[d].
+ * A_decay and the deterministic backward are not combined with the merge.
  */
 typedef struct {
     uint32_t flip_rows_mask, flip_cols_mask;
     int32_t shared_input;
+    int32_t reserved;        /* zero */
+    const float *merge_w;    /* NULL: no merge */
+    float *merge_dw;
 } cs2d_dirs;
 
 /* cs2d_fwd / cs2d_bwd with scan directions (dirs may be NULL = cs2d_fwd / cs2d_bwd). */

@@ -17,7 +17,8 @@ _i32, _i64, _p = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p
 class Dirs(ctypes.Structure):
     """Mirror of ``cs2d_dirs``."""
     _fields_ = [("flip_rows_mask", ctypes.c_uint32), ("flip_cols_mask", ctypes.c_uint32),
-                ("shared_input", ctypes.c_int32)]
+                ("shared_input", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("merge_w", ctypes.c_void_p), ("merge_dw", ctypes.c_void_p)]
 
 
 class Problem(ctypes.Structure):
@@ -83,7 +84,7 @@ def lib():
         L.cs2d_abi_version.restype = ctypes.c_int
         L.cs2d_launch_count.restype = ctypes.c_int64
         L.cs2d_device_status.restype = ctypes.c_int
-        if L.cs2d_abi_version() != 1:
+        if L.cs2d_abi_version() != 2:
             raise RuntimeError("cs2d: ABI version mismatch between libcs2d.so and the Python binding")
         _lib = L
     return _lib

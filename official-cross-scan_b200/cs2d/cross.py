@@ -16,11 +16,13 @@ over ``u[b, d]`` with the direction's own ``delta[b, k*D+d]``, ``A[k*D+d]``,
 image coordinates.
 
 All four directions run in ONE kernel launch each way.  The kernels apply the
-flips as index maps while they stage tiles and write results
-(``cs2d_fwd_dir`` / ``cs2d_bwd_dir``), and the K directions read the same
-``u``: nothing is flipped or replicated in memory.  What remains in torch is
-the weighted sum over the K direction planes (y, du, dw).  Rows wider than 256
-columns take the composed path (materialised flips around ``ops.fwd`` /
+flips as index maps while they stage tiles and write results, the K directions
+read the same ``u`` (and, in the backward, the same ``dy``), and the weighted sum
+over the directions happens inside the kernels as well (``cs2d_dirs.merge_w``):
+the forward adds ``w*y_k`` onto one fp32 image, the backward adds ``w*du_k`` onto
+one fp32 image, scales the other gradients by ``w`` and accumulates ``dw``.
+Nothing is flipped, replicated or kept per direction in memory.  Rows wider than
+256 columns take the composed path (materialised flips around ``ops.fwd`` /
 ``ops.bwd``) until direction maps and column tiles are combined.
 """
 from __future__ import annotations
@@ -59,20 +61,21 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
-def _dir_forward(u, delta, A, B, C, D, delta_bias, delta_softplus, keep_state=True):
-    """One launch for all directions; returns per-direction outputs (b, K*d, h, w) fp32 and the saved state
+def _dir_forward(u, delta, A, B, C, w, D, delta_bias, delta_softplus, keep_state=True):
+    """One launch for all directions, merged in the kernel: returns y (b, d, h, w) fp32 and the saved state
     (``None`` when ``keep_state`` is false: the forward then only holds one rolling row of state)."""
     L = _lib.lib()
     K, dim = B.size(1), A.size(0)
     p = ops._problem(u, delta, A, B, C, D, delta_bias, None, delta_softplus, torch.float32, "cross_scan_fwd",
                      shared_u_dim=dim)
     rows, cols = _masks(K)
-    dirs = _lib.Dirs(rows, cols, 1)
+    wf = w.detach().float().contiguous()
+    dirs = _lib.Dirs(rows, cols, 1, 0, wf.data_ptr(), None)
     nbytes = (L.cs2d_saved_bytes if keep_state else L.cs2d_fwd_only_scratch_bytes)(ctypes.byref(p))
     if nbytes == 0:
         raise RuntimeError(f"cs2d forward: {_lib.last_error()}")
     with torch.cuda.device(u.device):
-        out = torch.empty(u.size(0), dim, u.size(2), u.size(3), dtype=torch.float32, device=u.device)
+        out = torch.zeros(tuple(u.shape), dtype=torch.float32, device=u.device)   # the directions add onto it
         saved = torch.empty(nbytes // 4, dtype=torch.float32, device=u.device)
         rc = (L.cs2d_fwd_dir if keep_state else L.cs2d_fwd_only)(
             ctypes.byref(p), ctypes.byref(dirs), _ptr(out), out.stride(0), out.stride(1), out.stride(2), _ptr(saved),
@@ -81,31 +84,33 @@ def _dir_forward(u, delta, A, B, C, D, delta_bias, delta_softplus, keep_state=Tr
     return out, (saved if keep_state else None)
 
 
-def _dir_backward(u, delta, A, B, C, D, delta_bias, g, saved, delta_softplus):
-    """g: per-direction output gradient (b, K*d, h, w) fp32 in image coordinates."""
+def _dir_backward(u, delta, A, B, C, w, D, delta_bias, dy, saved, delta_softplus):
+    """dy: gradient of the merged image (b, d, h, w), input dtype or fp32, shared by the directions."""
     L = _lib.lib()
     K, dim, n = B.size(1), A.size(0), A.size(1)
     dev = u.device
-    p = ops._problem(u, delta, A, B, C, D, delta_bias, None, delta_softplus, torch.float32, "cross_scan_bwd",
+    p = ops._problem(u, delta, A, B, C, D, delta_bias, None, delta_softplus, dy.dtype, "cross_scan_bwd",
                      shared_u_dim=dim)
     rows, cols = _masks(K)
-    dirs = _lib.Dirs(rows, cols, 1)  # u shared; g is per direction (it carries the fusion weight)
+    wf = w.detach().float().contiguous()
     with torch.cuda.device(dev):
-        shape = (u.size(0), dim, u.size(2), u.size(3))
-        du = torch.empty(shape, dtype=u.dtype, device=dev)
-        ddelta = torch.empty(shape, dtype=u.dtype, device=dev)
+        du = torch.zeros(tuple(u.shape), dtype=torch.float32, device=dev)          # sum over the directions
+        dw = torch.zeros(dim, dtype=torch.float32, device=dev)
+        ddelta = torch.empty(tuple(delta.shape), dtype=u.dtype, device=dev)
         total, parts = ops.param_grad_layout(dim, n, D is not None, delta_bias is not None, False)
         flat = torch.zeros(total, dtype=torch.float32, device=dev)
         part = lambda name: flat[parts[name][0]:parts[name][0] + parts[name][1]] if name in parts else None
         dB = torch.zeros(tuple(B.shape), dtype=torch.float32, device=dev)
         dC = torch.zeros(tuple(C.shape), dtype=torch.float32, device=dev)
         scratch = torch.empty(L.cs2d_bwd_scratch_bytes(ctypes.byref(p)) // 4, dtype=torch.float32, device=dev)
-        rc = L.cs2d_bwd_dir(ctypes.byref(p), ctypes.byref(dirs), _ptr(g), g.stride(0), g.stride(1), g.stride(2),
+        dirs = _lib.Dirs(rows, cols, 3, 0, wf.data_ptr(), dw.data_ptr())  # u and dy shared by the directions
+        rc = L.cs2d_bwd_dir(ctypes.byref(p), ctypes.byref(dirs), _ptr(dy), dy.stride(0), dy.stride(1), dy.stride(2),
                             _ptr(saved), _ptr(scratch), _ptr(du), _ptr(ddelta), _ptr(part("dA")), _ptr(dB), _ptr(dC),
                             _ptr(part("dD")), _ptr(part("ddelta_bias")), None,
                             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     ops._raise_on(rc, "backward")
-    return du, ddelta, part("dA").view(dim, n), dB.to(B.dtype), dC.to(C.dtype), part("dD"), part("ddelta_bias")
+    return (du.to(u.dtype), ddelta, part("dA").view(dim, n), dB.to(B.dtype), dC.to(C.dtype), dw.view(K, dim // K),
+            part("dD"), part("ddelta_bias"))
 
 
 class CrossScan2D(torch.autograd.Function):
@@ -119,9 +124,9 @@ class CrossScan2D(torch.autograd.Function):
         ctx.delta_softplus = delta_softplus
         if ctx.direct:
             u, delta, B, C = u.contiguous(), delta.contiguous(), B.contiguous(), C.contiguous()
-            out, saved = _dir_forward(u, delta, A, B, C, D, delta_bias, delta_softplus)
-            yk = out.view(b, K, d, h, wd)                       # per direction, image coordinates, fp32
-            ctx.save_for_backward(u, delta, A, B, C, D, delta_bias, w, yk, saved)
+            y, saved = _dir_forward(u, delta, A, B, C, w, D, delta_bias, delta_softplus)
+            ctx.save_for_backward(u, delta, A, B, C, D, delta_bias, w, saved)
+            return y.to(u.dtype)
         else:
             us = torch.cat([_flip(u, k) for k in range(K)], 1).contiguous()
             ds = _to_scan(delta, K, d).contiguous()
@@ -134,17 +139,18 @@ class CrossScan2D(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
+        if ctx.direct:
+            u, delta, A, B, C, D, delta_bias, w, saved = ctx.saved_tensors
+            if dy.stride(-1) != 1:
+                dy = dy.contiguous()
+            du, ddelta, dA, dB, dC, dw, dD, dbias = _dir_backward(u, delta, A, B, C, w, D, delta_bias, dy, saved,
+                                                                  ctx.delta_softplus)
+            return du, ddelta, dA, dB, dC, dw.to(w.dtype), dD, dbias, None
         u, delta, A, B, C, D, delta_bias, w, yk, saved = ctx.saved_tensors
         b, K, d, h, wd = yk.shape
         dyf = dy.float()
         dw = (dyf[:, None] * yk).sum((0, 3, 4)).to(w.dtype)
         gk = dyf[:, None] * w.float()[None, :, :, None, None]   # (b, K, d, h, w): gradient of each y_k
-        if ctx.direct:
-            g = gk.reshape(b, K * d, h, wd).contiguous()
-            du_k, ddelta, dA, dB, dC, dD, dbias = _dir_backward(u, delta, A, B, C, D, delta_bias, g, saved,
-                                                                ctx.delta_softplus)
-            du = du_k.view(b, K, d, h, wd).float().sum(1).to(u.dtype)
-            return du, ddelta, dA, dB, dC, dw, dD, dbias, None
         g = torch.cat([_flip(gk[:, k], k) for k in range(K)], 1).contiguous()
         empty = torch.empty(0, dtype=torch.float32, device=u.device)
         du_s, dd_s, dA, dB_s, dC_s, dD, dbias, _ = ops.bwd(u, delta, A, B, C, D, delta_bias, g, empty, saved,
@@ -162,7 +168,7 @@ def cross_scan_2d(u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplus=
         K = B.size(1)
         if delta.size(1) != K * d or A.size(0) != K * d or tuple(w.shape) != (K, d):
             raise RuntimeError("expected delta (b, K*D, h, w), A (K*D, n), w (K, D)")
-        out, _ = _dir_forward(u.contiguous(), delta.contiguous(), A, B.contiguous(), C.contiguous(), D, delta_bias,
-                              delta_softplus, keep_state=False)
-        return (out.view(b, K, d, h, wd) * w.float()[None, :, :, None, None]).sum(1).to(u.dtype)
+        y, _ = _dir_forward(u.contiguous(), delta.contiguous(), A, B.contiguous(), C.contiguous(), w, D, delta_bias,
+                            delta_softplus, keep_state=False)
+        return y.to(u.dtype)
     return CrossScan2D.apply(u, delta, A, B, C, w, D, delta_bias, delta_softplus)

@@ -176,6 +176,7 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     if (vec_ok(p->C, es, p->ncols, {p->C_bs, p->C_gs, p->C_ns, p->C_hs})) d.vec |= VEC_C;
     d.adj = nullptr;
     d.det = 0; d.det_ts = 0;
+    d.mw = nullptr; d.dw = nullptr;
     d.ck_roll = 0;
     d.status = nullptr;
     d.tile_left = d.tile_right = 0; d.Wout = p->ncols;
@@ -254,7 +255,8 @@ size_t cs2d_bwd_scratch_bytes(const cs2d_problem *p) { return layout_bytes(p, tr
 size_t cs2d_fwd_only_scratch_bytes(const cs2d_problem *p) { return layout_bytes(p, false, true); }
 
 static int check_dirs(const cs2d_problem *p, const cs2d_dirs *o) {
-    if (!o || (!o->flip_rows_mask && !o->flip_cols_mask && !o->shared_input)) return CS2D_OK;
+    if (o && o->merge_w && p->A_decay) return fail(CS2D_ERR_UNSUPPORTED, "A_decay is not combined with the direction merge");
+    if (!o || (!o->flip_rows_mask && !o->flip_cols_mask && !o->shared_input && !o->merge_w)) return CS2D_OK;
     if (p->n_groups > 32) return fail(CS2D_ERR_INVALID, "direction masks cover at most 32 groups");
     if (n_tiles(p->ncols) > 1)
         return fail(CS2D_ERR_UNSUPPORTED, "scan directions are not combined with column tiles (ncols > %d) yet",
@@ -267,8 +269,10 @@ static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_
     int rc = validate(p);
     if (rc) return rc;
     if ((rc = check_dirs(p, o))) return rc;
-    const bool dirs = o && (o->flip_rows_mask || o->flip_cols_mask || o->shared_input);
+    const bool dirs = o && (o->flip_rows_mask || o->flip_cols_mask || o->shared_input || o->merge_w);
     if (!out || !saved) return fail(CS2D_ERR_INVALID, "out and saved must be given");
+    if (o && o->merge_w && p->out_dtype != CS2D_F32)
+        return fail(CS2D_ERR_INVALID, "the direction merge adds onto an fp32 image: out_dtype must be CS2D_F32");
     if (reinterpret_cast<uintptr_t>(saved) & 15) return fail(CS2D_ERR_INVALID, "saved must be 16-byte aligned");
     int *status = status_ptr();
     if (!status) return fail(CS2D_ERR_CUDA, "cannot locate the device status word");
@@ -299,7 +303,7 @@ static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_
         char *edges = reinterpret_cast<char *>(saved) + ck_total;
         d.edge_in = t > 0 ? reinterpret_cast<const float4 *>(edges + (size_t)(t - 1) * eb) : nullptr;
         d.edge_out = t + 1 < nt ? reinterpret_cast<float4 *>(edges + (size_t)t * eb) : nullptr;
-        if (dirs) { d.flip_h = o->flip_rows_mask; d.flip_w = o->flip_cols_mask; d.u_shared = o->shared_input; }
+        if (dirs) { d.flip_h = o->flip_rows_mask; d.flip_w = o->flip_cols_mask; d.u_shared = o->shared_input; d.mw = o->merge_w; }
         cudaError_t e = launch_fwd(d, tv.g.L, tv.g.grid, reinterpret_cast<cudaStream_t>(stream));
         if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
         g_launches.fetch_add(1);
@@ -373,7 +377,10 @@ static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout,
     if ((rc = check_dirs(p, o))) return rc;
     DetLayout dl = {};
     if (det && (rc = det_layout(p, &dl))) return rc;
-    const bool dirs = o && (o->flip_rows_mask || o->flip_cols_mask || o->shared_input);
+    const bool dirs = o && (o->flip_rows_mask || o->flip_cols_mask || o->shared_input || o->merge_w);
+    if (o && o->merge_w && (det || !(o->shared_input & 2)))
+        return fail(CS2D_ERR_INVALID, "the direction merge needs the shared gradient image (shared_input bit 1) "
+                                      "and is not combined with the deterministic backward");
     if (!dout || !saved || !scratch || !du || !ddelta || !dA || !dB || !dC)
         return fail(CS2D_ERR_INVALID, "dout, saved, scratch, du, ddelta, dA, dB, dC must be given");
     if ((reinterpret_cast<uintptr_t>(saved) | reinterpret_cast<uintptr_t>(scratch)) & 15)
@@ -417,7 +424,10 @@ static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout,
         d.edge_in = t > 0 ? reinterpret_cast<const float4 *>(edges + (size_t)(t - 1) * eb) : nullptr;
         d.adj_in = t + 1 < nt ? reinterpret_cast<const float4 *>(aedges + (size_t)t * eb) : nullptr;
         d.adj_out = t > 0 ? reinterpret_cast<float4 *>(aedges + (size_t)(t - 1) * eb) : nullptr;
-        if (dirs) { d.flip_h = o->flip_rows_mask; d.flip_w = o->flip_cols_mask; d.u_shared = o->shared_input; }
+        if (dirs) {
+            d.flip_h = o->flip_rows_mask; d.flip_w = o->flip_cols_mask; d.u_shared = o->shared_input;
+            d.mw = o->merge_w; d.dw = o->merge_dw;
+        }
         if (det) {  // per-tile planes and per-batch slots instead of the results themselves
             if (dl.zero && cudaMemsetAsync(det + dl.dB, 0, (size_t)(2 * dl.ntiles * dl.nB) * sizeof(float),
                                            reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess)

@@ -49,9 +49,10 @@ struct BwdSmem {
     // dD / ddelta_bias partial sums: one slot per (channel, segment of the channel's RB*T4 write-out
     // items that one warp reduces), so that every slot has a single owner and needs no atomics
     static constexpr int SEG = RB * (Wp / 4) < 32 ? RB * (Wp / 4) : 32, NSEG = RB * (Wp / 4) / SEG;
-    // dA: [CT][2*NPp], red: [CT][NSEG][2], decay: [warps], par: [CT][2] (D, delta_bias of the CTA's channels)
+    // dA: [CT][2*NPp], red: [CT][NSEG][2], decay: [warps], par: [CT][2] (D, delta_bias of the CTA's
+    // channels), merge weights [CT], dw: [CT][NPp]
     static __host__ __device__ constexpr int total(int CP, int NPp, int CT, int nw, bool acc) {
-        return dA(CP, NPp, nw, acc) + CT * 2 * NPp + CT * NSEG * 2 + nw + CT * 2;
+        return dA(CP, NPp, nw, acc) + CT * 2 * NPp + CT * NSEG * 2 + nw + CT * 3 + CT * NPp;
     }
 };
 
@@ -100,6 +101,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     float *sred = sdA + CT * 2 * NPp;
     float *sdecay = sred + CT * S::NSEG * 2;
     float *spar = sdecay + nw;
+    float *smw = spar + 2 * CT, *sdw = smw + CT;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int j = lane & (L - 1), cl = lane / L;
@@ -123,7 +125,9 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     for (int i = tid; i < nch; i += nthr) {  // D and delta_bias of this CTA's channels
         spar[2 * i] = P.D ? __ldg(P.D + dbase + i) : 0.f;
         spar[2 * i + 1] = P.bias ? __ldg(P.bias + (dbase + i) / P.drep) : 0.f;
+        smw[i] = P.mw ? __ldg(P.mw + dbase + i) : 1.f;
     }
+    for (int i = tid; i < CT * NPp; i += nthr) sdw[i] = 0.f;
     float2 ddecay_acc = bc(0.f);
 
     const int nblk = P.nck, npass = P.npass;
@@ -331,7 +335,15 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                     a1.z = fmaf(Dv, gv.z, a1.z); a1.w = fmaf(Dv, gv.w, a1.w);
                     a2.x *= sv.x; a2.y *= sv.y; a2.z *= sv.z; a2.w *= sv.w;
                     const int64_t o = ((int64_t)b * P.dim + sd) * H * P.Wout;
-                    st4d(P.du, o, P.Wout, pr0 + rr, c, H, W, fh, fw, P.io_dt, P.vec & VEC_DU, a1);
+                    if (P.mw) {  // direction merge: the sweep ran on the raw dy; w enters here
+                        const float wv = smw[pch0 + sc];
+                        a1.x *= wv; a1.y *= wv; a1.z *= wv; a1.w *= wv;
+                        a2.x *= wv; a2.y *= wv; a2.z *= wv; a2.w *= wv;
+                        red4d(reinterpret_cast<float *>(P.du), ((int64_t)b * P.dpg + sd - g_ * P.dpg) * H * P.Wout, P.Wout,
+                              pr0 + rr, c, H, W, fh, fw, a1);
+                    } else {
+                        st4d(P.du, o, P.Wout, pr0 + rr, c, H, W, fh, fw, P.io_dt, P.vec & VEC_DU, a1);
+                    }
                     st4d(P.ddelta, o, P.Wout, pr0 + rr, c, H, W, fh, fw, P.io_dt, P.vec & VEC_DU, a2);
                     // columns past the image carry g = 0 and ddl = 0
                     dDp = gv.x * uv.x + gv.y * uv.y + gv.z * uv.z + gv.w * uv.w;
@@ -501,7 +513,8 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
 #pragma unroll
                 for (int i = 0; i < STRIP; ++i) { m_dn[i] = bc(0.f); a_dn[i] = bc(0.f); }
             }
-            float2 dAacc = bc(0.f);
+            float2 dAacc = bc(0.f), dwacc = bc(0.f);
+            const float wv = smw[min(ch0 + cp, CT - 1)];   // 1 unless directions are merged
             // -- reverse sweep over the block --
             float2 hrow[STRIP], hup[STRIP];
             fetch8x2(slot_u + (RB - 1) * Wp, slot_d + (RB - 1) * Wp, L4, j, hrow);
@@ -643,8 +656,10 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                         ddv[i] = fmaf(uu[i], S1, t2.x + t2.y);
                         dAacc = fma2(bc(dl[i]), G, dAacc);
                         if (want_decay) ddecay_acc = add2(ddecay_acc, Gh);
-                        const float2 dBv = mul2(bc(dl[i] * uu[i]), eps);
-                        const float2 dCv = mul2(bc(gg[i]), fma2(p[i], bc(0.25f), sub2(hrow[i], s[i])));
+                        const float2 dBv = mul2(bc(dl[i] * uu[i] * wv), eps);
+                        const float2 yt = fma2(p[i], bc(0.25f), sub2(hrow[i], s[i]));
+                        const float2 dCv = mul2(bc(gg[i] * wv), yt);
+                        if (P.mw) dwacc = fma2(gC[i], yt, dwacc);   // dy * (C*(h - s + p/4)): this pair's share of dy*y
                         if constexpr (CW == 1) {
                             if (acc_on) {
                                 float2 *qb = accB + pos2<L>(j * STRIP + i), *qc = accC + pos2<L>(j * STRIP + i);
@@ -704,11 +719,15 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
             }
             if constexpr (L > 1) {
 #pragma unroll
-                for (int off = L / 2; off; off >>= 1) dAacc = add2(dAacc, shfl_xor2<L>(dAacc, off));
+                for (int off = L / 2; off; off >>= 1) {
+                    dAacc = add2(dAacc, shfl_xor2<L>(dAacc, off));
+                    dwacc = add2(dwacc, shfl_xor2<L>(dwacc, off));
+                }
             }
             if (j == 0 && ch_ok) {  // one owner per (channel, pair): no atomics needed
                 float *q = sdA + (ch0 + cp) * 2 * NPp + 2 * pp;
                 q[0] += dAacc.x; q[1] += dAacc.y;
+                sdw[(ch0 + cp) * NPp + pp] += dwacc.x + dwacc.y;
             }
         }
         cta_sync();
@@ -729,13 +748,23 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
         const int sc = i / (2 * NPp), n = i % (2 * NPp);
         if (n < N) {
             float *q = P.dA + (slot + dbase + sc) * N + n;
-            if (P.det) *q = sdA[i]; else atomicAdd(q, sdA[i]);
+            const float v = sdA[i] * smw[sc];
+            if (P.det) *q = v; else atomicAdd(q, v);
         }
     }
     for (int i = tid; i < nch * 2; i += nthr) {
         const int sd = dbase + i / 2;
         float v = 0.f;
         for (int q = 0; q < S::NSEG; ++q) v += sred[((i / 2) * S::NSEG + q) * 2 + (i & 1)];
+        // dD slots hold sum dy*u of the raw gradient: dD = w*that, and D*that is dw's D*u share
+        if ((i & 1) == 0) {
+            if (P.mw && P.dw) {
+                float dwv = spar[i] * v;
+                for (int q = 0; q < NPp; ++q) dwv += sdw[(i / 2) * NPp + q];
+                atomicAdd(P.dw + sd, dwv);
+            }
+            v *= smw[i / 2];
+        }
         float *q = (i & 1) == 0 ? P.dD : P.dbias;
         if (q) { if (P.det) q[slot + sd] = v; else atomicAdd(q + sd, v); }
     }

@@ -90,6 +90,13 @@ struct Dev {
     // [batch][dim], ddecay [grid]; a second kernel adds the planes and slots up in a fixed order.
     int det;
     int64_t det_ts;
+    // Direction merge (four-corner CrossScan with fusion weights w[dim], one per (direction,
+    // channel)): the forward ADDS w[d]*y_d onto an fp32 image out[batch][dim/G][H][W] shared by the
+    // G directions; the backward reads the shared raw gradient dy of that image (u_shared bit 1),
+    // ADDS w[d]*du_d onto an fp32 du[batch][dim/G][H][W], scales every other gradient of channel d
+    // by w[d] and accumulates dw[d] = sum dy*y_d.
+    const float *mw;
+    float *dw;
 };
 enum { VEC_U = 1, VEC_DELTA = 2, VEC_B = 4, VEC_C = 8, VEC_OUT = 16, VEC_DU = 32 };
 
@@ -253,6 +260,18 @@ __device__ __forceinline__ float lds1(const unsigned char *raw, int idx, int dt)
     if (dt == CS2D_F32) return reinterpret_cast<const float *>(raw)[idx];
     if (dt == CS2D_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(raw)[idx]);
     return __half2float(reinterpret_cast<const __half *>(raw)[idx]);
+}
+
+// out[...] += v for 4 consecutive SCAN columns c..c+3 of scan row r of an fp32 image plane
+// (several CTAs add onto the same image, one per scan direction)
+__device__ __forceinline__ void red4d(float *p, int64_t plane, int64_t hs, int r, int c, int H, int W, bool fh, bool fw,
+                                      float4 v) {
+    float *row = p + plane + (int64_t)(fh ? H - 1 - r : r) * hs;
+    const int nv = W - c;
+    const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        if (k < nv) atomicAdd(row + (fw ? W - 1 - (c + k) : c + k), e[k]);
 }
 
 // Direction-aware access to 4 consecutive SCAN columns c..c+3 of scan row r of an image plane

@@ -41,7 +41,7 @@ struct FwdSmem {
         return edl(CP, NPp, nw, tiled) + (tiled ? CP * 4 : 0);
     }
     static __host__ __device__ constexpr int bars(int CP, int NPp, int nw, bool tiled, int CT) {
-        return par(CP, NPp, nw, tiled) + ((2 * CT + 3) & ~3);
+        return par(CP, NPp, nw, tiled) + ((3 * CT + 3) & ~3);   // D, delta_bias, merge weight
     }
     static __host__ __device__ constexpr int raw(int CP, int NPp, int nw, bool tiled, int CT) {
         return bars(CP, NPp, nw, tiled, CT) + 4;
@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
     for (int i = tid; i < nch; i += nthr) {  // D and delta_bias of this CTA's channels
         spar[2 * i] = P.D ? __ldg(P.D + dbase + i) : 0.f;
         spar[2 * i + 1] = P.bias ? __ldg(P.bias + (dbase + i) / P.drep) : 0.f;
+        spar[2 * P.CT + i] = P.mw ? __ldg(P.mw + dbase + i) : 1.f;
     }
 
     const int nblk = P.nck;
@@ -281,8 +282,15 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
                         acc.x = fmaf(Dv, uv.x, acc.x); acc.y = fmaf(Dv, uv.y, acc.y);
                         acc.z = fmaf(Dv, uv.z, acc.z); acc.w = fmaf(Dv, uv.w, acc.w);
                     }
-                    st4d(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds, P.o_hs, pr0 + rr, c, H, W, fh, fw, P.out_dt,
-                         P.vec & VEC_OUT, acc);
+                    if (P.mw) {  // direction merge: add w*y onto the image shared by the directions
+                        const float wv = spar[2 * P.CT + pch0 + sc];
+                        acc.x *= wv; acc.y *= wv; acc.z *= wv; acc.w *= wv;
+                        red4d(reinterpret_cast<float *>(P.out), (int64_t)b * P.o_bs + (int64_t)(sd - g * P.dpg) * P.o_ds,
+                              P.o_hs, pr0 + rr, c, H, W, fh, fw, acc);
+                    } else {
+                        st4d(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds, P.o_hs, pr0 + rr, c, H, W, fh, fw, P.out_dt,
+                             P.vec & VEC_OUT, acc);
+                    }
                 }
             }
             if constexpr (WS) {
@@ -402,7 +410,7 @@ size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk, int CT, 
     const int CP = CG * (32 / L);
     // after the tiles: tile-edge areas (tiled kernels), the parameter copies, the mbarriers, then
     // either the raw row blocks of the bulk copies (two stages) or, warp-specialised, the second tile set
-    const size_t extra = (size_t)((tiled ? CP * NPp * (RB + 1) * 4 + CP * 4 : 0) + ((2 * CT + 3) & ~3)) * 4 + (ws ? 32 : 16) +
+    const size_t extra = (size_t)((tiled ? CP * NPp * (RB + 1) * 4 + CP * 4 : 0) + ((3 * CT + 3) & ~3)) * 4 + (ws ? 32 : 16) +
                          (bulk && !ws ? 2 * (size_t)CP * (2 * RB + 1) * W * es : 0);
     switch (L) {
         case 1: return smem_floats<1>(CP, NPp, nw, ws) * 4 + extra;

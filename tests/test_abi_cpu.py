@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
             "cs2d_abi_version", "cs2d_launch_count", "cs2d_device_status"} <= set(names)
     for n in names:
         assert hasattr(lib, n), n
-    assert _lib.lib().cs2d_abi_version() == 1
+    assert _lib.lib().cs2d_abi_version() == 2
 
 
 def _problem(**over):

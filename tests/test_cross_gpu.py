@@ -61,5 +61,6 @@ def test_evaluation_path_keeps_no_state_and_matches():
     y_train = cs2d.cross_scan_2d(*[a.clone().requires_grad_(True) if isinstance(a, torch.Tensor) else a for a in args])
     with torch.no_grad():
         y_eval = cs2d.cross_scan_2d(*args)
-    assert torch.equal(y_train.detach(), y_eval)
+    # the directions add onto the image with fp32 atomics: the order, hence the last bit, may differ
+    torch.testing.assert_close(y_train.detach(), y_eval, rtol=1e-5, atol=1e-6)
     assert cs2d.device_status() == 0
