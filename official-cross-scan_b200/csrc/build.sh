@@ -1,9 +1,11 @@
 #!/usr/bin/env bash
 # Builds the cs2d shared library in-tree for sm_100a.
 #   official-cross-scan_b200/csrc/build.sh [extra nvcc flags]
+# CS2D_OUT=<file> writes the library elsewhere, e.g. a profiling build with per-phase cycle
+# counters:  CS2D_OUT=/tmp/libcs2d_timers.so csrc/build.sh -DCS2D_PHASE_TIMERS
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-out="$here/../cs2d/libcs2d.so"
+out="${CS2D_OUT:-$here/../cs2d/libcs2d.so}"
 NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
 "$NVCC" -gencode arch=compute_100a,code=sm_100a -lineinfo -O3 -std=c++17 \
   -Xcompiler -fPIC -shared -cudart static --threads 3 "$@" \

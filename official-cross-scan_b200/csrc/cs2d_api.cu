@@ -186,6 +186,9 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
 }
 }  // namespace cs2d
 
+#ifdef CS2D_PHASE_TIMERS
+namespace cs2d { void phase_read_fwd(unsigned long long *); void phase_read_bwd(unsigned long long *); }
+#endif
 using namespace cs2d;
 
 extern "C" {
@@ -553,5 +556,17 @@ int cs2d_device_status(void) {
 const char *cs2d_last_error(void) { return g_err; }
 int cs2d_abi_version(void) { return CS2D_ABI_VERSION; }
 int64_t cs2d_launch_count(void) { return g_launches.load(); }
+
+int cs2d_phase_cycles(unsigned long long *out16) {
+#ifdef CS2D_PHASE_TIMERS
+    if (!out16) return fail(CS2D_ERR_INVALID, "out16 is NULL");
+    phase_read_fwd(out16);
+    phase_read_bwd(out16 + 8);
+    return CS2D_OK;
+#else
+    (void)out16;
+    return fail(CS2D_ERR_UNSUPPORTED, "this library was built without -DCS2D_PHASE_TIMERS");
+#endif
+}
 
 }  // extern "C"

@@ -27,6 +27,15 @@
 
 namespace cs2d {
 
+#ifdef CS2D_PHASE_TIMERS
+__device__ unsigned long long g_phase_bwd[8];
+void phase_read_bwd(unsigned long long *o) {
+    unsigned long long z[8] = {};
+    cudaMemcpyFromSymbol(o, g_phase_bwd, sizeof(z));
+    cudaMemcpyToSymbol(g_phase_bwd, z, sizeof(z));
+}
+#endif
+
 template <int L>
 struct BwdSmem {
     static constexpr int Wp = L * STRIP, CW = 32 / L;
@@ -270,6 +279,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     auto cta_sync = [&]() {
         if constexpr (WS) group_sync(1, WS_COMPUTE); else __syncthreads();
     };
+    PT_DECL
     for (int step = 0; step <= steps; ++step) {
         const int blk = nblk - 1 - step / npass, pass = step % npass;  // bottom-up
         const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
@@ -296,6 +306,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                 adj_pre[k] = (ok && r0 + RB < H) ? pa[k] : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
+        PT_MARK(PT_PREFETCH)
         // ---- phase A: write out the previous step, stage this one -------------------
         if (!WS && bulk) {
             if (warp == 0 && step + 1 < steps) issue(step + 1);   // lands while this step computes
@@ -306,6 +317,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                 return;
             }
         }
+        PT_MARK(PT_BULK_WAIT)
         {
             // tiles of the previous step (being written out) and of this one
             float *prev = WS && (pstep & 1) ? set1 : smem, *cur = WS && (step & 1) ? set1 : smem;
@@ -362,6 +374,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                     q[1] += dbp;
                 }
             }
+            PT_MARK(PT_WRITE_OUT)
             if constexpr (WS) {
                 // the previous step's tile set may be refilled by the staging warps from here on
                 if (step > 0) mbar_arrive(freeb + (pstep & 1));
@@ -369,6 +382,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                 // every thread replaces the tile entries it has just read (same item mapping)
                 stage_step(step, smem, raw + (size_t)(step & 1) * stage_bytes, tid, nthr);
             }
+            PT_MARK(PT_STAGE)
             // a row block is complete when its last pass has been written out
             if (acc_on && pnr > 0 && ppass == npass - 1) {
                 const int itemsB = NPp * RB * Wp;  // one float2 (two states) per item
@@ -432,6 +446,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                 }
             }
         }
+        PT_MARK(PT_FLUSH_BC)
         if constexpr (WS) {  // this step's tiles have to be complete
             const bool ok = nr == 0 || mbar_wait_bounded(full + (step & 1), (step >> 1) & 1);
             if (group_or(2, WS_COMPUTE, !ok)) {  // the staging warps stopped (they flagged why): leave together
@@ -440,6 +455,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
             }
         }
         cta_sync();
+        PT_MARK(PT_TILES_WAIT)
         if (nr == 0) break;
 
         // ---- compute ---------------------------------------------------------------------
@@ -497,6 +513,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                     }
                 }
             }
+            PT_MARK(PT_RECOMPUTE)
             // -- adjoint row below the block --
             float2 m_dn[STRIP], a_dn[STRIP];
             float2 *adj = P.adj + (((int64_t)b * P.dim + d) * NPp + pp) * Wp + j * STRIP;
@@ -731,7 +748,9 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
             }
         }
         cta_sync();
+        PT_MARK(PT_SWEEP)
     }
+    PT_FLUSH(g_phase_bwd)
 
     // ---- per-channel parameter gradients ---------------------------------------
     if (want_decay) {
