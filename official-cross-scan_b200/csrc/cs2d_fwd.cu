@@ -247,9 +247,8 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
         {
             const bool ok = nr > 0 && r0 > 0 && pair_on && ch0 + cp < nch;
             const int dq = dbase + min(ch0 + cp, nch - 1);
-            if (nr > 0 && pair_on)
-                A2 = f2(__ldg(P.A + dq * P.A_ds + n0 * P.A_ns) * LOG2E,
-                        n1 < N ? __ldg(P.A + dq * P.A_ds + n1 * P.A_ns) * LOG2E : 0.f);
+            if (nr > 0 && pair_on)   // raw values here; the scaling waits until they are used
+                A2 = f2(__ldg(P.A + dq * P.A_ds + n0 * P.A_ns), n1 < N ? __ldg(P.A + dq * P.A_ds + n1 * P.A_ns) : 0.f);
             const float4 *pk = reinterpret_cast<const float4 *>(
                 P.saved + ((((int64_t)b * P.dim + dq) * ckn + (P.ck_roll ? 0 : blk - 1)) * NPp + pp) * Wp + j * STRIP);
 #pragma unroll
@@ -356,6 +355,7 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
         if (pair_on) {
             const bool ch_ok = ch0 + cp < nch;
             const int d = dbase + min(ch0 + cp, nch - 1);
+            A2 = mul2(A2, bc(LOG2E));
             float2 h_up[STRIP], a_up[STRIP];
             float2 *ck = P.saved + ((((int64_t)b * P.dim + d) * ckn + (P.ck_roll ? 0 : blk)) * NPp + pp) * Wp + j * STRIP;
             if (r0 > 0) {
