@@ -202,7 +202,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default=DEFAULT_CONFIG)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--e2e-chunks", type=int, default=4, help="batch chunks of the host-buffer pipeline")
+    ap.add_argument("--e2e-chunks", type=int, default=0,
+                    help="batch chunks of the host-buffer pipeline (0: chosen by the library, about 32 MB each)")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling captures only)")
     ap.add_argument("--op", choices=("scan", "cross"), default="scan",
                     help="scan: the drop-in fwd/bwd operator (the headline); cross: the four-corner operator with "
@@ -331,14 +332,15 @@ def main():
     params = {"A": d["A"], "D": d["D"], "delta_bias": d["delta_bias"]}
 
     def e2e_step():
-        cs2d.fwd_bwd_from_host(host, params, hout, True, False, chunks=args.e2e_chunks, allreduce=world > 1)
+        cs2d.fwd_bwd_from_host(host, params, hout, True, False, chunks=args.e2e_chunks or None, allreduce=world > 1)
 
-    e2e_step()
+    for _ in range(3):   # the chunk shapes are new to the allocator and the kernels' attribute caches
+        e2e_step()
     torch.cuda.synchronize()
     e2e_steps = max(2, min(args.steps, 5))
     e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
     e2e = {"value": el_step / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "ms_per_step": e2e_ms, "chunks": args.e2e_chunks}
+           "ms_per_step": e2e_ms, "chunks": args.e2e_chunks or "auto (about 32 MB of input each)"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

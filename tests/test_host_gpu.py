@@ -10,7 +10,7 @@ from cs2d.synthetic import make_inputs
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("chunks", [1, 3, 8])
+@pytest.mark.parametrize("chunks", [1, 3, 8, None])
 def test_host_pipeline_matches_device_operators(chunks):
     inp = make_inputs(5, 2, 6, 4, 12, 16, dtype=torch.float32, seed=4)
     host = {k: inp[k].pin_memory() for k in ("u", "delta", "B", "C", "dout")}
