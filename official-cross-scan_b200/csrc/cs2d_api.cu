@@ -93,8 +93,8 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, 
         // The common geometry (8 state-pair slots, one channel group, one column tile) runs
         // warp-specialised when the second tile set fits: staging warps replace the bulk copies.
         static const bool ws_off = [] { const char *e = getenv("CS2D_BWD_WS"); return e && e[0] == '0'; }();
-        if (!ws_off && NPp == 8 && CG == 1 && !tiled &&
-            bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false, false, true) <= kMaxSmem) {
+        if (!ws_off && NPp == 8 && CG == 1 &&
+            bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false, tiled, true) <= kMaxSmem) {
             g->ws = 1;
             g->bulk = 0;
         }
@@ -106,8 +106,8 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, 
                         p->ncols, p->dstate);
         // warp-specialised like the backward, as long as two CTAs still share an SM
         static const bool fws_off = [] { const char *e = getenv("CS2D_FWD_WS"); return e && e[0] == '0'; }();
-        if (!fws_off && NPp == 8 && CG == 1 && !tiled &&
-            2 * (fwd_smem_bytes(L, CG, NPp, W, es, false, npass * CP, false, true) + kCtaReserve) <= kSmSmem) {
+        if (!fws_off && NPp == 8 && CG == 1 &&
+            2 * (fwd_smem_bytes(L, CG, NPp, W, es, false, npass * CP, tiled, true) + kCtaReserve) <= kSmSmem) {
             g->ws = 1;
             g->bulk = 0;
         }
@@ -200,7 +200,12 @@ extern "C" {
 // to left in the backward (each tile leaves dh and ds of its first column for its left
 // neighbour).  Stream order is the only synchronisation between tiles.
 static const int kTileCols = 32 * STRIP;
-static int n_tiles(int ncols) { return (ncols + kTileCols - 1) / kTileCols; }
+// Rows that need several tiles anyway are cut into 64-column tiles: those run the 8-lane kernels
+// (four channels per warp, dB/dC tiles in shared memory, warp-specialised), which cost far less per
+// element than the 32-lane ones a 256-column tile would use.
+static const int kNarrowTileCols = 8 * STRIP;
+static int tile_cols(int ncols) { return ncols > kTileCols ? kNarrowTileCols : kTileCols; }
+static int n_tiles(int ncols) { return (ncols + tile_cols(ncols) - 1) / tile_cols(ncols); }
 
 struct TileView {
     cs2d_problem q;   // the problem restricted to the tile (pointers moved, ncols = tile width)
@@ -216,9 +221,10 @@ static const char *at(const void *p, int64_t elems, int es) {
 // Fills `tv` for tile t and returns the bytes of the per-tile buffers; edge buffers follow them.
 static int tile_view(const cs2d_problem *p, int t, bool backward, bool bulk_ok, TileView *tv) {
     const int es = esize(p->io_dtype);
-    tv->c0 = t * kTileCols;
+    const int tc = tile_cols(p->ncols);
+    tv->c0 = t * tc;
     tv->q = *p;
-    tv->q.ncols = p->ncols - tv->c0 < kTileCols ? p->ncols - tv->c0 : kTileCols;
+    tv->q.ncols = p->ncols - tv->c0 < tc ? p->ncols - tv->c0 : tc;
     tv->q.u = at(p->u, tv->c0, es);
     tv->q.delta = at(p->delta, tv->c0, es);
     tv->q.B = at(p->B, tv->c0, es);

@@ -81,7 +81,7 @@ __device__ __forceinline__ void add_dbc(const Dev &P, int tile, int64_t og, bool
 // NPC = 8 specialises the common geometry (8 state-pair slots, one channel group, 8 warps) so
 // that every shared-memory offset is a compile-time constant; NPC = 0 reads it from P.
 // TILED compiles the column-tile edge handling in; the common single-tile launch leaves it out.
-// WS (with NPC = 8, not TILED) is the warp-specialised form: warps 0-7 compute as before and
+// WS (with NPC = 8) is the warp-specialised form: warps 0-7 compute as before and
 // write out the previous step, warps 8-11 load and transform (softplus, sigmoid) the tiles of
 // the NEXT step into a second tile set meanwhile, so that the staging - global-memory latency
 // and the transcendental chains - no longer sits between two compute phases.  The two groups
@@ -90,7 +90,7 @@ __device__ __forceinline__ void add_dbc(const Dev &P, int tile, int64_t og, bool
 constexpr int WS_COMPUTE = 256, WS_STAGE = 128, WS_REGS_COMPUTE = 232, WS_REGS_STAGE = 40;
 template <int L, int NPC, bool TILED, bool WS>
 __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) bwd_kernel(const Dev P) {
-    static_assert(!WS || (NPC == 8 && !TILED), "the warp-specialised form covers the common geometry only");
+    static_assert(!WS || NPC == 8, "the warp-specialised form covers the common geometry only");
     using S = BwdSmem<L>;
     constexpr int Wp = S::Wp, CW = S::CW, T4 = Wp / 4, CS4 = S::CS4, CS6 = S::CS6, L4 = 4 * L, L2 = 2 * L;
     constexpr int NU = CW >= 8 ? 1 : 8 / CW;  // columns of a strip owned by a lane after the channel sum
@@ -833,14 +833,14 @@ static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) 
 template <int L>
 static cudaError_t launch_L(const Dev &P, int grid, size_t smem, cudaStream_t st) {
     const bool spec = P.NPp == 8 && P.CG == 1, tiled = P.tile_left || P.tile_right;
-    if (P.ws) return launch<L, 8, false, true>(P, grid, smem, st);
+    if (P.ws) return tiled ? launch<L, 8, true, true>(P, grid, smem, st) : launch<L, 8, false, true>(P, grid, smem, st);
     return tiled ? (spec ? launch<L, 8, true, false>(P, grid, smem, st) : launch<L, 0, true, false>(P, grid, smem, st))
                  : (spec ? launch<L, 8, false, false>(P, grid, smem, st) : launch<L, 0, false, false>(P, grid, smem, st));
 }
 
 cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st) {
     const bool tiled = P.tile_left || P.tile_right;
-    if (P.ws && (P.NPp != 8 || P.CG != 1 || tiled)) return cudaErrorInvalidValue;
+    if (P.ws && (P.NPp != 8 || P.CG != 1)) return cudaErrorInvalidValue;
     const size_t smem = bwd_smem_bytes(L, P.CG, P.NPp, P.CT, P.acc_dbc != 0, P.W, P.io_dt == CS2D_F32 ? 4 : 2,
                                        P.out_dt == CS2D_F32 ? 4 : 2, P.bulk != 0, tiled, P.ws != 0);
     switch (L) {

@@ -63,7 +63,7 @@ struct FwdSmem {
 // NPC = 8 specialises the common geometry (8 state-pair slots, one channel group, 8 warps) so
 // that every shared-memory offset is a compile-time constant; NPC = 0 reads it from P.
 // TILED compiles the column-tile edge handling in; the common single-tile launch leaves it out.
-// WS (with NPC = 8, not TILED) is the warp-specialised form: warps 0-7 compute and write out the
+// WS (with NPC = 8) is the warp-specialised form: warps 0-7 compute and write out the
 // previous step, warps 8-11 load and transform (softplus) the tiles of the NEXT step into a
 // second tile set meanwhile; the groups meet on mbarriers (tile set full / free), every wait
 // bounded, and the staging warps give registers to the compute warps (setmaxnreg).  Two such
@@ -71,7 +71,7 @@ struct FwdSmem {
 constexpr int FWS_COMPUTE = 256, FWS_STAGE = 128, FWS_REGS_COMPUTE = 104, FWS_REGS_STAGE = 32;
 template <int L, int NPC, bool TILED, bool WS>
 __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2) fwd_kernel(const Dev P) {
-    static_assert(!WS || (NPC == 8 && !TILED), "the warp-specialised form covers the common geometry only");
+    static_assert(!WS || NPC == 8, "the warp-specialised form covers the common geometry only");
     using S = FwdSmem<L>;
     constexpr int Wp = S::Wp, CW = S::CW, T4 = Wp / 4, CS4 = S::CS4, CS5 = S::CS5, L4 = 4 * L, L2 = 2 * L;
     extern __shared__ __align__(16) float smem[];
@@ -457,14 +457,14 @@ static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) 
 template <int L>
 static cudaError_t launch_L(const Dev &P, int grid, size_t smem, cudaStream_t st) {
     const bool spec = P.NPp == 8 && P.CG == 1, tiled = P.tile_left || P.tile_right;
-    if (P.ws) return launch<L, 8, false, true>(P, grid, smem, st);
+    if (P.ws) return tiled ? launch<L, 8, true, true>(P, grid, smem, st) : launch<L, 8, false, true>(P, grid, smem, st);
     return tiled ? (spec ? launch<L, 8, true, false>(P, grid, smem, st) : launch<L, 0, true, false>(P, grid, smem, st))
                  : (spec ? launch<L, 8, false, false>(P, grid, smem, st) : launch<L, 0, false, false>(P, grid, smem, st));
 }
 
 cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st) {
     const bool tiled = P.tile_left || P.tile_right;
-    if (P.ws && (P.NPp != 8 || P.CG != 1 || tiled)) return cudaErrorInvalidValue;
+    if (P.ws && (P.NPp != 8 || P.CG != 1)) return cudaErrorInvalidValue;
     const size_t smem = fwd_smem_bytes(L, P.CG, P.NPp, P.W, P.io_dt == CS2D_F32 ? 4 : 2, P.bulk != 0, P.CT, tiled, P.ws != 0);
     switch (L) {
         case 1: return launch_L<1>(P, grid, smem, st);

@@ -48,11 +48,12 @@ def test_sizes_without_gpu():
     assert L.cs2d_bwd_scratch_bytes(ctypes.byref(p)) == 2 * 8 * 8 * 64 * 8
     p1 = _problem(dstate=1, nrows=7, ncols=7)
     assert L.cs2d_saved_bytes(ctypes.byref(p1)) == 2 * 8 * 2 * 1 * 8 * 8
-    # 336 columns = a 256-column tile + an 80-column tile (padded to 128) + one edge buffer
+    # 336 columns = five 64-column tiles + a 16-column tile, and one edge buffer per tile boundary
     pw = _problem(ncols=336)
     per = 2 * 8 * 8 * 8  # batch x dim x pair slots x bytes per float2
-    assert L.cs2d_saved_bytes(ctypes.byref(pw)) == per * 14 * (256 + 128) + 2 * 8 * 8 * 56 * 16
-    assert L.cs2d_bwd_scratch_bytes(ctypes.byref(pw)) == per * (256 + 128) + 2 * 8 * 8 * 56 * 16
+    edge = 2 * 8 * 8 * 56 * 16
+    assert L.cs2d_saved_bytes(ctypes.byref(pw)) == per * 14 * (5 * 64 + 16) + 5 * edge
+    assert L.cs2d_bwd_scratch_bytes(ctypes.byref(pw)) == per * (5 * 64 + 16) + 5 * edge
     # deterministic backward: per-channel-tile dB/dC planes + per-batch parameter slots + one slot per CTA
     det = L.cs2d_bwd_det_scratch_bytes(ctypes.byref(p))
     nB, slots = 2 * 4 * 16 * 56 * 56, 2 * 8 * (16 + 2)
@@ -60,7 +61,7 @@ def test_sizes_without_gpu():
     assert L.cs2d_bwd_det_scratch_bytes(ctypes.byref(pw)) == 0   # wider than one column tile
     # a forward that no backward follows keeps one rolling row instead of 14 checkpoints
     assert L.cs2d_fwd_only_scratch_bytes(ctypes.byref(p)) == 2 * 8 * 8 * 64 * 8
-    assert L.cs2d_fwd_only_scratch_bytes(ctypes.byref(pw)) == per * (256 + 128) + 2 * 8 * 8 * 56 * 16
+    assert L.cs2d_fwd_only_scratch_bytes(ctypes.byref(pw)) == per * (5 * 64 + 16) + 5 * edge
 
 
 @pytest.mark.parametrize("over,msg", [
