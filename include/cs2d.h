@@ -125,7 +125,7 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
  * bit 0: u has dim/n_groups channels that all groups read - channel d of group g
  * reads u channel d - g*dim/n_groups, u_ds being the stride of those channels;
  * bit 1: the same for dout in the backward.  out, du, ddelta keep `dim` channels
- * (one result per direction).  Not yet combined with ncols > 256.
+ * (one result per direction).
  *
  * Direction merge (merge_w != NULL): the weighted sum over the directions happens
  * inside the kernels.  merge_w holds one fp32 weight per channel (dim values:

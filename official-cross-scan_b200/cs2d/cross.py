@@ -21,9 +21,8 @@ read the same ``u`` (and, in the backward, the same ``dy``), and the weighted su
 over the directions happens inside the kernels as well (``cs2d_dirs.merge_w``):
 the forward adds ``w*y_k`` onto one fp32 image, the backward adds ``w*du_k`` onto
 one fp32 image, scales the other gradients by ``w`` and accumulates ``dw``.
-Nothing is flipped, replicated or kept per direction in memory.  Rows wider than
-256 columns take the composed path (materialised flips around ``ops.fwd`` /
-``ops.bwd``) until direction maps and column tiles are combined.
+Nothing is flipped, replicated or kept per direction in memory; rows wider than
+256 columns run as column tiles like the plain operator.
 """
 from __future__ import annotations
 
@@ -33,28 +32,11 @@ import torch
 
 from . import _lib, ops
 
-_FLIPS = ((), (-1,), (-2,), (-2, -1))  # k: 0 none, 1 columns, 2 rows, 3 both
-_MAX_DIRECT_COLS = 256
-
 
 def _masks(K):
     rows = sum(1 << k for k in range(K) if k % 4 in (2, 3))
     cols = sum(1 << k for k in range(K) if k % 4 in (1, 3))
     return rows, cols
-
-
-def _flip(t, k):
-    return torch.flip(t, _FLIPS[k % 4]) if _FLIPS[k % 4] else t
-
-
-def _to_scan(t, K, per_dir):
-    b, _, h, w = t.shape
-    v = t.view(b, K, per_dir, h, w)
-    return torch.stack([_flip(v[:, k], k) for k in range(K)], 1).reshape(b, K * per_dir, h, w)
-
-
-def _to_scan5(t):
-    return torch.stack([_flip(t[:, k], k) for k in range(t.size(1))], 1)
 
 
 def _ptr(t):
@@ -116,58 +98,35 @@ def _dir_backward(u, delta, A, B, C, w, D, delta_bias, dy, saved, delta_softplus
 class CrossScan2D(torch.autograd.Function):
     @staticmethod
     def forward(ctx, u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplus=True):
-        b, d, h, wd = u.shape
-        K = B.size(1)
-        if delta.size(1) != K * d or A.size(0) != K * d or tuple(w.shape) != (K, d):
-            raise RuntimeError("expected delta (b, K*D, h, w), A (K*D, n), w (K, D)")
-        ctx.direct = wd <= _MAX_DIRECT_COLS
+        _check_shapes(u, delta, A, B, w)
         ctx.delta_softplus = delta_softplus
-        if ctx.direct:
-            u, delta, B, C = u.contiguous(), delta.contiguous(), B.contiguous(), C.contiguous()
-            y, saved = _dir_forward(u, delta, A, B, C, w, D, delta_bias, delta_softplus)
-            ctx.save_for_backward(u, delta, A, B, C, D, delta_bias, w, saved)
-            return y.to(u.dtype)
-        else:
-            us = torch.cat([_flip(u, k) for k in range(K)], 1).contiguous()
-            ds = _to_scan(delta, K, d).contiguous()
-            Bs, Cs = _to_scan5(B).contiguous(), _to_scan5(C).contiguous()
-            out, x, x_v, x_sd = ops.fwd(us, ds, A, Bs, Cs, D, delta_bias, delta_softplus, True, None)
-            yk = torch.stack([_flip(out[:, k * d:(k + 1) * d], k) for k in range(K)], 1)
-            ctx.save_for_backward(us, ds, A, Bs, Cs, D, delta_bias, w, yk, x_v)
-        y = (yk * w.float()[None, :, :, None, None]).sum(1)
+        u, delta, B, C = u.contiguous(), delta.contiguous(), B.contiguous(), C.contiguous()
+        y, saved = _dir_forward(u, delta, A, B, C, w, D, delta_bias, delta_softplus)
+        ctx.save_for_backward(u, delta, A, B, C, D, delta_bias, w, saved)
         return y.to(u.dtype)
 
     @staticmethod
     def backward(ctx, dy):
-        if ctx.direct:
-            u, delta, A, B, C, D, delta_bias, w, saved = ctx.saved_tensors
-            if dy.stride(-1) != 1:
-                dy = dy.contiguous()
-            du, ddelta, dA, dB, dC, dw, dD, dbias = _dir_backward(u, delta, A, B, C, w, D, delta_bias, dy, saved,
-                                                                  ctx.delta_softplus)
-            return du, ddelta, dA, dB, dC, dw.to(w.dtype), dD, dbias, None
-        u, delta, A, B, C, D, delta_bias, w, yk, saved = ctx.saved_tensors
-        b, K, d, h, wd = yk.shape
-        dyf = dy.float()
-        dw = (dyf[:, None] * yk).sum((0, 3, 4)).to(w.dtype)
-        gk = dyf[:, None] * w.float()[None, :, :, None, None]   # (b, K, d, h, w): gradient of each y_k
-        g = torch.cat([_flip(gk[:, k], k) for k in range(K)], 1).contiguous()
-        empty = torch.empty(0, dtype=torch.float32, device=u.device)
-        du_s, dd_s, dA, dB_s, dC_s, dD, dbias, _ = ops.bwd(u, delta, A, B, C, D, delta_bias, g, empty, saved,
-                                                           ctx.delta_softplus, None, empty)
-        du = sum(_flip(du_s[:, k * d:(k + 1) * d].float(), k) for k in range(K)).to(u.dtype)
-        return du, _to_scan(dd_s, K, d), dA, _to_scan5(dB_s), _to_scan5(dC_s), dw, dD, dbias, None
+        u, delta, A, B, C, D, delta_bias, w, saved = ctx.saved_tensors
+        if dy.stride(-1) != 1:
+            dy = dy.contiguous()
+        du, ddelta, dA, dB, dC, dw, dD, dbias = _dir_backward(u, delta, A, B, C, w, D, delta_bias, dy, saved,
+                                                              ctx.delta_softplus)
+        return du, ddelta, dA, dB, dC, dw.to(w.dtype), dD, dbias, None
+
+
+def _check_shapes(u, delta, A, B, w):
+    d, K = u.size(1), B.size(1)
+    if delta.size(1) != K * d or A.size(0) != K * d or tuple(w.shape) != (K, d):
+        raise RuntimeError("expected delta (b, K*D, h, w), A (K*D, n), w (K, D)")
 
 
 def cross_scan_2d(u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplus=True):
     """Differentiable four-corner CrossScan; see the module docstring for shapes."""
     needs_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad
                                                  for t in (u, delta, A, B, C, w, D, delta_bias))
-    if not needs_grad and u.size(-1) <= _MAX_DIRECT_COLS:  # evaluation: no saved state
-        b, d, h, wd = u.shape
-        K = B.size(1)
-        if delta.size(1) != K * d or A.size(0) != K * d or tuple(w.shape) != (K, d):
-            raise RuntimeError("expected delta (b, K*D, h, w), A (K*D, n), w (K, D)")
+    if not needs_grad:  # evaluation: no saved state
+        _check_shapes(u, delta, A, B, w)
         y, _ = _dir_forward(u.contiguous(), delta.contiguous(), A, B.contiguous(), C.contiguous(), w, D, delta_bias,
                             delta_softplus, keep_state=False)
         return y.to(u.dtype)

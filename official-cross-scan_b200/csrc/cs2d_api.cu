@@ -177,6 +177,7 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     d.adj = nullptr;
     d.det = 0; d.det_ts = 0;
     d.mw = nullptr; d.dw = nullptr;
+    d.cshift = 0;
     d.ck_roll = 0;
     d.status = nullptr;
     d.tile_left = d.tile_right = 0; d.Wout = p->ncols;
@@ -263,13 +264,18 @@ size_t cs2d_bwd_scratch_bytes(const cs2d_problem *p) { return layout_bytes(p, tr
 
 size_t cs2d_fwd_only_scratch_bytes(const cs2d_problem *p) { return layout_bytes(p, false, true); }
 
+// A group that walks the columns right-to-left sees the tile's scan columns at mirrored image
+// columns (Dev::cshift); 4-element accesses are only kept when that shift preserves 16-byte alignment.
+static void tile_flip(Dev &d, int ncols, int c0, int tw, int nt) {
+    if (nt <= 1 || !d.flip_w) return;
+    d.cshift = (int64_t)ncols - 2 * (int64_t)c0 - tw;
+    if (d.cshift % 8) d.vec = 0;
+}
+
 static int check_dirs(const cs2d_problem *p, const cs2d_dirs *o) {
     if (o && o->merge_w && p->A_decay) return fail(CS2D_ERR_UNSUPPORTED, "A_decay is not combined with the direction merge");
     if (!o || (!o->flip_rows_mask && !o->flip_cols_mask && !o->shared_input && !o->merge_w)) return CS2D_OK;
     if (p->n_groups > 32) return fail(CS2D_ERR_INVALID, "direction masks cover at most 32 groups");
-    if (n_tiles(p->ncols) > 1)
-        return fail(CS2D_ERR_UNSUPPORTED, "scan directions are not combined with column tiles (ncols > %d) yet",
-                    kTileCols);
     return CS2D_OK;
 }
 
@@ -312,7 +318,10 @@ static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_
         char *edges = reinterpret_cast<char *>(saved) + ck_total;
         d.edge_in = t > 0 ? reinterpret_cast<const float4 *>(edges + (size_t)(t - 1) * eb) : nullptr;
         d.edge_out = t + 1 < nt ? reinterpret_cast<float4 *>(edges + (size_t)t * eb) : nullptr;
-        if (dirs) { d.flip_h = o->flip_rows_mask; d.flip_w = o->flip_cols_mask; d.u_shared = o->shared_input; d.mw = o->merge_w; }
+        if (dirs) {
+            d.flip_h = o->flip_rows_mask; d.flip_w = o->flip_cols_mask; d.u_shared = o->shared_input; d.mw = o->merge_w;
+            tile_flip(d, p->ncols, tv.c0, tv.q.ncols, nt);
+        }
         cudaError_t e = launch_fwd(d, tv.g.L, tv.g.grid, reinterpret_cast<cudaStream_t>(stream));
         if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
         g_launches.fetch_add(1);
@@ -418,7 +427,7 @@ static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout,
         fill(d, &tv.q, tv.g);
         d.out = const_cast<char *>(at(dout, tv.c0, eso)); d.o_bs = dout_bs; d.o_ds = dout_ds; d.o_hs = dout_hs;
         if (vec_ok(d.out, eso, tv.q.ncols, {dout_bs, dout_ds, dout_hs})) d.vec |= VEC_OUT;
-        d.du = const_cast<char *>(at(du, tv.c0, es));
+        d.du = const_cast<char *>(at(du, tv.c0, o && o->merge_w ? 4 : es));   // the merged du image is fp32
         d.ddelta = const_cast<char *>(at(ddelta, tv.c0, es));
         if (vec_ok(d.du, es, tv.q.ncols, {(int64_t)p->ncols}) && vec_ok(d.ddelta, es, tv.q.ncols, {(int64_t)p->ncols}))
             d.vec |= VEC_DU;
@@ -436,6 +445,7 @@ static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout,
         if (dirs) {
             d.flip_h = o->flip_rows_mask; d.flip_w = o->flip_cols_mask; d.u_shared = o->shared_input;
             d.mw = o->merge_w; d.dw = o->merge_dw;
+            tile_flip(d, p->ncols, tv.c0, tv.q.ncols, nt);
         }
         if (det) {  // per-tile planes and per-batch slots instead of the results themselves
             if (dl.zero && cudaMemsetAsync(det + dl.dB, 0, (size_t)(2 * dl.ntiles * dl.nB) * sizeof(float),

@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     const bool fh = (P.flip_h >> g_) & 1u, fw = (P.flip_w >> g_) & 1u;  // scan direction of this group
     const int ush = (P.u_shared & 1) ? g_ * P.dpg : 0;                    // u indexed by channel - ush
     const int gsh = (P.u_shared & 2) ? g_ * P.dpg : 0;                    // dout indexed by channel - gsh
+    const int64_t cs = fw ? P.cshift : 0;                                 // see Dev::cshift
     uint64_t *bars = reinterpret_cast<uint64_t *>(sedl_r + (TILED ? CP * 8 : 0));
     unsigned char *raw = reinterpret_cast<unsigned char *>(bars + 2);
     const int stage_bytes = CP * W * (RB * es + RB * eso + (RB + 2) * es);
@@ -226,11 +227,11 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                     gv = lds4(raw_g, (sc * RB + rr) * W + c, P.out_dt);
                     xv = lds4(raw_dl, (sc * (RB + 2) + (r - lo)) * W + c, P.io_dt);
                 } else {
-                    uv = ld4d(P.u, (int64_t)b * P.u_bs + (int64_t)(sd - ush) * P.u_ds, P.u_hs, r, c, H, W, fh, fw,
+                    uv = ld4d(P.u, (int64_t)b * P.u_bs + (int64_t)(sd - ush) * P.u_ds + cs, P.u_hs, r, c, H, W, fh, fw,
                               P.io_dt, P.vec & VEC_U);
-                    gv = ld4d(P.out, (int64_t)b * P.o_bs + (int64_t)(sd - gsh) * P.o_ds, P.o_hs, r, c, H, W, fh, fw,
+                    gv = ld4d(P.out, (int64_t)b * P.o_bs + (int64_t)(sd - gsh) * P.o_ds + cs, P.o_hs, r, c, H, W, fh, fw,
                               P.out_dt, P.vec & VEC_OUT);
-                    xv = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, r, c, H, W, fh, fw,
+                    xv = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + cs, P.dl_hs, r, c, H, W, fh, fw,
                               P.io_dt, P.vec & VEC_DELTA);
                 }
                 soft4(xv, sv, spar[2 * (kch0 + sc) + 1], P.softplus, W - c);
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                     if (!WS && bulk)
                         x = lds1(raw_dl, (sc * (RB + 2) + (r - lo)) * W + c, P.io_dt);
                     else
-                        x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds +
+                        x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + cs +
                                                  (int64_t)(fh ? H - 1 - r : r) * P.dl_hs + (fw ? W - 1 - c : c), P.io_dt);
                     x += spar[2 * (kch0 + sc) + 1];
                     if (P.softplus) x = softplus20(x);
@@ -346,12 +347,12 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                     a1.x = fmaf(Dv, gv.x, a1.x); a1.y = fmaf(Dv, gv.y, a1.y);
                     a1.z = fmaf(Dv, gv.z, a1.z); a1.w = fmaf(Dv, gv.w, a1.w);
                     a2.x *= sv.x; a2.y *= sv.y; a2.z *= sv.z; a2.w *= sv.w;
-                    const int64_t o = ((int64_t)b * P.dim + sd) * H * P.Wout;
+                    const int64_t o = ((int64_t)b * P.dim + sd) * H * P.Wout + cs;
                     if (P.mw) {  // direction merge: the sweep ran on the raw dy; w enters here
                         const float wv = smw[pch0 + sc];
                         a1.x *= wv; a1.y *= wv; a1.z *= wv; a1.w *= wv;
                         a2.x *= wv; a2.y *= wv; a2.z *= wv; a2.w *= wv;
-                        red4d(reinterpret_cast<float *>(P.du), ((int64_t)b * P.dpg + sd - g_ * P.dpg) * H * P.Wout, P.Wout,
+                        red4d(reinterpret_cast<float *>(P.du), ((int64_t)b * P.dpg + sd - g_ * P.dpg) * H * P.Wout + cs, P.Wout,
                               pr0 + rr, c, H, W, fh, fw, a1);
                     } else {
                         st4d(P.du, o, P.Wout, pr0 + rr, c, H, W, fh, fw, P.io_dt, P.vec & VEC_DU, a1);
@@ -396,7 +397,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                     }
                     if (c < W && rr < pnr && 2 * spp < N) {
                         const int64_t og = ((((int64_t)b * P.G + g_) * N + 2 * spp) * H + (fh ? H - 1 - (pr0 + rr) : pr0 + rr)) * P.Wout +
-                                           (fw ? W - 1 - c : c);
+                                           (fw ? W - 1 - c : c) + cs;
                         if (P.det) {  // this channel tile's own plane: each element has one writer
                             float *qb = P.dB + (int64_t)tile * P.det_ts + og, *qc = P.dC + (int64_t)tile * P.det_ts + og;
                             qb[0] = vb.x; qc[0] = vc.x;
@@ -431,13 +432,14 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                     if (ch0 + sc < nch) {
                         const int sdd = (dbase + ch0 + sc) / P.drep;
                         const float bv = P.bias ? __ldg(P.bias + sdd) : 0.f;
-                        const int64_t row0 = (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds;
-                        if (has_left && k < nr) {
-                            xl = ld_elem(P.delta, row0 + (int64_t)(r0 + k) * P.dl_hs - 1, P.io_dt) + bv;
+                        const int64_t row0 = (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + cs +
+                                             (int64_t)(fh ? H - 1 - (r0 + k) : r0 + k) * P.dl_hs;
+                        if (has_left && k < nr) {   // scan column -1
+                            xl = ld_elem(P.delta, row0 + (fw ? W : -1), P.io_dt) + bv;
                             if (P.softplus) xl = softplus20(xl);
                         }
                         if (has_right && k <= RB && r0 + k < H) {
-                            xr = ld_elem(P.delta, row0 + (int64_t)(r0 + k) * P.dl_hs + W, P.io_dt) + bv;
+                            xr = ld_elem(P.delta, row0 + (fw ? -1 : W), P.io_dt) + bv;   // scan column W
                             if (P.softplus) xr = softplus20(xr);
                         }
                     }
@@ -684,7 +686,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                                 *qc = add2(*qc, dCv);
                             } else if (ch_ok && j * STRIP + i < W) {
                                 const int64_t og = ((((int64_t)b * P.G + g_) * N + n0) * H + (fh ? H - 1 - (r0 + rr) : r0 + rr)) * P.Wout +
-                                                   (fw ? W - 1 - (j * STRIP + i) : j * STRIP + i);
+                                                   (fw ? W - 1 - (j * STRIP + i) : j * STRIP + i) + cs;
                                 add_dbc(P, tile, og, n1 < N, dBv, dCv);
                             }
                         } else {
@@ -717,7 +719,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                                 } else if (j * STRIP + col < W) {
                                     const int64_t og =
                                         ((((int64_t)b * P.G + g_) * N + n0) * H + (fh ? H - 1 - (r0 + rr) : r0 + rr)) * P.Wout +
-                                        (fw ? W - 1 - (j * STRIP + col) : j * STRIP + col);
+                                        (fw ? W - 1 - (j * STRIP + col) : j * STRIP + col) + cs;
                                     add_dbc(P, tile, og, n1 < N, sb, sc2);
                                 }
                             }

@@ -97,6 +97,10 @@ struct Dev {
     // by w[d] and accumulates dw[d] = sum dy*y_d.
     const float *mw;
     float *dw;
+    // Column tiles of a group that walks the columns right-to-left: the launch's scan columns
+    // c0..c0+W-1 are image columns Wfull-c0-W..Wfull-c0-1, so every tensor access of such a group
+    // adds cshift = Wfull - 2*c0 - W elements to the (c0-shifted) pointers.  0 without tiles.
+    int64_t cshift;
 };
 enum { VEC_U = 1, VEC_DELTA = 2, VEC_B = 4, VEC_C = 8, VEC_OUT = 16, VEC_DU = 32 };
 
@@ -555,6 +559,7 @@ __device__ __forceinline__ void row_forward(int j, const float (&dl)[STRIP], con
 template <int L>
 __device__ __forceinline__ void stage_BC(const Dev &P, int b, int g, int r0, int nr, float2 *sB, float2 *sC,
                                          bool fh, bool fw, int tid, int nthr) {
+    const int64_t cs = fw ? P.cshift : 0;
     constexpr int Wp = L * STRIP, T4 = Wp / 4;
     const int items = P.NPp * RB * T4;
     for (int it = tid; it < items; it += nthr) {
@@ -563,7 +568,7 @@ __device__ __forceinline__ void stage_BC(const Dev &P, int b, int g, int r0, int
         float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0, c0 = b0, c1 = b0;
         if (rr < nr && n0 < P.N) {
             const int r = r0 + rr;
-            const int64_t ob = (int64_t)b * P.B_bs + (int64_t)g * P.B_gs, oc = (int64_t)b * P.C_bs + (int64_t)g * P.C_gs;
+            const int64_t ob = (int64_t)b * P.B_bs + (int64_t)g * P.B_gs + cs, oc = (int64_t)b * P.C_bs + (int64_t)g * P.C_gs + cs;
             b0 = ld4d(P.B, ob + (int64_t)n0 * P.B_ns, P.B_hs, r, c, P.H, P.W, fh, fw, P.io_dt, P.vec & VEC_B);
             c0 = ld4d(P.C, oc + (int64_t)n0 * P.C_ns, P.C_hs, r, c, P.H, P.W, fh, fw, P.io_dt, P.vec & VEC_C);
             if (n0 + 1 < P.N) {

@@ -95,6 +95,7 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
     const int g = bg % P.G, b = bg / P.G;
     const bool fh = (P.flip_h >> g) & 1u, fw = (P.flip_w >> g) & 1u;  // scan direction of this group
     const int ush = (P.u_shared & 1) ? g * P.dpg : 0;                        // u is indexed by channel - ush
+    const int64_t cs = fw ? P.cshift : 0;                                    // see Dev::cshift
     const int dbase = g * P.dpg + tile * P.CT;
     const int nch = min(P.CT, (g + 1) * P.dpg - dbase);  // valid channels of this CTA
     const int H = P.H, W = P.W, N = P.N;
@@ -180,9 +181,9 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
                     uv = lds4(raw_u, (sc * RB + rr) * W + c, P.io_dt);
                     x = lds4(raw_dl, (sc * (RB + 1) + (kr0 + rr - lo)) * W + c, P.io_dt);
                 } else {
-                    uv = ld4d(P.u, (int64_t)b * P.u_bs + (int64_t)(dbase + kch0 + sc - ush) * P.u_ds, P.u_hs, kr0 + rr, c,
+                    uv = ld4d(P.u, (int64_t)b * P.u_bs + (int64_t)(dbase + kch0 + sc - ush) * P.u_ds + cs, P.u_hs, kr0 + rr, c,
                               H, W, fh, fw, P.io_dt, P.vec & VEC_U);
-                    x = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds, P.dl_hs, kr0 + rr, c, H, W, fh, fw,
+                    x = ld4d(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + cs, P.dl_hs, kr0 + rr, c, H, W, fh, fw,
                              P.io_dt, P.vec & VEC_DELTA);
                 }
                 const float bv = spar[2 * (kch0 + sc) + 1];
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
                     if (!WS && bulk)
                         x = lds1(raw_dl, sc * (RB + 1) * W + c, P.io_dt);
                     else
-                        x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds +
+                        x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + cs +
                                                  (int64_t)(fh ? H - 1 - r : r) * P.dl_hs + (fw ? W - 1 - c : c), P.io_dt);
                     x += spar[2 * (kch0 + sc) + 1];
                     if (P.softplus) x = softplus20(x);
@@ -296,10 +297,10 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
                     if (P.mw) {  // direction merge: add w*y onto the image shared by the directions
                         const float wv = spar[2 * P.CT + pch0 + sc];
                         acc.x *= wv; acc.y *= wv; acc.z *= wv; acc.w *= wv;
-                        red4d(reinterpret_cast<float *>(P.out), (int64_t)b * P.o_bs + (int64_t)(sd - g * P.dpg) * P.o_ds,
+                        red4d(reinterpret_cast<float *>(P.out), (int64_t)b * P.o_bs + (int64_t)(sd - g * P.dpg) * P.o_ds + cs,
                               P.o_hs, pr0 + rr, c, H, W, fh, fw, acc);
                     } else {
-                        st4d(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds, P.o_hs, pr0 + rr, c, H, W, fh, fw, P.out_dt,
+                        st4d(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + cs, P.o_hs, pr0 + rr, c, H, W, fh, fw, P.out_dt,
                              P.vec & VEC_OUT, acc);
                     }
                 }
@@ -329,8 +330,8 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
                         float x = 0.f;
                         if (rr < nr && ch0 + sc < nch) {
                             const int sdd = (dbase + ch0 + sc) / P.drep;
-                            x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds +
-                                                     (int64_t)(r0 + rr) * P.dl_hs - 1, P.io_dt);
+                            x = ld_elem(P.delta, (int64_t)b * P.dl_bs + (int64_t)sdd * P.dl_ds + cs +
+                                                     (int64_t)(fh ? H - 1 - (r0 + rr) : r0 + rr) * P.dl_hs + (fw ? W : -1), P.io_dt);
                             if (P.bias) x += __ldg(P.bias + sdd);
                             if (P.softplus) x = softplus20(x);
                         }

@@ -13,7 +13,8 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("shape,dtype", [((2, 4, 3, 4, 6, 9), torch.float32), ((1, 4, 4, 16, 8, 8), torch.bfloat16),
-                                         ((1, 4, 2, 2, 5, 13), torch.float32), ((1, 4, 1, 2, 3, 260), torch.float32)])
+                                         ((1, 4, 2, 2, 5, 13), torch.float32), ((1, 4, 1, 2, 3, 260), torch.float32),
+                                         ((1, 4, 2, 16, 5, 336), torch.float32), ((2, 4, 3, 9, 6, 300), torch.bfloat16)])
 def test_cross_scan_forward_and_gradients(shape, dtype):
     b, K, d, n, h, w = shape
     inp = make_inputs(b, K, d, n, h, w, dtype=dtype, seed=2)
