@@ -111,3 +111,14 @@ def test_missing_library_is_an_error_not_a_fallback(monkeypatch):
 def test_drop_in_module_name():
     import selective_nd_scan_cuda_oflex as ext
     assert ext.fwd is ops.fwd and ext.bwd is ops.bwd
+
+
+def test_abi_version_is_consistent_everywhere():
+    """The header, the Python binding and the build entry point name the same ABI version."""
+    header = open(os.path.join(ROOT, "include", "cs2d.h")).read()
+    version = int(re.search(r"#define CS2D_ABI_VERSION (\d+)", header).group(1))
+    assert _lib.lib().cs2d_abi_version() == version
+    binding = open(os.path.join(ROOT, "official-cross-scan_b200", "cs2d", "_lib.py")).read()
+    assert f"cs2d_abi_version() != {version}" in binding
+    entry = open(os.path.join(ROOT, "__graft_entry__.py")).read()
+    assert f"cs2d_abi_version() == {version}" in entry
