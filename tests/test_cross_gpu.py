@@ -53,15 +53,17 @@ def test_module_trains_all_parameters():
         assert p.grad is not None and torch.isfinite(p.grad).all() and p.grad.abs().sum() > 0, name
 
 
-def test_evaluation_path_keeps_no_state_and_matches():
-    inp = make_inputs(2, 4, 5, 16, 12, 20, seed=3)
-    u0 = torch.randn(2, 5, 12, 20, device="cuda")
-    w = torch.rand(4, 5, device="cuda") + 0.1
+@pytest.mark.parametrize("shape", [(2, 4, 5, 16, 12, 20), (1, 4, 3, 9, 6, 300)])
+def test_evaluation_path_keeps_no_state_and_matches(shape):
+    b, K, d, n, h, w_ = shape
+    inp = make_inputs(b, K, d, n, h, w_, seed=3)
+    u0 = torch.randn(b, d, h, w_, device="cuda")
+    w = torch.rand(K, d, device="cuda") + 0.1
     dev = {k: (v.cuda() if v is not None else None) for k, v in inp.items()}
     args = (u0, dev["delta"], dev["A"], dev["B"], dev["C"], w, dev["D"], dev["delta_bias"], True)
     y_train = cs2d.cross_scan_2d(*[a.clone().requires_grad_(True) if isinstance(a, torch.Tensor) else a for a in args])
     with torch.no_grad():
         y_eval = cs2d.cross_scan_2d(*args)
     # the directions add onto the image with fp32 atomics: the order, hence the last bit, may differ
-    torch.testing.assert_close(y_train.detach(), y_eval, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(y_train.detach(), y_eval, rtol=1e-5, atol=1e-5)
     assert cs2d.device_status() == 0
