@@ -131,10 +131,13 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     if (acc_on)
         for (int i = tid; i < nw * RB * Wp; i += nthr) { saB[i] = bc(0.f); saC[i] = bc(0.f); }
     for (int i = tid; i < CT * 2 * NPp + CT * S::NSEG * 2 + nw; i += nthr) sdA[i] = 0.f;
-    for (int i = tid; i < nch; i += nthr) {  // D and delta_bias of this CTA's channels
-        spar[2 * i] = P.D ? __ldg(P.D + dbase + i) : 0.f;
-        spar[2 * i + 1] = P.bias ? __ldg(P.bias + (dbase + i) / P.drep) : 0.f;
-        smw[i] = P.mw ? __ldg(P.mw + dbase + i) : 1.f;
+    // D, delta_bias and merge weight of this CTA's channels; slots past the last valid channel
+    // are read too (their staged values are zero, so the weight has to be finite)
+    for (int i = tid; i < CT; i += nthr) {
+        const bool on = i < nch;
+        spar[2 * i] = on && P.D ? __ldg(P.D + dbase + i) : 0.f;
+        spar[2 * i + 1] = on && P.bias ? __ldg(P.bias + (dbase + i) / P.drep) : 0.f;
+        smw[i] = on && P.mw ? __ldg(P.mw + dbase + i) : 1.f;
     }
     for (int i = tid; i < CT * NPp; i += nthr) sdw[i] = 0.f;
     float2 ddecay_acc = bc(0.f);

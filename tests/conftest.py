@@ -15,38 +15,76 @@ GOLDEN = sorted(glob.glob(os.path.join(ROOT, "tests", "golden", "*.npz")))
 # Tolerances of the operator contract: y and every gradient within
 # rtol 1e-4 / atol 1e-5 for fp32 I/O and rtol 2e-2 / atol 1e-3 for 16-bit I/O.
 TOL = {"float32": (1e-4, 1e-5), "bfloat16": (2e-2, 1e-3), "float16": (2e-2, 1e-3)}
-# dA, dD, ddelta_bias, dA_decay are sums of batch*H*W (and more) fp32 terms with
-# cancellation; both the reference (fp32 atomics, run-to-run different) and the
-# kernels here carry rounding noise proportional to the number of terms, so
-# they get ten times the element tolerance, judged against the float64 oracle.
+# dA, dD, ddelta_bias, dA_decay are sums over batch*H*W (and more) fp32 terms.  They are held
+# to the same element tolerance as everything else; `REDUCED` only names them for the tests
+# that compare two fp32-atomic runs with each other.
 REDUCED = ("dA", "dD", "ddelta_bias", "dA_decay")
+
+# worst err/tol ratio seen per (test, tensor); written as JSON to the file named by the
+# environment variable CS2D_MARGINS_JSON at the end of the session, so that the margin of every
+# parity check is on record, not just pass/fail
+MARGINS = {}
+_current = {"id": ""}
 
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
 
 
-def check_close(name, got, ref, rtol, atol, outlier_frac=2e-5):
-    """allclose with a bounded number of fp32-noise outliers.
+@pytest.fixture(autouse=True)
+def _margin_scope(request):
+    _current["id"] = request.node.nodeid
+    yield
+    _current["id"] = ""
 
-    A handful of elements out of 1e5..1e9 sit on cancellations where fp32
-    evaluation order moves the result by a few atol; the reference extension
-    misses the float64 oracle on the same elements.  Up to ``outlier_frac`` of
-    the elements may exceed the tolerance, by at most a factor of eight.
+
+def pytest_sessionfinish(session, exitstatus):
+    if not MARGINS:
+        return
+    path = os.environ.get("CS2D_MARGINS_JSON")
+    if not path:
+        return
+    import json
+    try:
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        worst = {}
+        for (test, name), r in MARGINS.items():
+            base = name.split("[")[0]
+            worst[base] = max(worst.get(base, 0.0), r)
+        with open(path, "w") as f:
+            json.dump({"worst_ratio_per_tensor": worst,
+                       "per_check": {f"{t}::{n}": r for (t, n), r in sorted(MARGINS.items())}}, f, indent=1)
+    except OSError:
+        pass
+
+
+def check_close(name, got, ref, rtol, atol, outlier_frac=0.0, outlier_factor=1.0):
+    """Element-wise |got - ref| <= atol + rtol*|ref| for EVERY element; returns the worst
+    err/tol ratio (<= 1 when the check passes) and records it in MARGINS.
+
+    ``outlier_frac`` / ``outlier_factor`` relax this for the few callers that compare two
+    fp32-atomic results with each other: that fraction of the elements may exceed the tolerance
+    by at most that factor.  The parity tests against the reference's golden vectors and
+    against the float64 oracle use the defaults (no allowance).
     """
     got = np.asarray(got, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
     assert got.shape == ref.shape, f"{name}: shape {got.shape} vs {ref.shape}"
     assert np.isfinite(got).all(), f"{name}: non-finite values"
+    if got.size == 0:
+        return 0.0
     err = np.abs(got - ref)
     tol = atol + rtol * np.abs(ref)
-    bad = err > tol
-    nbad = int(bad.sum())
+    ratio = err / tol
+    worst = float(ratio.max())
+    key = (_current["id"], name)
+    MARGINS[key] = max(MARGINS.get(key, 0.0), worst)
+    nbad = int((ratio > 1.0).sum())
     if nbad:
-        worst = float((err / tol).max())
-        assert nbad <= max(1, int(outlier_frac * err.size)) and worst <= 8.0, (
-            f"{name}: {nbad}/{err.size} elements out of tolerance, worst {worst:.1f}x "
+        assert nbad <= int(outlier_frac * err.size) and worst <= outlier_factor, (
+            f"{name}: {nbad}/{err.size} elements out of tolerance, worst {worst:.2f}x "
             f"(max abs err {err.max():.3e}, max |ref| {np.abs(ref).max():.3e})")
+    return worst
 
 
 def load_golden(path):
