@@ -12,6 +12,9 @@
 namespace cs2d {
 cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st);
 cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st);
+cudaError_t launch_stream_fwd(const Dev &P, int L, int grid, cudaStream_t st);
+cudaError_t launch_stream_bwd(const Dev &P, int L, int grid, cudaStream_t st);
+int stream_pairs_per_cta(int L);
 size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk, int CT, bool tiled, bool ws);
 size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk, bool tiled, bool ws);
 static __device__ int g_cs2d_status = 0;  // see ERR_* in cs2d_common.cuh
@@ -179,6 +182,7 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     d.mw = nullptr; d.dw = nullptr;
     d.cshift = 0;
     d.ck_roll = 0;
+    d.ck_pairs = 0;
     d.status = nullptr;
     d.tile_left = d.tile_right = 0; d.Wout = p->ncols;
     d.flip_h = d.flip_w = 0; d.u_shared = 0;
@@ -279,18 +283,63 @@ static int check_dirs(const cs2d_problem *p, const cs2d_dirs *o) {
     return CS2D_OK;
 }
 
+// ---- streaming kernels (cs2d_stream.cu) -------------------------------------------------------
+// A problem with a single state per channel, one scan orientation, no A_decay and rows of at most
+// 256 columns runs on the streaming kernels: no shared-memory tiles, no backward scratch, and
+// checkpoints that pack two channels per value (half the bytes of the tile kernels' layout, which
+// is what cs2d_saved_bytes reports and therefore always large enough).  The choice depends on
+// nothing but these properties, so the forward and the backward of a problem always agree.
+static bool has_dirs(const cs2d_dirs *o) {
+    return o && (o->flip_rows_mask || o->flip_cols_mask || o->shared_input || o->merge_w);
+}
+static bool stream_ok(const cs2d_problem *p, const cs2d_dirs *o) {
+    return p->dstate == 1 && !has_dirs(o) && !p->A_decay && p->ncols <= kTileCols;
+}
+static int stream_lanes(const cs2d_problem *p) {
+    const int strips = (p->ncols + STRIP - 1) / STRIP;
+    int L = 1;
+    while (L < strips) L <<= 1;
+    return L;
+}
+// Geometry shared by both streaming launches: lanes per row, CTAs per (batch, group), grid.
+static void stream_fill(Dev &d, const cs2d_problem *p, int *L, int *grid) {
+    Geometry g = {};
+    g.L = stream_lanes(p);
+    g.NPp = 1; g.CG = 1; g.CP = 1; g.CT = 1; g.npass = 1;
+    const int npairs = (p->dim / p->n_groups + 1) / 2, pc = stream_pairs_per_cta(g.L);
+    g.ntiles = (npairs + pc - 1) / pc;
+    g.nck = (p->nrows + STREAM_RB - 1) / STREAM_RB;
+    g.grid = p->batch * p->n_groups * g.ntiles;
+    fill(d, p, g);
+    *L = g.L; *grid = g.grid;
+}
+
 static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_t out_bs, int64_t out_ds,
                     int64_t out_hs, void *saved, void *stream, bool rolling = false) {
     int rc = validate(p);
     if (rc) return rc;
     if ((rc = check_dirs(p, o))) return rc;
-    const bool dirs = o && (o->flip_rows_mask || o->flip_cols_mask || o->shared_input || o->merge_w);
+    const bool dirs = has_dirs(o);
     if (!out || !saved) return fail(CS2D_ERR_INVALID, "out and saved must be given");
     if (o && o->merge_w && p->out_dtype != CS2D_F32)
         return fail(CS2D_ERR_INVALID, "the direction merge adds onto an fp32 image: out_dtype must be CS2D_F32");
     if (reinterpret_cast<uintptr_t>(saved) & 15) return fail(CS2D_ERR_INVALID, "saved must be 16-byte aligned");
     int *status = status_ptr();
     if (!status) return fail(CS2D_ERR_CUDA, "cannot locate the device status word");
+    if (stream_ok(p, o)) {
+        Dev d;
+        int L, grid;
+        stream_fill(d, p, &L, &grid);
+        d.out = out; d.o_bs = out_bs; d.o_ds = out_ds; d.o_hs = out_hs;
+        if (vec_ok(out, esize(p->out_dtype), p->ncols, {out_bs, out_ds, out_hs})) d.vec |= VEC_OUT;
+        d.saved = reinterpret_cast<float2 *>(saved);
+        d.ck_roll = rolling;
+        d.status = status;
+        cudaError_t e = launch_stream_fwd(d, L, grid, reinterpret_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
+        g_launches.fetch_add(1);
+        return CS2D_OK;
+    }
     const int es = esize(p->io_dtype), eso = esize(p->out_dtype), nt = n_tiles(p->ncols);
     // saved = [checkpoints tile 0 | ... | checkpoints tile nt-1 | edge 0|1 | ... | edge nt-2|nt-1]
     size_t ck_total = 0;
@@ -406,6 +455,25 @@ static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout,
     if (dA_decay && !p->A_decay) return fail(CS2D_ERR_INVALID, "dA_decay requested without A_decay");
     int *status = status_ptr();
     if (!status) return fail(CS2D_ERR_CUDA, "cannot locate the device status word");
+    const bool streamed = stream_ok(p, o);   // the forward of this problem ran on the streaming kernel
+    if (streamed && !det) {
+        Dev d;
+        int L, grid;
+        stream_fill(d, p, &L, &grid);
+        d.out = const_cast<void *>(dout); d.o_bs = dout_bs; d.o_ds = dout_ds; d.o_hs = dout_hs;
+        if (vec_ok(dout, esize(p->out_dtype), p->ncols, {dout_bs, dout_ds, dout_hs})) d.vec |= VEC_OUT;
+        d.du = du; d.ddelta = ddelta;
+        if (vec_ok(du, esize(p->io_dtype), p->ncols, {(int64_t)p->ncols}) &&
+            vec_ok(ddelta, esize(p->io_dtype), p->ncols, {(int64_t)p->ncols}))
+            d.vec |= VEC_DU;
+        d.saved = reinterpret_cast<float2 *>(const_cast<void *>(saved));
+        d.dA = dA; d.dB = dB; d.dC = dC; d.dD = dD; d.dbias = ddelta_bias;
+        d.status = status;
+        cudaError_t e = launch_stream_bwd(d, L, grid, reinterpret_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
+        g_launches.fetch_add(1);
+        return CS2D_OK;
+    }
     const int es = esize(p->io_dtype), eso = esize(p->out_dtype), nt = n_tiles(p->ncols);
     // saved as laid out by the forward; scratch = [adjoint rows tile 0 | ... | dh/ds edges]
     size_t ck_total = 0, adj_total = 0;
@@ -435,6 +503,7 @@ static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout,
         d.adj = reinterpret_cast<float2 *>(reinterpret_cast<char *>(scratch) + adj_offs[t]);
         d.dA = dA; d.dB = dB + tv.c0; d.dC = dC + tv.c0; d.dD = dD; d.dbias = ddelta_bias; d.ddecay = dA_decay;
         d.status = status;
+        d.ck_pairs = streamed;   // deterministic backward of a streamed forward: read its checkpoint layout
         d.tile_left = t > 0; d.tile_right = t + 1 < nt; d.Wout = p->ncols;
         const size_t eb = edge_bytes(p, tv.g.NPp);
         const char *edges = reinterpret_cast<const char *>(saved) + ck_total;

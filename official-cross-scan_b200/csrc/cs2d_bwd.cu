@@ -27,6 +27,8 @@
 
 namespace cs2d {
 
+static_assert(RB == STREAM_RB, "the tile backward reads the streaming forward's checkpoints at its own row-block cadence");
+
 #ifdef CS2D_PHASE_TIMERS
 __device__ unsigned long long g_phase_bwd[8];
 void phase_read_bwd(unsigned long long *o) {
@@ -304,10 +306,24 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                 P.saved + ((((int64_t)b * P.dim + dq) * P.nck + (blk - 1)) * NPp + pp) * Wp + j * STRIP);
             const float4 *pa = reinterpret_cast<const float4 *>(
                 P.adj + (((int64_t)b * P.dim + dq) * NPp + pp) * Wp + j * STRIP);
+            if (P.ck_pairs) {
+                // checkpoints of the streaming forward (single state): one value holds channels 2q, 2q+1
+                // of the group
+                const int dl_ = dq - g_ * P.dpg;
+                const float4 *pq = reinterpret_cast<const float4 *>(
+                    P.saved + ((((int64_t)b * P.G + g_) * ((P.dpg + 1) >> 1) + (dl_ >> 1)) * P.nck + (blk - 1)) * Wp + j * STRIP);
+#pragma unroll
+                for (int k = 0; k < STRIP / 2; ++k) {
+                    const float4 v = (ok && r0 > 0) ? __ldg(pq + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    ck_pre[k] = (dl_ & 1) ? make_float4(v.y, 0.f, v.w, 0.f) : make_float4(v.x, 0.f, v.z, 0.f);
+                    adj_pre[k] = (ok && r0 + RB < H) ? pa[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            } else {
 #pragma unroll
             for (int k = 0; k < STRIP / 2; ++k) {
                 ck_pre[k] = (ok && r0 > 0) ? __ldg(pk + k) : make_float4(0.f, 0.f, 0.f, 0.f);
                 adj_pre[k] = (ok && r0 + RB < H) ? pa[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
             }
         }
         PT_MARK(PT_PREFETCH)

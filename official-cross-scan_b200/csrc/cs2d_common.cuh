@@ -35,6 +35,7 @@ namespace cs2d {
 
 constexpr int STRIP = 8;     // columns per thread
 constexpr int RB = 4;        // rows per block == checkpoint cadence
+constexpr int STREAM_RB = 4; // the same for the streaming (dstate 1) kernels; the tile backward can read their checkpoints
 constexpr int MAX_WARPS = 8;  // warps per CTA: state-pair slots x channel groups, at most 8
 constexpr int MAX_THREADS = MAX_WARPS * 32;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -71,6 +72,8 @@ struct Dev {
     void *out; int64_t o_bs, o_ds, o_hs;  // forward: out; backward: dout
     float2 *saved;                         // [batch][dim][nck][NPp][L*8] checkpoints of h
     int ck_roll;                           // forward without backward: one rolling row [batch][dim][1][NPp][L*8]
+    int ck_pairs;                          // checkpoints were written by the streaming forward (dstate 1):
+                                           // [batch][G][ceil(dpg/2)][nck][L*8] float2 = two CHANNELS per value
     // Column tiling of rows wider than 256 columns: this launch covers one tile (all
     // tensor pointers are already moved to the tile's first column).  The values that
     // cross a tile boundary travel through global edge buffers [batch][dim][NPp][H] float4

@@ -48,6 +48,18 @@ def test_random_shape_matches_oracle(shape, dtype, kw, seed):
     go = O.bwd(f["u"], f["delta"], f["A"], f["B"], f["C"], f["D"], f["delta_bias"], f["dout"], True)
     rtol, atol = TOL[str(dtype)[6:]]
     check_close("out", o[0].float().cpu().numpy(), yo, rtol, atol)
+    ddim = kw.get("delta_dim")
+    if ddim and dtype != torch.float32:
+        # delta shared by `rep` channels, 16-bit gradients: the operator (like the reference host code,
+        # src/cusoflex/selective_scan_oflex.cpp:433-438) rounds every channel's ddelta to the input
+        # type and then adds the `rep` rounded values.  The oracle gets the same rounding model:
+        # per-channel ddelta in float64, rounded, summed in float32, rounded.
+        b, K, D, _, h, w = shape
+        rep = K * D // ddim
+        bias = f["delta_bias"].repeat_interleave(rep) if f["delta_bias"] is not None else None
+        per = O.bwd(f["u"], f["delta"].repeat_interleave(rep, 1), f["A"], f["B"], f["C"], f["D"], bias, f["dout"], True)
+        dd = torch.from_numpy(per["ddelta"]).to(dtype).float().view(b, ddim, rep, h, w).sum(2).to(dtype).float()
+        go["ddelta"] = dd.numpy()
     for name, t in zip(NAMES, g):
         if t is None:
             assert go[name] is None, name
