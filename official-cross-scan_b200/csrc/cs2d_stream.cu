@@ -34,34 +34,70 @@ constexpr float LN2 = 0.6931471805599453f;
 template <bool F32>
 struct Raw8 { uint32_t w[F32 ? 8 : 4]; };
 
-// `row` = address of the strip's first column; nv = columns of the strip inside the image
+// `row` = address of the strip's first column; nv = columns of the strip inside the image.
+// mode 2: the 8 columns are one aligned 16-byte word (16-bit types) - one load; mode 1: two aligned
+// words of 4 columns; mode 0: element by element.  In the vector modes the image width is a multiple
+// of the word, so a word is either wholly inside the row or wholly outside: the load is predicated,
+// never a divergent branch (an idle lane of a row would otherwise drag its warp through the scalar path).
 template <bool F32>
-__device__ __forceinline__ void ld_raw8(Raw8<F32> &r, const char *row, bool vec, int nv) {
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int n = nv - 4 * h;
-        if constexpr (F32) {
-            const float *p = reinterpret_cast<const float *>(row) + 4 * h;
-            if (vec && n >= 4) {
-                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p));
-                r.w[4 * h] = v.x; r.w[4 * h + 1] = v.y; r.w[4 * h + 2] = v.z; r.w[4 * h + 3] = v.w;
-            } else {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) r.w[4 * h + k] = k < n ? __float_as_uint(__ldg(p + k)) : 0u;
-            }
-        } else {
-            const uint16_t *p = reinterpret_cast<const uint16_t *>(row) + 4 * h;
-            if (vec && n >= 4) {
-                const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p));
-                r.w[2 * h] = v.x; r.w[2 * h + 1] = v.y;
-            } else {
-                uint32_t e[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) e[k] = k < n ? (uint32_t)__ldg(p + k) : 0u;
-                r.w[2 * h] = e[0] | (e[1] << 16); r.w[2 * h + 1] = e[2] | (e[3] << 16);
-            }
+__device__ __forceinline__ void ld_raw8(Raw8<F32> &r, const char *row, int mode, int nv) {
+    if constexpr (!F32) {
+        if (mode == 2) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (nv >= 8) v = __ldg(reinterpret_cast<const uint4 *>(row));
+            r.w[0] = v.x; r.w[1] = v.y; r.w[2] = v.z; r.w[3] = v.w;
+            return;
         }
     }
+    if (mode) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if constexpr (F32) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (nv >= 4 * h + 4) v = __ldg(reinterpret_cast<const uint4 *>(row) + h);
+                r.w[4 * h] = v.x; r.w[4 * h + 1] = v.y; r.w[4 * h + 2] = v.z; r.w[4 * h + 3] = v.w;
+            } else {
+                uint2 v = make_uint2(0u, 0u);
+                if (nv >= 4 * h + 4) v = __ldg(reinterpret_cast<const uint2 *>(row) + h);
+                r.w[2 * h] = v.x; r.w[2 * h + 1] = v.y;
+            }
+        }
+        return;
+    }
+    if constexpr (F32) {
+        const float *p = reinterpret_cast<const float *>(row);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) r.w[k] = k < nv ? __float_as_uint(__ldg(p + k)) : 0u;
+    } else {
+        const uint16_t *p = reinterpret_cast<const uint16_t *>(row);
+        uint32_t e[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) e[k] = k < nv ? (uint32_t)__ldg(p + k) : 0u;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) r.w[k] = e[2 * k] | (e[2 * k + 1] << 16);
+    }
+}
+// 8 results of one strip to a tensor of type dt (fp32 or 16-bit); modes as ld_raw8
+__device__ __forceinline__ void st_row8(void *base, int64_t off, int dt, int mode, int nv, const float (&v)[STRIP]) {
+    if (nv <= 0) return;
+    if (dt != CS2D_F32 && mode == 2) {
+        uint4 raw;
+        if (dt == CS2D_BF16) {
+            *reinterpret_cast<__nv_bfloat162 *>(&raw.x) = __floats2bfloat162_rn(v[0], v[1]);
+            *reinterpret_cast<__nv_bfloat162 *>(&raw.y) = __floats2bfloat162_rn(v[2], v[3]);
+            *reinterpret_cast<__nv_bfloat162 *>(&raw.z) = __floats2bfloat162_rn(v[4], v[5]);
+            *reinterpret_cast<__nv_bfloat162 *>(&raw.w) = __floats2bfloat162_rn(v[6], v[7]);
+        } else {
+            *reinterpret_cast<__half2 *>(&raw.x) = __floats2half2_rn(v[0], v[1]);
+            *reinterpret_cast<__half2 *>(&raw.y) = __floats2half2_rn(v[2], v[3]);
+            *reinterpret_cast<__half2 *>(&raw.z) = __floats2half2_rn(v[4], v[5]);
+            *reinterpret_cast<__half2 *>(&raw.w) = __floats2half2_rn(v[6], v[7]);
+        }
+        *reinterpret_cast<uint4 *>(reinterpret_cast<uint16_t *>(base) + off) = raw;
+        return;
+    }
+    st4(base, off, dt, mode != 0, nv, make_float4(v[0], v[1], v[2], v[3]));
+    st4(base, off + 4, dt, mode != 0, nv - 4, make_float4(v[4], v[5], v[6], v[7]));
 }
 template <bool F32>
 __device__ __forceinline__ void cvt8(const Raw8<F32> &r, int dt, float (&v)[STRIP]) {
@@ -151,6 +187,9 @@ __device__ __forceinline__ void srow_fwd(int j, const float2 (&a)[STRIP], const 
     }
 }
 
+// access mode of a tensor (see ld_raw8): bit set in Dev::vec8 -> 2, in Dev::vec -> 1, else 0
+__device__ __forceinline__ int vmode(const Dev &P, int bit) { return (P.vec8 & bit) ? 2 : (P.vec & bit) ? 1 : 0; }
+
 // Which channels, rows and columns a thread owns; shared by both kernels.
 template <int L>
 struct Who {
@@ -187,7 +226,7 @@ __global__ void __launch_bounds__(STHREADS, F32 ? 3 : 4) sfwd_kernel(const Dev P
     const char *pC = reinterpret_cast<const char *>(P.C) + ((int64_t)w.b * P.C_bs + (int64_t)w.g * P.C_gs + w.c0) * es;
     const int64_t su = P.u_hs * es, sx = P.dl_hs * es, sB = P.B_hs * es, sC = P.C_hs * es;
     const int64_t o0 = (int64_t)w.b * P.o_bs + (int64_t)w.d0 * P.o_ds + w.c0, o1 = (int64_t)w.b * P.o_bs + (int64_t)w.d1 * P.o_ds + w.c0;
-    const bool vu = P.vec & VEC_U, vx = P.vec & VEC_DELTA, vB = P.vec & VEC_B, vC = P.vec & VEC_C, vo = P.vec & VEC_OUT;
+    const int vu = vmode(P, VEC_U), vx = vmode(P, VEC_DELTA), vB = vmode(P, VEC_B), vC = vmode(P, VEC_C), vo = vmode(P, VEC_OUT);
     const float2 A2 = mul2(f2(__ldg(P.A + (int64_t)w.d0 * P.A_ds), __ldg(P.A + (int64_t)w.d1 * P.A_ds)), bc(LOG2E));
     const float2 D2 = P.D ? f2(__ldg(P.D + w.d0), __ldg(P.D + w.d1)) : bc(0.f);
     const float2 bias = P.bias ? f2(__ldg(P.bias + w.d0 / P.drep), __ldg(P.bias + w.d1 / P.drep)) : bc(0.f);
@@ -229,14 +268,8 @@ __global__ void __launch_bounds__(STHREADS, F32 ? 3 : 4) sfwd_kernel(const Dev P
             h_up[i] = h[i]; a_up[i] = a[i];
         }
         const int64_t ro = (int64_t)r * P.o_hs;
-        if (w.on0) {
-            st4(P.out, o0 + ro, P.out_dt, vo, nv, make_float4(y0[0], y0[1], y0[2], y0[3]));
-            st4(P.out, o0 + ro + 4, P.out_dt, vo, nv - 4, make_float4(y0[4], y0[5], y0[6], y0[7]));
-        }
-        if (w.on1) {
-            st4(P.out, o1 + ro, P.out_dt, vo, nv, make_float4(y1[0], y1[1], y1[2], y1[3]));
-            st4(P.out, o1 + ro + 4, P.out_dt, vo, nv - 4, make_float4(y1[4], y1[5], y1[6], y1[7]));
-        }
+        if (w.on0) st_row8(P.out, o0 + ro, P.out_dt, vo, nv, y0);
+        if (w.on1) st_row8(P.out, o1 + ro, P.out_dt, vo, nv, y1);
         // checkpoint: the last row of every block but the last one
         if (!P.ck_roll && w.on0 && (r + 1) % SRB == 0 && r + 1 < H) {   // every lane: the row is read back whole
             float4 *pk = reinterpret_cast<float4 *>(P.saved + w.ck + (int64_t)(r / SRB) * Wp);
@@ -360,8 +393,8 @@ __global__ void __launch_bounds__(STHREADS, 2) sbwd_kernel(const Dev P) {
     const char *pB = reinterpret_cast<const char *>(P.B) + ((int64_t)w.b * P.B_bs + (int64_t)w.g * P.B_gs + w.c0) * es;
     const char *pC = reinterpret_cast<const char *>(P.C) + ((int64_t)w.b * P.C_bs + (int64_t)w.g * P.C_gs + w.c0) * es;
     const int64_t su = P.u_hs * es, sx = P.dl_hs * es, sg = P.o_hs * eso, sB = P.B_hs * es, sC = P.C_hs * es;
-    const bool vu = P.vec & VEC_U, vx = P.vec & VEC_DELTA, vB = P.vec & VEC_B, vC = P.vec & VEC_C, vg = P.vec & VEC_OUT,
-               vd = P.vec & VEC_DU;
+    const int vu = vmode(P, VEC_U), vx = vmode(P, VEC_DELTA), vB = vmode(P, VEC_B), vC = vmode(P, VEC_C), vg = vmode(P, VEC_OUT),
+              vd = vmode(P, VEC_DU);
     const float2 Araw = f2(__ldg(P.A + (int64_t)w.d0 * P.A_ds), __ldg(P.A + (int64_t)w.d1 * P.A_ds));
     const float2 A2 = mul2(Araw, bc(LOG2E));
     const float2 D2 = P.D ? f2(__ldg(P.D + w.d0), __ldg(P.D + w.d1)) : bc(0.f);
@@ -426,9 +459,8 @@ __global__ void __launch_bounds__(STHREADS, 2) sbwd_kernel(const Dev P) {
                 ld_raw8<F32>(rB, pB + r * sB, vB, nv);
             };
             load(r0);
-#pragma unroll
-            for (int rr = 0; rr < SRB; ++rr) {
-                if (rr < nr) {
+            for (int rr = 0; rr < nr; ++rr) {   // not unrolled: the rows live in shared memory, the code stays small
+                {
                     float u0[STRIP], u1[STRIP], Bf[STRIP];
                     float2 dl[STRIP], sig[STRIP];
                     cvt8<F32>(ru0, P.io_dt, u0); cvt8<F32>(ru1, P.io_dt, u1); cvt8<F32>(rB, P.io_dt, Bf);
@@ -457,9 +489,8 @@ __global__ void __launch_bounds__(STHREADS, 2) sbwd_kernel(const Dev P) {
             ld_raw8<G32>(rg0, pg0 + r * sg, vg, nv); ld_raw8<G32>(rg1, pg1 + r * sg, vg, nv);
         };
         load(r0 + nr - 1);
-#pragma unroll
-        for (int rr = SRB - 1; rr >= 0; --rr) {
-            if (rr < nr) {
+        for (int rr = nr - 1; rr >= 0; --rr) {
+            {
                 const int r = r0 + rr;
                 float Bf[STRIP], Cf[STRIP];
                 float2 dl[STRIP], sig[STRIP], g2[STRIP], u2[STRIP];
@@ -566,16 +597,12 @@ __global__ void __launch_bounds__(STHREADS, 2) sbwd_kernel(const Dev P) {
                     v[8 + i] = dCv.x + dCv.y;
                 }
                 if (w.on0) {
-                    st4(P.du, q0 + (int64_t)r * W, P.io_dt, vd, nv, make_float4(du0[0], du0[1], du0[2], du0[3]));
-                    st4(P.du, q0 + (int64_t)r * W + 4, P.io_dt, vd, nv - 4, make_float4(du0[4], du0[5], du0[6], du0[7]));
-                    st4(P.ddelta, q0 + (int64_t)r * W, P.io_dt, vd, nv, make_float4(dd0[0], dd0[1], dd0[2], dd0[3]));
-                    st4(P.ddelta, q0 + (int64_t)r * W + 4, P.io_dt, vd, nv - 4, make_float4(dd0[4], dd0[5], dd0[6], dd0[7]));
+                    st_row8(P.du, q0 + (int64_t)r * W, P.io_dt, vd, nv, du0);
+                    st_row8(P.ddelta, q0 + (int64_t)r * W, P.io_dt, vd, nv, dd0);
                 }
                 if (w.on1) {
-                    st4(P.du, q1 + (int64_t)r * W, P.io_dt, vd, nv, make_float4(du1[0], du1[1], du1[2], du1[3]));
-                    st4(P.du, q1 + (int64_t)r * W + 4, P.io_dt, vd, nv - 4, make_float4(du1[4], du1[5], du1[6], du1[7]));
-                    st4(P.ddelta, q1 + (int64_t)r * W, P.io_dt, vd, nv, make_float4(dd1[0], dd1[1], dd1[2], dd1[3]));
-                    st4(P.ddelta, q1 + (int64_t)r * W + 4, P.io_dt, vd, nv - 4, make_float4(dd1[4], dd1[5], dd1[6], dd1[7]));
+                    st_row8(P.du, q1 + (int64_t)r * W, P.io_dt, vd, nv, du1);
+                    st_row8(P.ddelta, q1 + (int64_t)r * W, P.io_dt, vd, nv, dd1);
                 }
                 add_dbc_rows<L>(v, dBp + (int64_t)r * W, dCp + (int64_t)r * W, w.c0, W, vBC, lane);
             }
