@@ -293,7 +293,7 @@ static int check_dirs(const cs2d_problem *p, const cs2d_dirs *o) {
 
 // ---- streaming kernels (cs2d_stream.cu) -------------------------------------------------------
 // A problem with a single state per channel, one scan orientation, no A_decay and rows of at most
-// 256 columns runs on the streaming kernels: no shared-memory tiles, no backward scratch, and
+// 128 columns (16 lanes of 8) runs on the streaming kernels: no shared-memory tiles, no backward scratch, and
 // checkpoints that pack two channels per value (half the bytes of the tile kernels' layout, which
 // is what cs2d_saved_bytes reports and therefore always large enough).  The choice depends on
 // nothing but these properties, so the forward and the backward of a problem always agree.
@@ -301,7 +301,7 @@ static bool has_dirs(const cs2d_dirs *o) {
     return o && (o->flip_rows_mask || o->flip_cols_mask || o->shared_input || o->merge_w);
 }
 static bool stream_ok(const cs2d_problem *p, const cs2d_dirs *o) {
-    return p->dstate == 1 && !has_dirs(o) && !p->A_decay && p->ncols <= kTileCols;
+    return p->dstate == 1 && !has_dirs(o) && !p->A_decay && p->ncols <= 16 * STRIP;
 }
 static int stream_lanes(const cs2d_problem *p) {
     const int strips = (p->ncols + STRIP - 1) / STRIP;

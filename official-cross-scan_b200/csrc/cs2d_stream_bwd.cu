@@ -1,0 +1,392 @@
+// Streaming backward kernel for dstate == 1 (sm_100a); see cs2d_stream.cuh.
+#include "cs2d_stream.cuh"
+
+namespace cs2d {
+
+// Sum of 16 per-thread values (dB of the strip's 8 columns, then dC) over the CW = 32/L channel
+// pairs of a warp, as a reduce-scatter: every step halves the values a lane keeps and adds the
+// partner's copy of them, so a lane ends with 16/CW complete sums, which it adds to global memory
+// with one predicated vector reduction.
+template <int L>
+__device__ __forceinline__ void add_dbc_rows(float (&v)[16], float *rowB, float *rowC, int c0, int W, bool vec,
+                                             int lane) {
+    constexpr int CW = 32 / L;
+    int base = 0;
+    if constexpr (CW >= 2) {
+        const bool hi = lane & L;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float keep = hi ? v[i + 8] : v[i], send = hi ? v[i] : v[i + 8];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, L);
+        }
+        base += hi ? 8 : 0;
+    }
+    if constexpr (CW >= 4) {
+        const bool hi = lane & (2 * L);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float keep = hi ? v[i + 4] : v[i], send = hi ? v[i] : v[i + 4];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2 * L);
+        }
+        base += hi ? 4 : 0;
+    }
+    if constexpr (CW >= 8) {
+        const bool hi = lane & (4 * L);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float keep = hi ? v[i + 2] : v[i], send = hi ? v[i] : v[i + 2];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4 * L);
+        }
+        base += hi ? 2 : 0;
+    }
+    if constexpr (CW >= 16) {
+        const bool hi = lane & (8 * L);
+        const float keep = hi ? v[1] : v[0], send = hi ? v[0] : v[1];
+        v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 8 * L);
+        base += hi ? 1 : 0;
+    }
+    bool writer = true;
+    if constexpr (CW >= 32) {   // one value left per lane pair: both get the sum, one writes
+        v[0] += __shfl_xor_sync(0xffffffffu, v[0], 16);
+        writer = !(lane & 16);
+    }
+    // this lane holds the sums of the original indices base .. base+CNT-1; index i is dB (i < 8) or
+    // dC (i >= 8) of column c0 + (i & 7).  vec: the rows are 16-byte aligned and W % 4 == 0, so a
+    // group of 4 (or 2) columns is wholly inside the row or wholly outside.
+    constexpr int CNT = CW >= 16 ? 1 : 16 / CW;
+    if constexpr (CNT >= 4) {
+#pragma unroll
+        for (int k = 0; k < CNT; k += 4) {
+            const int idx = base + k, c = c0 + (idx & 7);
+            float *dst = (idx < 8 ? rowB : rowC) + c;
+            if (vec) {
+                red16_if(dst, v[k], v[k + 1], v[k + 2], v[k + 3], c < W);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) red4_if(dst + e, v[k + e], c + e < W);
+            }
+        }
+    } else {
+        const int c = c0 + (base & 7);
+        float *dst = (base < 8 ? rowB : rowC) + c;
+        if constexpr (CNT == 2) {
+            if (vec) {
+                red8_if(dst, v[0], v[1], c < W);
+            } else {
+                red4_if(dst, v[0], c < W);
+                red4_if(dst + 1, v[1], c + 1 < W);
+            }
+        } else {
+            red4_if(dst, v[0], writer && c < W);
+        }
+    }
+}
+
+// Thread-private rows parked in shared memory: row `k` of thread `tid` is four float4 (8 float2) at
+// [(k*4 + q) * STHREADS + tid], so that a warp's accesses are consecutive 16-byte words.
+constexpr int SB_ROWS = SRB + 3;   // h above the block, h of the block's rows, adjoint row m, its a
+constexpr int SB_SMEM = SB_ROWS * 4 * STHREADS * 16;
+__device__ __forceinline__ void park(float4 *sm, int k, const float2 (&v)[STRIP]) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) sm[(k * 4 + q) * STHREADS] = make_float4(v[2 * q].x, v[2 * q].y, v[2 * q + 1].x, v[2 * q + 1].y);
+}
+__device__ __forceinline__ void fetch(const float4 *sm, int k, float2 (&v)[STRIP]) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float4 t = sm[(k * 4 + q) * STHREADS];
+        v[2 * q] = f2(t.x, t.y); v[2 * q + 1] = f2(t.z, t.w);
+    }
+}
+
+// DT: type of u, delta, B, C, du, ddelta; G32: dout is fp32 (always with fp32 inputs; with 16-bit
+// inputs when the forward returned fp32).
+template <int L, int DT, bool G32>
+__global__ void __launch_bounds__(STHREADS, 2) sbwd_kernel(const Dev P) {
+    static_assert(G32 || DT != CS2D_F32, "fp32 inputs come with an fp32 dout");
+    extern __shared__ __align__(16) float4 sm_all[];
+    float4 *sm = sm_all + threadIdx.x;
+    constexpr int K_TOP = 0, K_ROW = 1, K_M = SRB + 1, K_A = SRB + 2;
+    constexpr int GT = G32 ? CS2D_F32 : DT;
+    constexpr bool FAST = DT != CS2D_F32;
+    const Who<L> w(P);
+    constexpr int Wp = Who<L>::Wp;
+    const int j = w.j, H = P.H, W = P.W, nv = w.nv, lane = threadIdx.x & 31;
+    constexpr int es = DT == CS2D_F32 ? 4 : 2, eso = G32 ? 4 : 2;
+    const char *pu0 = reinterpret_cast<const char *>(P.u) + ((int64_t)w.b * P.u_bs + (int64_t)w.d0 * P.u_ds + w.c0) * es;
+    const char *pu1 = reinterpret_cast<const char *>(P.u) + ((int64_t)w.b * P.u_bs + (int64_t)w.d1 * P.u_ds + w.c0) * es;
+    const char *px0 = reinterpret_cast<const char *>(P.delta) + ((int64_t)w.b * P.dl_bs + (int64_t)(w.d0 / P.drep) * P.dl_ds + w.c0) * es;
+    const char *px1 = reinterpret_cast<const char *>(P.delta) + ((int64_t)w.b * P.dl_bs + (int64_t)(w.d1 / P.drep) * P.dl_ds + w.c0) * es;
+    const char *pg0 = reinterpret_cast<const char *>(P.out) + ((int64_t)w.b * P.o_bs + (int64_t)w.d0 * P.o_ds + w.c0) * eso;
+    const char *pg1 = reinterpret_cast<const char *>(P.out) + ((int64_t)w.b * P.o_bs + (int64_t)w.d1 * P.o_ds + w.c0) * eso;
+    const char *pB = reinterpret_cast<const char *>(P.B) + ((int64_t)w.b * P.B_bs + (int64_t)w.g * P.B_gs + w.c0) * es;
+    const char *pC = reinterpret_cast<const char *>(P.C) + ((int64_t)w.b * P.C_bs + (int64_t)w.g * P.C_gs + w.c0) * es;
+    const int64_t su = P.u_hs * es, sx = P.dl_hs * es, sg = P.o_hs * eso, sB = P.B_hs * es, sC = P.C_hs * es;
+    const int vu = vmode(P, VEC_U), vx = vmode(P, VEC_DELTA), vB = vmode(P, VEC_B), vC = vmode(P, VEC_C), vg = vmode(P, VEC_OUT),
+              vd = vmode(P, VEC_DU);
+    const bool softplus = P.softplus != 0;
+    const float2 Araw = f2(__ldg(P.A + (int64_t)w.d0 * P.A_ds), __ldg(P.A + (int64_t)w.d1 * P.A_ds));
+    const float2 A2 = mul2(Araw, bc(LOG2E));
+    const float2 D2 = P.D ? f2(__ldg(P.D + w.d0), __ldg(P.D + w.d1)) : bc(0.f);
+    const float2 bias = P.bias ? f2(__ldg(P.bias + w.d0 / P.drep), __ldg(P.bias + w.d1 / P.drep)) : bc(0.f);
+    // du / ddelta rows of the two channels (contiguous (batch, dim, H, W) tensors of the input type)
+    const int64_t q0 = ((int64_t)w.b * P.dim + w.d0) * H * W + w.c0, q1 = ((int64_t)w.b * P.dim + w.d1) * H * W + w.c0;
+    float *dBp = P.dB + (((int64_t)w.b * P.G + w.g) * H) * W, *dCp = P.dC + (((int64_t)w.b * P.G + w.g) * H) * W;
+    const bool vBC = (W % 4) == 0;   // dB / dC are dense fp32: rows start 16-byte aligned when W % 4 == 0
+    const float2 *ckp = P.saved + w.ck;
+
+    {
+        float2 z[STRIP];
+#pragma unroll
+        for (int i = 0; i < STRIP; ++i) z[i] = bc(0.f);
+        park(sm, K_M, z); park(sm, K_A, z);   // below the image: no adjoint
+    }
+    float2 dA2 = bc(0.f), dD2 = bc(0.f), db2 = bc(0.f);
+
+    // softplus'd delta (and its derivative) of both channels for one raw row pair.  Columns past the
+    // image come out as softplus(bias): harmless, because u, dout, B, C read as zeros there (no
+    // input, no gradient) and whatever h holds there only flows further right.
+    auto soft8 = [&](const Raw8<DT> &r0, const Raw8<DT> &r1, float2 (&dl)[STRIP], float2 (&sig)[STRIP]) {
+        float x0[STRIP], x1[STRIP];
+        cvt8<DT>(r0, x0); cvt8<DT>(r1, x1);
+#pragma unroll
+        for (int i = 0; i < STRIP; ++i) {
+            dl[i] = add2(f2(x0[i], x1[i]), bias);
+            sig[i] = bc(1.f);
+            if (softplus) softplus2<FAST, true>(dl[i], dl[i], sig[i]);
+        }
+    };
+
+    for (int blk = P.nck - 1; blk >= 0; --blk) {
+        const int r0 = blk * SRB, nr = min(SRB, H - r0);
+        {
+            // ---- row above the block: h from the checkpoint, a from delta ----
+            float2 a_up[STRIP], hprev[STRIP];
+            {
+                const bool top = r0 > 0;
+                const int rt = max(r0 - 1, 0);
+                Raw8<DT> rx0, rx1;
+                ld_raw8<DT>(rx0, px0 + rt * sx, vx, nv, top); ld_raw8<DT>(rx1, px1 + rt * sx, vx, nv, top);
+                const float4 *pk = reinterpret_cast<const float4 *>(ckp + (int64_t)max(blk - 1, 0) * Wp);
+#pragma unroll
+                for (int k = 0; k < STRIP / 2; ++k) {
+                    const uint4 v = ldg16_if(pk + k, top);
+                    hprev[2 * k] = f2(__uint_as_float(v.x), __uint_as_float(v.y));
+                    hprev[2 * k + 1] = f2(__uint_as_float(v.z), __uint_as_float(v.w));
+                }
+                float2 dl[STRIP], sig[STRIP];
+                soft8(rx0, rx1, dl, sig);
+                // above the first row h is zero, so the value of a there never matters
+#pragma unroll
+                for (int i = 0; i < STRIP; ++i) a_up[i] = ex2_2(mul2(dl[i], A2));
+            }
+            park(sm, K_TOP, hprev);
+            // ---- recompute h of the block's rows ----
+            Raw8<DT> ru0, ru1, rx0, rx1, rB;
+            auto load = [&](int r) {
+                ld_raw8<DT>(ru0, pu0 + r * su, vu, nv); ld_raw8<DT>(ru1, pu1 + r * su, vu, nv);
+                ld_raw8<DT>(rx0, px0 + r * sx, vx, nv); ld_raw8<DT>(rx1, px1 + r * sx, vx, nv);
+                ld_raw8<DT>(rB, pB + r * sB, vB, nv);
+            };
+            load(r0);
+            for (int rr = 0; rr < nr; ++rr) {   // not unrolled: the rows live in shared memory, the code stays small
+                float u0[STRIP], u1[STRIP], Bf[STRIP];
+                float2 dl[STRIP], sig[STRIP];
+                cvt8<DT>(ru0, u0); cvt8<DT>(ru1, u1); cvt8<DT>(rB, Bf);
+                soft8(rx0, rx1, dl, sig);
+                load(r0 + min(rr + 1, nr - 1));
+                float2 a[STRIP], p[STRIP], h[STRIP], sdummy[STRIP];
+#pragma unroll
+                for (int i = 0; i < STRIP; ++i) {
+                    a[i] = ex2_2(mul2(dl[i], A2));
+                    p[i] = mul2(bc(Bf[i]), mul2(dl[i], f2(u0[i], u1[i])));
+                }
+                srow_fwd<L, false>(j, a, p, hprev, a_up, h, sdummy);
+                park(sm, K_ROW + rr, h);
+#pragma unroll
+                for (int i = 0; i < STRIP; ++i) { a_up[i] = a[i]; hprev[i] = h[i]; }
+            }
+        }
+        // ---- reverse sweep ----
+        Raw8<DT> ru0, ru1, rx0, rx1, rB, rC;
+        Raw8<GT> rg0, rg1;
+        auto load = [&](int r) {
+            ld_raw8<DT>(ru0, pu0 + r * su, vu, nv); ld_raw8<DT>(ru1, pu1 + r * su, vu, nv);
+            ld_raw8<DT>(rx0, px0 + r * sx, vx, nv); ld_raw8<DT>(rx1, px1 + r * sx, vx, nv);
+            ld_raw8<DT>(rB, pB + r * sB, vB, nv); ld_raw8<DT>(rC, pC + r * sC, vC, nv);
+            // idle slots and the missing second channel of an odd group carry no gradient
+            ld_raw8<GT>(rg0, pg0 + r * sg, vg, nv, w.on0); ld_raw8<GT>(rg1, pg1 + r * sg, vg, nv, w.on1);
+        };
+        load(r0 + nr - 1);
+        for (int rr = nr - 1; rr >= 0; --rr) {
+            const int r = r0 + rr;
+            float Bf[STRIP], Cf[STRIP];
+            float2 dl[STRIP], sig[STRIP], g2[STRIP], u2[STRIP];
+            {
+                float t0[STRIP], t1[STRIP];
+                cvt8<DT>(ru0, t0); cvt8<DT>(ru1, t1);
+#pragma unroll
+                for (int i = 0; i < STRIP; ++i) u2[i] = f2(t0[i], t1[i]);
+                cvt8<GT>(rg0, t0); cvt8<GT>(rg1, t1);
+#pragma unroll
+                for (int i = 0; i < STRIP; ++i) g2[i] = f2(t0[i], t1[i]);
+            }
+            cvt8<DT>(rB, Bf); cvt8<DT>(rC, Cf);
+            soft8(rx0, rx1, dl, sig);
+            load(max(r - 1, r0));   // the block's first row is fetched twice rather than branched around
+            float2 a[STRIP], p[STRIP], s[STRIP], gC[STRIP], dh[STRIP], ds[STRIP];
+#pragma unroll
+            for (int i = 0; i < STRIP; ++i) {
+                a[i] = ex2_2(mul2(dl[i], A2));
+                p[i] = mul2(bc(Bf[i]), mul2(dl[i], u2[i]));
+                gC[i] = mul2(bc(Cf[i]), g2[i]);
+            }
+            float2 a_r7 = bc(0.f);  // next lane's first column
+            {
+                float2 m_dn[STRIP], a_dn[STRIP], bt[STRIP], mdr7 = bc(0.f);
+                fetch(sm, K_M, m_dn); fetch(sm, K_A, a_dn);
+                if constexpr (L > 1) {
+                    a_r7 = shfl_down2<L>(a[0], 1);
+                    mdr7 = shfl_down2<L>(m_dn[0], 1);
+                    const bool last = j == L - 1;
+                    a_r7.x = last ? 0.f : a_r7.x; a_r7.y = last ? 0.f : a_r7.y;
+                    mdr7.x = last ? 0.f : mdr7.x; mdr7.y = last ? 0.f : mdr7.y;
+                }
+#pragma unroll
+                for (int i = 0; i < STRIP; ++i) {
+                    const float2 ar = i < STRIP - 1 ? a[i + 1] : a_r7;
+                    const float2 mdr = i < STRIP - 1 ? m_dn[i + 1] : mdr7;
+                    bt[i] = fma2(mul2(add2(ar, a_dn[i]), mdr), bc(-0.5f), add2(gC[i], m_dn[i]));
+                }
+                // s forward, dh and ds reverse (multiplier of column c is a(c+1)), as half chains
+                constexpr int HS = STRIP / 2;
+                float2 Pf0 = a[0], Pf1 = a[HS], S0 = p[0], S1 = p[HS];
+                float2 Pr0 = a_r7, Pr1 = a[HS], H0 = bt[STRIP - 1], H1 = bt[HS - 1];
+                float2 D0 = neg2(gC[STRIP - 1]), D1 = neg2(gC[HS - 1]);
+#pragma unroll
+                for (int k = 1; k < HS; ++k) {
+                    S0 = fma2(a[k], S0, p[k]); Pf0 = mul2(Pf0, a[k]);
+                    S1 = fma2(a[HS + k], S1, p[HS + k]); Pf1 = mul2(Pf1, a[HS + k]);
+                    const float2 ar0 = a[STRIP - k], ar1 = a[HS - k];
+                    H0 = fma2(ar0, H0, bt[STRIP - 1 - k]); D0 = fma2(ar0, D0, neg2(gC[STRIP - 1 - k]));
+                    H1 = fma2(ar1, H1, bt[HS - 1 - k]); D1 = fma2(ar1, D1, neg2(gC[HS - 1 - k]));
+                    Pr0 = mul2(Pr0, ar0); Pr1 = mul2(Pr1, ar1);
+                }
+                float2 cs, unused, cdh, cds, Pfin, Prin;
+                carry_fwd<L, false>(j, mul2(Pf0, Pf1), fma2(Pf1, S0, S1), bc(0.f), cs, unused, Pfin);
+                carry_rev<L, true>(j, mul2(Pr0, Pr1), fma2(Pr1, H0, H1), fma2(Pr1, D0, D1), cdh, cds, Prin);
+                float2 cs1 = fma2(Pf0, cs, S0);
+                float2 cdh1 = fma2(Pr0, cdh, H0), cds1 = fma2(Pr0, cds, D0);
+#pragma unroll
+                for (int k = 0; k < HS; ++k) {
+                    cs = fma2(a[k], cs, p[k]); s[k] = cs;
+                    cs1 = fma2(a[HS + k], cs1, p[HS + k]); s[HS + k] = cs1;
+                    const float2 ar0 = k ? a[STRIP - k] : a_r7, ar1 = a[HS - k];
+                    cdh = fma2(ar0, cdh, bt[STRIP - 1 - k]); dh[STRIP - 1 - k] = cdh;
+                    cds = fma2(ar0, cds, neg2(gC[STRIP - 1 - k])); ds[STRIP - 1 - k] = cds;
+                    cdh1 = fma2(ar1, cdh1, bt[HS - 1 - k]); dh[HS - 1 - k] = cdh1;
+                    cds1 = fma2(ar1, cds1, neg2(gC[HS - 1 - k])); ds[HS - 1 - k] = cds1;
+                }
+            }
+            float2 m[STRIP], m_dn[STRIP], hrow[STRIP], hup[STRIP];
+#pragma unroll
+            for (int i = 0; i < STRIP; ++i) m[i] = mul2(a[i], dh[i]);
+            fetch(sm, K_M, m_dn); fetch(sm, K_ROW + rr, hrow); fetch(sm, K_ROW + rr - 1, hup);   // K_ROW - 1 == K_TOP
+            float2 m_r7 = bc(0.f), h_l0 = bc(0.f);
+            if constexpr (L > 1) {
+                m_r7 = shfl_down2<L>(m[0], 1);
+                h_l0 = shfl_up2<L>(hrow[STRIP - 1], 1);
+                m_r7.x = j == L - 1 ? 0.f : m_r7.x; m_r7.y = j == L - 1 ? 0.f : m_r7.y;
+                h_l0.x = j == 0 ? 0.f : h_l0.x; h_l0.y = j == 0 ? 0.f : h_l0.y;
+            }
+            park(sm, K_M, m); park(sm, K_A, a);   // the adjoint row for the row above
+            float v[16], du0[STRIP], du1[STRIP], dd0[STRIP], dd1[STRIP];
+#pragma unroll
+            for (int i = 0; i < STRIP; ++i) {
+                const float2 hl = i ? hrow[i - 1] : h_l0;
+                const float2 mr = i < STRIP - 1 ? m[i + 1] : m_r7;
+                const float2 X = fma2(m_dn[i], hl, mul2(mr, hup[i]));
+                const float2 hm = sub2(hrow[i], p[i]);
+                const float2 sm_ = sub2(s[i], p[i]);
+                const float2 Gh = fma2(dh[i], hm, mul2(mul2(a[i], X), bc(-0.5f)));
+                const float2 G = fma2(ds[i], sm_, Gh);
+                const float2 eps = fma2(gC[i], bc(0.25f), add2(dh[i], ds[i]));
+                const float2 t1 = mul2(bc(Bf[i]), eps);
+                const float2 duv = fma2(dl[i], t1, mul2(D2, g2[i]));
+                const float2 ddv = mul2(fma2(u2[i], t1, mul2(Araw, G)), sig[i]);
+                du0[i] = duv.x; du1[i] = duv.y; dd0[i] = ddv.x; dd1[i] = ddv.y;
+                dA2 = fma2(dl[i], G, dA2);
+                dD2 = fma2(g2[i], u2[i], dD2);
+                db2 = add2(db2, ddv);
+                const float2 dBv = mul2(mul2(dl[i], u2[i]), eps);
+                const float2 yt = fma2(p[i], bc(0.25f), sub2(hrow[i], s[i]));
+                const float2 dCv = mul2(g2[i], yt);
+                v[i] = dBv.x + dBv.y;
+                v[8 + i] = dCv.x + dCv.y;
+            }
+            st_row8(P.du, q0 + (int64_t)r * W, DT, vd, nv, w.on0, du0);
+            st_row8(P.ddelta, q0 + (int64_t)r * W, DT, vd, nv, w.on0, dd0);
+            st_row8(P.du, q1 + (int64_t)r * W, DT, vd, nv, w.on1, du1);
+            st_row8(P.ddelta, q1 + (int64_t)r * W, DT, vd, nv, w.on1, dd1);
+            add_dbc_rows<L>(v, dBp + (int64_t)r * W, dCp + (int64_t)r * W, w.c0, W, vBC, lane);
+        }
+    }
+    // ---- per-channel parameter gradients: sum over the row's lanes, one atomic per channel ----
+    if constexpr (L > 1) {
+#pragma unroll
+        for (int off = L / 2; off; off >>= 1) {
+            dA2 = add2(dA2, shfl_xor2<L>(dA2, off));
+            dD2 = add2(dD2, shfl_xor2<L>(dD2, off));
+            db2 = add2(db2, shfl_xor2<L>(db2, off));
+        }
+    }
+    if (j == 0) {
+        if (w.on0) {
+            atomicAdd(P.dA + w.d0, dA2.x);
+            if (P.dD) atomicAdd(P.dD + w.d0, dD2.x);
+            if (P.dbias) atomicAdd(P.dbias + w.d0, db2.x);
+        }
+        if (w.on1) {
+            atomicAdd(P.dA + w.d1, dA2.y);
+            if (P.dD) atomicAdd(P.dD + w.d1, dD2.y);
+            if (P.dbias) atomicAdd(P.dbias + w.d1, db2.y);
+        }
+    }
+}
+
+template <int L, int DT, bool G32>
+static cudaError_t launch_sb3(const Dev &P, int grid, cudaStream_t st) {
+    static bool attr_done[64] = {};  // per template instance and device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(sbwd_kernel<L, DT, G32>, cudaFuncAttributeMaxDynamicSharedMemorySize, SB_SMEM);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    sbwd_kernel<L, DT, G32><<<grid, STHREADS, SB_SMEM, st>>>(P);
+    return cudaGetLastError();
+}
+template <int L>
+static cudaError_t launch_sb(const Dev &P, int grid, cudaStream_t st) {
+    const bool g32 = P.out_dt == CS2D_F32;
+    switch (P.io_dt) {
+        case CS2D_F32: return launch_sb3<L, CS2D_F32, true>(P, grid, st);
+        case CS2D_F16: return g32 ? launch_sb3<L, CS2D_F16, true>(P, grid, st) : launch_sb3<L, CS2D_F16, false>(P, grid, st);
+        default: return g32 ? launch_sb3<L, CS2D_BF16, true>(P, grid, st) : launch_sb3<L, CS2D_BF16, false>(P, grid, st);
+    }
+}
+
+cudaError_t launch_stream_bwd(const Dev &P, int L, int grid, cudaStream_t st) {
+    switch (L) {
+#ifndef CS2D_STREAM_L8_ONLY
+        case 1: return launch_sb<1>(P, grid, st);
+        case 2: return launch_sb<2>(P, grid, st);
+        case 4: return launch_sb<4>(P, grid, st);
+        case 16: return launch_sb<16>(P, grid, st);
+#endif
+        case 8: return launch_sb<8>(P, grid, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace cs2d
