@@ -121,6 +121,52 @@ __device__ __forceinline__ void ld_raw8(Raw8<DT> &r, const char *row, int mode, 
         for (int k = 0; k < 4; ++k) r.w[k] = e[2 * k] | (e[2 * k + 1] << 16);
     }
 }
+// ---- asynchronous staging of strips into thread-private shared-memory slots -------------------
+// A slot is one 16-byte word per thread (two for fp32: 8 columns are 32 bytes), laid out
+// [..][word][thread] so that a warp's accesses are consecutive words.  Each thread copies, waits for
+// (cp.async.wait_group) and reads only its own slots, so no barrier is involved.  A strip that is
+// switched off, or past the end of the row, is zero-filled (source size 0).
+__device__ __forceinline__ void cp16(uint32_t dst, const void *src, bool on) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(on ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp8(uint32_t dst, const void *src, bool on) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(on ? 8 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int DT>
+__host__ __device__ constexpr int slot_words() { return DT == CS2D_F32 ? 2 : 1; }
+// `slot` points at this thread's first word of the slot; further words follow STHREADS words later
+template <int DT>
+__device__ __forceinline__ void cp_raw8(uint4 *slot, const char *row, int mode, int nv, bool on = true) {
+    const uint32_t dst = smem_addr(slot);
+    if constexpr (DT == CS2D_F32) {
+        if (mode) {
+            cp16(dst, row, on && nv >= 4);
+            cp16(dst + STHREADS * 16, row + 16, on && nv >= 8);
+            return;
+        }
+    } else {
+        if (mode == 2) { cp16(dst, row, on && nv >= 8); return; }
+        if (mode == 1) { cp8(dst, row, on && nv >= 4); cp8(dst + 8, row + 8, on && nv >= 8); return; }
+    }
+    Raw8<DT> r;   // element by element: loaded now, parked in the slot
+    ld_raw8<DT>(r, row, 0, nv, on);
+    slot[0] = make_uint4(r.w[0], r.w[1], r.w[2], r.w[3]);
+    if constexpr (DT == CS2D_F32) slot[STHREADS] = make_uint4(r.w[4], r.w[5], r.w[6], r.w[7]);
+}
+template <int DT>
+__device__ __forceinline__ void lds_raw8(Raw8<DT> &r, const uint4 *slot) {
+    const uint4 v = slot[0];
+    r.w[0] = v.x; r.w[1] = v.y; r.w[2] = v.z; r.w[3] = v.w;
+    if constexpr (DT == CS2D_F32) {
+        const uint4 q = slot[STHREADS];
+        r.w[4] = q.x; r.w[5] = q.y; r.w[6] = q.z; r.w[7] = q.w;
+    }
+}
+
 template <int DT>
 __device__ __forceinline__ void cvt8(const Raw8<DT> &r, float (&v)[STRIP]) {
     if constexpr (DT == CS2D_F32) {

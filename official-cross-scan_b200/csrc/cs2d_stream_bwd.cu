@@ -85,7 +85,18 @@ __device__ __forceinline__ void add_dbc_rows(float (&v)[16], float *rowB, float 
 // Thread-private rows parked in shared memory: row `k` of thread `tid` is four float4 (8 float2) at
 // [(k*4 + q) * STHREADS + tid], so that a warp's accesses are consecutive 16-byte words.
 constexpr int SB_ROWS = SRB + 3;   // h above the block, h of the block's rows, adjoint row m, its a
-constexpr int SB_SMEM = SB_ROWS * 4 * STHREADS * 16;
+constexpr int SB_PARK = SB_ROWS * 4 * STHREADS * 16;
+// Staging ring: every row the thread is going to need - the row above a block (delta and the h
+// checkpoint), the block's rows for the recompute (u, delta, B), the same rows bottom-up for the
+// reverse sweep (u, delta, dout, B, C) - is copied asynchronously into one of BW_DEPTH slots,
+// BW_DEPTH-1 items ahead of its use, in exactly the order of use.  Word offsets inside a slot:
+// u0, u1, x0, x1, B, C (SW words each), g0, g1 (GW words each); the checkpoint row (4 words) takes
+// the place of B.. in the item of the row above a block.
+constexpr int BW_DEPTH = 3;
+template <int DT, int GT>
+__host__ __device__ constexpr int bw_slot_words() { return 6 * slot_words<DT>() + 2 * slot_words<GT>(); }
+template <int DT, int GT>
+__host__ __device__ constexpr int bw_smem() { return SB_PARK + BW_DEPTH * bw_slot_words<DT, GT>() * STHREADS * 16; }
 __device__ __forceinline__ void park(float4 *sm, int k, const float2 (&v)[STRIP]) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) sm[(k * 4 + q) * STHREADS] = make_float4(v[2 * q].x, v[2 * q].y, v[2 * q + 1].x, v[2 * q + 1].y);
@@ -101,12 +112,17 @@ __device__ __forceinline__ void fetch(const float4 *sm, int k, float2 (&v)[STRIP
 // DT: type of u, delta, B, C, du, ddelta; G32: dout is fp32 (always with fp32 inputs; with 16-bit
 // inputs when the forward returned fp32).
 template <int L, int DT, bool G32>
-__global__ void __launch_bounds__(STHREADS, 2) sbwd_kernel(const Dev P) {
+__global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 1 : 2) sbwd_kernel(const Dev P) {
     static_assert(G32 || DT != CS2D_F32, "fp32 inputs come with an fp32 dout");
     extern __shared__ __align__(16) float4 sm_all[];
     float4 *sm = sm_all + threadIdx.x;
     constexpr int K_TOP = 0, K_ROW = 1, K_M = SRB + 1, K_A = SRB + 2;
     constexpr int GT = G32 ? CS2D_F32 : DT;
+    constexpr int SW = slot_words<DT>(), GW = slot_words<GT>(), SLOTW = bw_slot_words<DT, GT>();
+    constexpr int O_U0 = 0, O_U1 = SW, O_X0 = 2 * SW, O_X1 = 3 * SW, O_B = 4 * SW, O_C = 5 * SW, O_G0 = 6 * SW,
+                  O_G1 = 6 * SW + GW, O_CK = 4 * SW;
+    static_assert(O_CK + 4 <= SLOTW, "the checkpoint row fits behind the two delta strips");
+    uint4 *ring = reinterpret_cast<uint4 *>(sm_all + SB_ROWS * 4 * STHREADS) + threadIdx.x;
     constexpr bool FAST = DT != CS2D_F32;
     const Who<L> w(P);
     constexpr int Wp = Who<L>::Wp;
@@ -142,6 +158,50 @@ __global__ void __launch_bounds__(STHREADS, 2) sbwd_kernel(const Dev P) {
     }
     float2 dA2 = bc(0.f), dD2 = bc(0.f), db2 = bc(0.f);
 
+    // ---- producer side of the staging ring ----
+    int pb = P.nck - 1, pp = 0, ps = 0;   // next item: block, position inside it (0 = row above, 1..nr recompute, then reverse), slot
+    auto issue_next = [&]() {
+        if (pb >= 0) {
+            const int r0p = pb * SRB, nrp = min(SRB, H - r0p);
+            uint4 *s = ring + ps * SLOTW * STHREADS;
+            if (pp == 0) {
+                const bool top = r0p > 0;
+                const int rt = max(r0p - 1, 0);
+                cp_raw8<DT>(s + O_X0 * STHREADS, px0 + rt * sx, vx, nv, top);
+                cp_raw8<DT>(s + O_X1 * STHREADS, px1 + rt * sx, vx, nv, top);
+                const float2 *ck = ckp + (int64_t)max(pb - 1, 0) * Wp;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) cp16(smem_addr(s + (O_CK + k) * STHREADS), ck + 2 * k, top);
+            } else {
+                const bool rev = pp > nrp;
+                const int r = rev ? r0p + 2 * nrp - pp : r0p + pp - 1;
+                cp_raw8<DT>(s + O_U0 * STHREADS, pu0 + r * su, vu, nv); cp_raw8<DT>(s + O_U1 * STHREADS, pu1 + r * su, vu, nv);
+                cp_raw8<DT>(s + O_X0 * STHREADS, px0 + r * sx, vx, nv); cp_raw8<DT>(s + O_X1 * STHREADS, px1 + r * sx, vx, nv);
+                cp_raw8<DT>(s + O_B * STHREADS, pB + r * sB, vB, nv);
+                if (rev) {
+                    cp_raw8<DT>(s + O_C * STHREADS, pC + r * sC, vC, nv);
+                    // idle slots and the missing second channel of an odd group carry no gradient
+                    cp_raw8<GT>(s + O_G0 * STHREADS, pg0 + r * sg, vg, nv, w.on0);
+                    cp_raw8<GT>(s + O_G1 * STHREADS, pg1 + r * sg, vg, nv, w.on1);
+                }
+            }
+            if (++pp > 2 * nrp) { pp = 0; --pb; }
+        }
+        cp_commit();   // an empty group once everything has been asked for: the wait below counts groups
+        ps = ps + 1 == BW_DEPTH ? 0 : ps + 1;
+    };
+    // consumer side: the slot of the item that is due now
+    int cs = 0;
+    auto next_item = [&]() -> const uint4 * {
+        issue_next();
+        cp_wait<BW_DEPTH - 1>();
+        const uint4 *s = ring + cs * SLOTW * STHREADS;
+        cs = cs + 1 == BW_DEPTH ? 0 : cs + 1;
+        return s;
+    };
+#pragma unroll
+    for (int k = 0; k < BW_DEPTH - 1; ++k) issue_next();
+
     // softplus'd delta (and its derivative) of both channels for one raw row pair.  Columns past the
     // image come out as softplus(bias): harmless, because u, dout, B, C read as zeros there (no
     // input, no gradient) and whatever h holds there only flows further right.
@@ -162,14 +222,12 @@ __global__ void __launch_bounds__(STHREADS, 2) sbwd_kernel(const Dev P) {
             // ---- row above the block: h from the checkpoint, a from delta ----
             float2 a_up[STRIP], hprev[STRIP];
             {
-                const bool top = r0 > 0;
-                const int rt = max(r0 - 1, 0);
+                const uint4 *it = next_item();
                 Raw8<DT> rx0, rx1;
-                ld_raw8<DT>(rx0, px0 + rt * sx, vx, nv, top); ld_raw8<DT>(rx1, px1 + rt * sx, vx, nv, top);
-                const float4 *pk = reinterpret_cast<const float4 *>(ckp + (int64_t)max(blk - 1, 0) * Wp);
+                lds_raw8<DT>(rx0, it + O_X0 * STHREADS); lds_raw8<DT>(rx1, it + O_X1 * STHREADS);
 #pragma unroll
                 for (int k = 0; k < STRIP / 2; ++k) {
-                    const uint4 v = ldg16_if(pk + k, top);
+                    const uint4 v = it[(O_CK + k) * STHREADS];
                     hprev[2 * k] = f2(__uint_as_float(v.x), __uint_as_float(v.y));
                     hprev[2 * k + 1] = f2(__uint_as_float(v.z), __uint_as_float(v.w));
                 }
@@ -181,19 +239,18 @@ __global__ void __launch_bounds__(STHREADS, 2) sbwd_kernel(const Dev P) {
             }
             park(sm, K_TOP, hprev);
             // ---- recompute h of the block's rows ----
-            Raw8<DT> ru0, ru1, rx0, rx1, rB;
-            auto load = [&](int r) {
-                ld_raw8<DT>(ru0, pu0 + r * su, vu, nv); ld_raw8<DT>(ru1, pu1 + r * su, vu, nv);
-                ld_raw8<DT>(rx0, px0 + r * sx, vx, nv); ld_raw8<DT>(rx1, px1 + r * sx, vx, nv);
-                ld_raw8<DT>(rB, pB + r * sB, vB, nv);
-            };
-            load(r0);
             for (int rr = 0; rr < nr; ++rr) {   // not unrolled: the rows live in shared memory, the code stays small
                 float u0[STRIP], u1[STRIP], Bf[STRIP];
                 float2 dl[STRIP], sig[STRIP];
-                cvt8<DT>(ru0, u0); cvt8<DT>(ru1, u1); cvt8<DT>(rB, Bf);
-                soft8(rx0, rx1, dl, sig);
-                load(r0 + min(rr + 1, nr - 1));
+                {
+                    const uint4 *it = next_item();
+                    Raw8<DT> q, q2;
+                    lds_raw8<DT>(q, it + O_U0 * STHREADS); cvt8<DT>(q, u0);
+                    lds_raw8<DT>(q, it + O_U1 * STHREADS); cvt8<DT>(q, u1);
+                    lds_raw8<DT>(q, it + O_B * STHREADS); cvt8<DT>(q, Bf);
+                    lds_raw8<DT>(q, it + O_X0 * STHREADS); lds_raw8<DT>(q2, it + O_X1 * STHREADS);
+                    soft8(q, q2, dl, sig);
+                }
                 float2 a[STRIP], p[STRIP], h[STRIP], sdummy[STRIP];
 #pragma unroll
                 for (int i = 0; i < STRIP; ++i) {
@@ -207,32 +264,28 @@ __global__ void __launch_bounds__(STHREADS, 2) sbwd_kernel(const Dev P) {
             }
         }
         // ---- reverse sweep ----
-        Raw8<DT> ru0, ru1, rx0, rx1, rB, rC;
-        Raw8<GT> rg0, rg1;
-        auto load = [&](int r) {
-            ld_raw8<DT>(ru0, pu0 + r * su, vu, nv); ld_raw8<DT>(ru1, pu1 + r * su, vu, nv);
-            ld_raw8<DT>(rx0, px0 + r * sx, vx, nv); ld_raw8<DT>(rx1, px1 + r * sx, vx, nv);
-            ld_raw8<DT>(rB, pB + r * sB, vB, nv); ld_raw8<DT>(rC, pC + r * sC, vC, nv);
-            // idle slots and the missing second channel of an odd group carry no gradient
-            ld_raw8<GT>(rg0, pg0 + r * sg, vg, nv, w.on0); ld_raw8<GT>(rg1, pg1 + r * sg, vg, nv, w.on1);
-        };
-        load(r0 + nr - 1);
         for (int rr = nr - 1; rr >= 0; --rr) {
             const int r = r0 + rr;
             float Bf[STRIP], Cf[STRIP];
             float2 dl[STRIP], sig[STRIP], g2[STRIP], u2[STRIP];
             {
+                const uint4 *it = next_item();
                 float t0[STRIP], t1[STRIP];
-                cvt8<DT>(ru0, t0); cvt8<DT>(ru1, t1);
+                Raw8<DT> q, q2;
+                Raw8<GT> qg;
+                lds_raw8<DT>(q, it + O_U0 * STHREADS); cvt8<DT>(q, t0);
+                lds_raw8<DT>(q, it + O_U1 * STHREADS); cvt8<DT>(q, t1);
 #pragma unroll
                 for (int i = 0; i < STRIP; ++i) u2[i] = f2(t0[i], t1[i]);
-                cvt8<GT>(rg0, t0); cvt8<GT>(rg1, t1);
+                lds_raw8<GT>(qg, it + O_G0 * STHREADS); cvt8<GT>(qg, t0);
+                lds_raw8<GT>(qg, it + O_G1 * STHREADS); cvt8<GT>(qg, t1);
 #pragma unroll
                 for (int i = 0; i < STRIP; ++i) g2[i] = f2(t0[i], t1[i]);
+                lds_raw8<DT>(q, it + O_B * STHREADS); cvt8<DT>(q, Bf);
+                lds_raw8<DT>(q, it + O_C * STHREADS); cvt8<DT>(q, Cf);
+                lds_raw8<DT>(q, it + O_X0 * STHREADS); lds_raw8<DT>(q2, it + O_X1 * STHREADS);
+                soft8(q, q2, dl, sig);
             }
-            cvt8<DT>(rB, Bf); cvt8<DT>(rC, Cf);
-            soft8(rx0, rx1, dl, sig);
-            load(max(r - 1, r0));   // the block's first row is fetched twice rather than branched around
             float2 a[STRIP], p[STRIP], s[STRIP], gC[STRIP], dh[STRIP], ds[STRIP];
 #pragma unroll
             for (int i = 0; i < STRIP; ++i) {
@@ -359,11 +412,11 @@ static cudaError_t launch_sb3(const Dev &P, int grid, cudaStream_t st) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(sbwd_kernel<L, DT, G32>, cudaFuncAttributeMaxDynamicSharedMemorySize, SB_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(sbwd_kernel<L, DT, G32>, cudaFuncAttributeMaxDynamicSharedMemorySize, bw_smem<DT, G32 ? CS2D_F32 : DT>());
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    sbwd_kernel<L, DT, G32><<<grid, STHREADS, SB_SMEM, st>>>(P);
+    sbwd_kernel<L, DT, G32><<<grid, STHREADS, bw_smem<DT, G32 ? CS2D_F32 : DT>(), st>>>(P);
     return cudaGetLastError();
 }
 template <int L>

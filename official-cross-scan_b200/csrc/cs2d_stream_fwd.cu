@@ -3,8 +3,12 @@
 
 namespace cs2d {
 
+constexpr int FW_DEPTH = 4;   // rows in the staging ring (a power of two)
+template <int DT>
+constexpr int fw_smem() { return FW_DEPTH * 6 * slot_words<DT>() * STHREADS * 16; }
+
 template <int L, int DT>
-__global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 3 : 4) sfwd_kernel(const Dev P) {
+__global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 2 : 4) sfwd_kernel(const Dev P) {
     const Who<L> w(P);
     constexpr int Wp = Who<L>::Wp;
     constexpr bool FAST = DT != CS2D_F32;
@@ -27,23 +31,41 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 3 : 4) sfwd_kernel(
     const float2 bias = P.bias ? f2(__ldg(P.bias + w.d0 / P.drep), __ldg(P.bias + w.d1 / P.drep)) : bc(0.f);
     float2 *ckp = P.saved + w.ck;
 
-    Raw8<DT> ru0, ru1, rx0, rx1, rB, rC;
-    auto load = [&](int r) {
-        ld_raw8<DT>(ru0, pu0 + r * su, vu, nv); ld_raw8<DT>(ru1, pu1 + r * su, vu, nv);
-        ld_raw8<DT>(rx0, px0 + r * sx, vx, nv); ld_raw8<DT>(rx1, px1 + r * sx, vx, nv);
-        ld_raw8<DT>(rB, pB + r * sB, vB, nv); ld_raw8<DT>(rC, pC + r * sC, vC, nv);
+    // The strips of u, delta (two channels each), B and C of the next FW_DEPTH-1 rows are always in
+    // flight into this thread's ring of shared-memory slots: enough bytes on the way to keep HBM busy
+    // at 16 resident warps per SM, without holding registers while they travel.
+    extern __shared__ __align__(16) uint4 ring_all[];
+    constexpr int NT = 6, SW = slot_words<DT>();
+    uint4 *ring = ring_all + threadIdx.x;
+    auto slot = [&](int stage, int t) { return ring + ((stage * NT + t) * SW) * STHREADS; };
+    auto issue = [&](int r) {
+        const bool on = r < H;
+        const int rc = min(r, H - 1), st = r & (FW_DEPTH - 1);
+        cp_raw8<DT>(slot(st, 0), pu0 + rc * su, vu, nv, on); cp_raw8<DT>(slot(st, 1), pu1 + rc * su, vu, nv, on);
+        cp_raw8<DT>(slot(st, 2), px0 + rc * sx, vx, nv, on); cp_raw8<DT>(slot(st, 3), px1 + rc * sx, vx, nv, on);
+        cp_raw8<DT>(slot(st, 4), pB + rc * sB, vB, nv, on); cp_raw8<DT>(slot(st, 5), pC + rc * sC, vC, nv, on);
+        cp_commit();
     };
-    load(0);
+#pragma unroll
+    for (int k = 0; k < FW_DEPTH - 1; ++k) issue(k);
     float2 h_up[STRIP], a_up[STRIP];
 #pragma unroll
     for (int i = 0; i < STRIP; ++i) { h_up[i] = bc(0.f); a_up[i] = bc(0.f); }
 
     for (int r = 0; r < H; ++r) {
+        issue(r + FW_DEPTH - 1);
+        cp_wait<FW_DEPTH - 1>();   // row r has landed
         float u0[STRIP], u1[STRIP], x0[STRIP], x1[STRIP], Bf[STRIP], Cf[STRIP];
-        cvt8<DT>(ru0, u0); cvt8<DT>(ru1, u1);
-        cvt8<DT>(rx0, x0); cvt8<DT>(rx1, x1);
-        cvt8<DT>(rB, Bf); cvt8<DT>(rC, Cf);
-        load(min(r + 1, H - 1));   // in flight while this row computes (the last row is fetched twice)
+        {
+            const int st = r & (FW_DEPTH - 1);
+            Raw8<DT> q;
+            lds_raw8<DT>(q, slot(st, 0)); cvt8<DT>(q, u0);
+            lds_raw8<DT>(q, slot(st, 1)); cvt8<DT>(q, u1);
+            lds_raw8<DT>(q, slot(st, 2)); cvt8<DT>(q, x0);
+            lds_raw8<DT>(q, slot(st, 3)); cvt8<DT>(q, x1);
+            lds_raw8<DT>(q, slot(st, 4)); cvt8<DT>(q, Bf);
+            lds_raw8<DT>(q, slot(st, 5)); cvt8<DT>(q, Cf);
+        }
         float2 a[STRIP], p[STRIP], h[STRIP], s[STRIP];
         // columns past the image read u = B = C = 0: p = 0 there, and what h and s hold there only ever
         // flows further right, never into the image
@@ -73,14 +95,26 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 3 : 4) sfwd_kernel(
     }
 }
 
+template <int L, int DT>
+static cudaError_t launch_sf2(const Dev &P, int grid, cudaStream_t st) {
+    static bool attr_done[64] = {};  // per template instance and device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(sfwd_kernel<L, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, fw_smem<DT>());
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    sfwd_kernel<L, DT><<<grid, STHREADS, fw_smem<DT>(), st>>>(P);
+    return cudaGetLastError();
+}
 template <int L>
 static cudaError_t launch_sf(const Dev &P, int grid, cudaStream_t st) {
     switch (P.io_dt) {
-        case CS2D_F32: sfwd_kernel<L, CS2D_F32><<<grid, STHREADS, 0, st>>>(P); break;
-        case CS2D_F16: sfwd_kernel<L, CS2D_F16><<<grid, STHREADS, 0, st>>>(P); break;
-        default: sfwd_kernel<L, CS2D_BF16><<<grid, STHREADS, 0, st>>>(P); break;
+        case CS2D_F32: return launch_sf2<L, CS2D_F32>(P, grid, st);
+        case CS2D_F16: return launch_sf2<L, CS2D_F16>(P, grid, st);
+        default: return launch_sf2<L, CS2D_BF16>(P, grid, st);
     }
-    return cudaGetLastError();
 }
 
 // channel pairs per CTA for a row of L lanes
