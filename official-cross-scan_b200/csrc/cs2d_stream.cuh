@@ -32,6 +32,8 @@ constexpr int SNW = 4;               // warps per CTA
 constexpr int STHREADS = SNW * 32;
 constexpr int SRB = STREAM_RB;       // rows per checkpoint block
 constexpr float LN2 = 0.6931471805599453f;
+template <int V>
+struct Int { static constexpr int value = V; };   // a compile-time integer passed as a function argument
 
 // ---- predicated global access (inline PTX: the guard is a predicate, not a branch) ----------
 __device__ __forceinline__ uint4 ldg16_if(const void *p, bool on) {
@@ -139,23 +141,23 @@ __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0
 template <int DT>
 __host__ __device__ constexpr int slot_words() { return DT == CS2D_F32 ? 2 : 1; }
 // `slot` points at this thread's first word of the slot; further words follow STHREADS words later
-template <int DT>
-__device__ __forceinline__ void cp_raw8(uint4 *slot, const char *row, int mode, int nv, bool on = true) {
+template <int DT, int M>
+__device__ __forceinline__ void cp_raw8(uint4 *slot, const char *row, int nv, bool on = true) {
     const uint32_t dst = smem_addr(slot);
-    if constexpr (DT == CS2D_F32) {
-        if (mode) {
-            cp16(dst, row, on && nv >= 4);
-            cp16(dst + STHREADS * 16, row + 16, on && nv >= 8);
-            return;
-        }
+    if constexpr (DT == CS2D_F32 && M >= 1) {
+        cp16(dst, row, on && nv >= 4);
+        cp16(dst + STHREADS * 16, row + 16, on && nv >= 8);
+    } else if constexpr (DT != CS2D_F32 && M == 2) {
+        cp16(dst, row, on && nv >= 8);
+    } else if constexpr (DT != CS2D_F32 && M == 1) {
+        cp8(dst, row, on && nv >= 4);
+        cp8(dst + 8, row + 8, on && nv >= 8);
     } else {
-        if (mode == 2) { cp16(dst, row, on && nv >= 8); return; }
-        if (mode == 1) { cp8(dst, row, on && nv >= 4); cp8(dst + 8, row + 8, on && nv >= 8); return; }
+        Raw8<DT> r;   // element by element: loaded now, parked in the slot
+        ld_raw8<DT>(r, row, 0, nv, on);
+        slot[0] = make_uint4(r.w[0], r.w[1], r.w[2], r.w[3]);
+        if constexpr (DT == CS2D_F32) slot[STHREADS] = make_uint4(r.w[4], r.w[5], r.w[6], r.w[7]);
     }
-    Raw8<DT> r;   // element by element: loaded now, parked in the slot
-    ld_raw8<DT>(r, row, 0, nv, on);
-    slot[0] = make_uint4(r.w[0], r.w[1], r.w[2], r.w[3]);
-    if constexpr (DT == CS2D_F32) slot[STHREADS] = make_uint4(r.w[4], r.w[5], r.w[6], r.w[7]);
 }
 template <int DT>
 __device__ __forceinline__ void lds_raw8(Raw8<DT> &r, const uint4 *slot) {
@@ -187,8 +189,9 @@ __device__ __forceinline__ void cvt8(const Raw8<DT> &r, float (&v)[STRIP]) {
     }
 }
 // 8 results of one strip to a tensor of runtime type dt; modes as ld_raw8
-__device__ __forceinline__ void st_row8(void *base, int64_t off, int dt, int mode, int nv, bool on,
-                                        const float (&v)[STRIP]) {
+template <int M>
+__device__ __forceinline__ void st_row8(void *base, int64_t off, int dt, int nv, bool on, const float (&v)[STRIP]) {
+    constexpr int mode = M;
     if (mode && dt == CS2D_F32) {
         float *p = reinterpret_cast<float *>(base) + off;
         stg16_if(p, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3])),
@@ -301,8 +304,8 @@ __device__ __forceinline__ void srow_fwd(int j, const float2 (&a)[STRIP], const 
     }
 }
 
-// access mode of a tensor (see ld_raw8): bit set in Dev::vec8 -> 2, in Dev::vec -> 1, else 0
-__device__ __forceinline__ int vmode(const Dev &P, int bit) { return (P.vec8 & bit) ? 2 : (P.vec & bit) ? 1 : 0; }
+// access mode of the launch (see ld_raw8): every tensor allows 8-element words -> 2, 4-element words -> 1, else 0
+__device__ __forceinline__ int vmode(const Dev &P, int all) { return (P.vec8 & all) == all ? 2 : (P.vec & all) == all ? 1 : 0; }
 
 // Which channels, rows and columns a thread owns; shared by both kernels.
 template <int L>

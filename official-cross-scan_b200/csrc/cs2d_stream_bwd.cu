@@ -137,8 +137,7 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 1 : 2) sbwd_kernel(
     const char *pB = reinterpret_cast<const char *>(P.B) + ((int64_t)w.b * P.B_bs + (int64_t)w.g * P.B_gs + w.c0) * es;
     const char *pC = reinterpret_cast<const char *>(P.C) + ((int64_t)w.b * P.C_bs + (int64_t)w.g * P.C_gs + w.c0) * es;
     const int64_t su = P.u_hs * es, sx = P.dl_hs * es, sg = P.o_hs * eso, sB = P.B_hs * es, sC = P.C_hs * es;
-    const int vu = vmode(P, VEC_U), vx = vmode(P, VEC_DELTA), vB = vmode(P, VEC_B), vC = vmode(P, VEC_C), vg = vmode(P, VEC_OUT),
-              vd = vmode(P, VEC_DU);
+    const int vm = vmode(P, VEC_U | VEC_DELTA | VEC_B | VEC_C | VEC_OUT | VEC_DU);   // one access mode for the launch
     const bool softplus = P.softplus != 0;
     const float2 Araw = f2(__ldg(P.A + (int64_t)w.d0 * P.A_ds), __ldg(P.A + (int64_t)w.d1 * P.A_ds));
     const float2 A2 = mul2(Araw, bc(LOG2E));
@@ -160,32 +159,36 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 1 : 2) sbwd_kernel(
 
     // ---- producer side of the staging ring ----
     int pb = P.nck - 1, pp = 0, ps = 0;   // next item: block, position inside it (0 = row above, 1..nr recompute, then reverse), slot
-    auto issue_next = [&]() {
-        if (pb >= 0) {
-            const int r0p = pb * SRB, nrp = min(SRB, H - r0p);
-            uint4 *s = ring + ps * SLOTW * STHREADS;
-            if (pp == 0) {
-                const bool top = r0p > 0;
-                const int rt = max(r0p - 1, 0);
-                cp_raw8<DT>(s + O_X0 * STHREADS, px0 + rt * sx, vx, nv, top);
-                cp_raw8<DT>(s + O_X1 * STHREADS, px1 + rt * sx, vx, nv, top);
-                const float2 *ck = ckp + (int64_t)max(pb - 1, 0) * Wp;
+    auto issue_item = [&](auto mode) {
+        constexpr int M = decltype(mode)::value;
+        const int r0p = pb * SRB, nrp = min(SRB, H - r0p);
+        uint4 *s = ring + ps * SLOTW * STHREADS;
+        if (pp == 0) {
+            const bool top = r0p > 0;
+            const int rt = max(r0p - 1, 0);
+            cp_raw8<DT, M>(s + O_X0 * STHREADS, px0 + rt * sx, nv, top);
+            cp_raw8<DT, M>(s + O_X1 * STHREADS, px1 + rt * sx, nv, top);
+            const float2 *ck = ckp + (int64_t)max(pb - 1, 0) * Wp;
 #pragma unroll
-                for (int k = 0; k < 4; ++k) cp16(smem_addr(s + (O_CK + k) * STHREADS), ck + 2 * k, top);
-            } else {
-                const bool rev = pp > nrp;
-                const int r = rev ? r0p + 2 * nrp - pp : r0p + pp - 1;
-                cp_raw8<DT>(s + O_U0 * STHREADS, pu0 + r * su, vu, nv); cp_raw8<DT>(s + O_U1 * STHREADS, pu1 + r * su, vu, nv);
-                cp_raw8<DT>(s + O_X0 * STHREADS, px0 + r * sx, vx, nv); cp_raw8<DT>(s + O_X1 * STHREADS, px1 + r * sx, vx, nv);
-                cp_raw8<DT>(s + O_B * STHREADS, pB + r * sB, vB, nv);
-                if (rev) {
-                    cp_raw8<DT>(s + O_C * STHREADS, pC + r * sC, vC, nv);
-                    // idle slots and the missing second channel of an odd group carry no gradient
-                    cp_raw8<GT>(s + O_G0 * STHREADS, pg0 + r * sg, vg, nv, w.on0);
-                    cp_raw8<GT>(s + O_G1 * STHREADS, pg1 + r * sg, vg, nv, w.on1);
-                }
+            for (int k = 0; k < 4; ++k) cp16(smem_addr(s + (O_CK + k) * STHREADS), ck + 2 * k, top);
+        } else {
+            const bool rev = pp > nrp;
+            const int r = rev ? r0p + 2 * nrp - pp : r0p + pp - 1;
+            cp_raw8<DT, M>(s + O_U0 * STHREADS, pu0 + r * su, nv); cp_raw8<DT, M>(s + O_U1 * STHREADS, pu1 + r * su, nv);
+            cp_raw8<DT, M>(s + O_X0 * STHREADS, px0 + r * sx, nv); cp_raw8<DT, M>(s + O_X1 * STHREADS, px1 + r * sx, nv);
+            cp_raw8<DT, M>(s + O_B * STHREADS, pB + r * sB, nv);
+            if (rev) {
+                cp_raw8<DT, M>(s + O_C * STHREADS, pC + r * sC, nv);
+                // idle slots and the missing second channel of an odd group carry no gradient
+                cp_raw8<GT, M>(s + O_G0 * STHREADS, pg0 + r * sg, nv, w.on0);
+                cp_raw8<GT, M>(s + O_G1 * STHREADS, pg1 + r * sg, nv, w.on1);
             }
-            if (++pp > 2 * nrp) { pp = 0; --pb; }
+        }
+        if (++pp > 2 * nrp) { pp = 0; --pb; }
+    };
+    auto issue_next = [&]() {
+        if (pb >= 0) {   // one (uniform) branch on the access mode per item, not one per strip
+            if (vm == 2) issue_item(Int<2>()); else if (vm == 1) issue_item(Int<1>()); else issue_item(Int<0>());
         }
         cp_commit();   // an empty group once everything has been asked for: the wait below counts groups
         ps = ps + 1 == BW_DEPTH ? 0 : ps + 1;
@@ -209,10 +212,10 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 1 : 2) sbwd_kernel(
         float x0[STRIP], x1[STRIP];
         cvt8<DT>(r0, x0); cvt8<DT>(r1, x1);
 #pragma unroll
-        for (int i = 0; i < STRIP; ++i) {
-            dl[i] = add2(f2(x0[i], x1[i]), bias);
-            sig[i] = bc(1.f);
-            if (softplus) softplus2<FAST, true>(dl[i], dl[i], sig[i]);
+        for (int i = 0; i < STRIP; ++i) { dl[i] = add2(f2(x0[i], x1[i]), bias); sig[i] = bc(1.f); }
+        if (softplus) {
+#pragma unroll
+            for (int i = 0; i < STRIP; ++i) softplus2<FAST, true>(dl[i], dl[i], sig[i]);
         }
     };
 
@@ -376,10 +379,14 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 1 : 2) sbwd_kernel(
                 v[i] = dBv.x + dBv.y;
                 v[8 + i] = dCv.x + dCv.y;
             }
-            st_row8(P.du, q0 + (int64_t)r * W, DT, vd, nv, w.on0, du0);
-            st_row8(P.ddelta, q0 + (int64_t)r * W, DT, vd, nv, w.on0, dd0);
-            st_row8(P.du, q1 + (int64_t)r * W, DT, vd, nv, w.on1, du1);
-            st_row8(P.ddelta, q1 + (int64_t)r * W, DT, vd, nv, w.on1, dd1);
+            auto store = [&](auto mode) {
+                constexpr int M = decltype(mode)::value;
+                st_row8<M>(P.du, q0 + (int64_t)r * W, DT, nv, w.on0, du0);
+                st_row8<M>(P.ddelta, q0 + (int64_t)r * W, DT, nv, w.on0, dd0);
+                st_row8<M>(P.du, q1 + (int64_t)r * W, DT, nv, w.on1, du1);
+                st_row8<M>(P.ddelta, q1 + (int64_t)r * W, DT, nv, w.on1, dd1);
+            };
+            if (vm == 2) store(Int<2>()); else if (vm == 1) store(Int<1>()); else store(Int<0>());
             add_dbc_rows<L>(v, dBp + (int64_t)r * W, dCp + (int64_t)r * W, w.c0, W, vBC, lane);
         }
     }

@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 2 : 4) sfwd_kernel(
     const int64_t su = P.u_hs * es, sx = P.dl_hs * es, sB = P.B_hs * es, sC = P.C_hs * es;
     const int64_t o0 = (int64_t)w.b * P.o_bs + (int64_t)w.d0 * P.o_ds + w.c0, o1 = (int64_t)w.b * P.o_bs + (int64_t)w.d1 * P.o_ds + w.c0;
     const int64_t so = P.o_hs;
-    const int vu = vmode(P, VEC_U), vx = vmode(P, VEC_DELTA), vB = vmode(P, VEC_B), vC = vmode(P, VEC_C), vo = vmode(P, VEC_OUT);
+    const int vm = vmode(P, VEC_U | VEC_DELTA | VEC_B | VEC_C | VEC_OUT);   // one access mode for the launch
     const int out_dt = P.out_dt;
     const bool softplus = P.softplus != 0, keep = !P.ck_roll && w.on0;
     const float2 A2 = mul2(f2(__ldg(P.A + (int64_t)w.d0 * P.A_ds), __ldg(P.A + (int64_t)w.d1 * P.A_ds)), bc(LOG2E));
@@ -38,13 +38,17 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 2 : 4) sfwd_kernel(
     constexpr int NT = 6, SW = slot_words<DT>();
     uint4 *ring = ring_all + threadIdx.x;
     auto slot = [&](int stage, int t) { return ring + ((stage * NT + t) * SW) * STHREADS; };
-    auto issue = [&](int r) {
+    auto issue_m = [&](int r, auto mode) {
+        constexpr int M = decltype(mode)::value;
         const bool on = r < H;
         const int rc = min(r, H - 1), st = r & (FW_DEPTH - 1);
-        cp_raw8<DT>(slot(st, 0), pu0 + rc * su, vu, nv, on); cp_raw8<DT>(slot(st, 1), pu1 + rc * su, vu, nv, on);
-        cp_raw8<DT>(slot(st, 2), px0 + rc * sx, vx, nv, on); cp_raw8<DT>(slot(st, 3), px1 + rc * sx, vx, nv, on);
-        cp_raw8<DT>(slot(st, 4), pB + rc * sB, vB, nv, on); cp_raw8<DT>(slot(st, 5), pC + rc * sC, vC, nv, on);
+        cp_raw8<DT, M>(slot(st, 0), pu0 + rc * su, nv, on); cp_raw8<DT, M>(slot(st, 1), pu1 + rc * su, nv, on);
+        cp_raw8<DT, M>(slot(st, 2), px0 + rc * sx, nv, on); cp_raw8<DT, M>(slot(st, 3), px1 + rc * sx, nv, on);
+        cp_raw8<DT, M>(slot(st, 4), pB + rc * sB, nv, on); cp_raw8<DT, M>(slot(st, 5), pC + rc * sC, nv, on);
         cp_commit();
+    };
+    auto issue = [&](int r) {   // one (uniform) branch per row instead of one per strip
+        if (vm == 2) issue_m(r, Int<2>()); else if (vm == 1) issue_m(r, Int<1>()); else issue_m(r, Int<0>());
     };
 #pragma unroll
     for (int k = 0; k < FW_DEPTH - 1; ++k) issue(k);
@@ -69,12 +73,17 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 2 : 4) sfwd_kernel(
         float2 a[STRIP], p[STRIP], h[STRIP], s[STRIP];
         // columns past the image read u = B = C = 0: p = 0 there, and what h and s hold there only ever
         // flows further right, never into the image
+        float2 dl[STRIP];
+#pragma unroll
+        for (int i = 0; i < STRIP; ++i) dl[i] = add2(f2(x0[i], x1[i]), bias);
+        if (softplus) {
+#pragma unroll
+            for (int i = 0; i < STRIP; ++i) { float2 unused; softplus2<FAST, false>(dl[i], dl[i], unused); }
+        }
 #pragma unroll
         for (int i = 0; i < STRIP; ++i) {
-            float2 dl = add2(f2(x0[i], x1[i]), bias), unused;
-            if (softplus) softplus2<FAST, false>(dl, dl, unused);
-            a[i] = ex2_2(mul2(dl, A2));
-            p[i] = mul2(bc(Bf[i]), mul2(dl, f2(u0[i], u1[i])));
+            a[i] = ex2_2(mul2(dl[i], A2));
+            p[i] = mul2(bc(Bf[i]), mul2(dl[i], f2(u0[i], u1[i])));
         }
         srow_fwd<L, true>(j, a, p, h_up, a_up, h, s);
         float y0[STRIP], y1[STRIP];
@@ -84,8 +93,13 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 2 : 4) sfwd_kernel(
             y0[i] = y.x; y1[i] = y.y;
             h_up[i] = h[i]; a_up[i] = a[i];
         }
-        st_row8(P.out, o0 + r * so, out_dt, vo, nv, w.on0, y0);
-        st_row8(P.out, o1 + r * so, out_dt, vo, nv, w.on1, y1);
+        if (vm == 2) {
+            st_row8<2>(P.out, o0 + r * so, out_dt, nv, w.on0, y0); st_row8<2>(P.out, o1 + r * so, out_dt, nv, w.on1, y1);
+        } else if (vm == 1) {
+            st_row8<1>(P.out, o0 + r * so, out_dt, nv, w.on0, y0); st_row8<1>(P.out, o1 + r * so, out_dt, nv, w.on1, y1);
+        } else {
+            st_row8<0>(P.out, o0 + r * so, out_dt, nv, w.on0, y0); st_row8<0>(P.out, o1 + r * so, out_dt, nv, w.on1, y1);
+        }
         // checkpoint: the last row of every block but the last one (every lane: the row is read back whole)
         if (keep && (r + 1) % SRB == 0 && r + 1 < H) {
             float4 *pk = reinterpret_cast<float4 *>(ckp + (int64_t)(r / SRB) * Wp);
