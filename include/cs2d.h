@@ -229,16 +229,6 @@ int cs2d_abi_version(void);
 /* Number of kernels this library has launched in this process (for benchmarks). */
 int64_t cs2d_launch_count(void);
 
-/*
- * Profiling builds only (csrc/build.sh -DCS2D_PHASE_TIMERS): reads and clears the cycles that
- * warp 0 of every CTA spent in the eight phases of a step (prefetch, bulk-copy wait, write-out,
- * staging, dB/dC flush + B/C staging, wait for the staged tiles, recompute of h, sweep), summed
- * over all CTAs launched since the last call: out16[0..7] forward, out16[8..15] backward
- * (the forward has no recompute; its compute is under "sweep").  Synchronises with the device.
- * A normal build returns CS2D_ERR_UNSUPPORTED.
- */
-int cs2d_phase_cycles(unsigned long long *out16);
-
 #ifdef __cplusplus
 }
 #endif

@@ -5,8 +5,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# CS2D_LIB selects another build of the same library (e.g. one with per-phase cycle counters)
-LIB_PATH = os.environ.get("CS2D_LIB") or os.path.join(_HERE, "libcs2d.so")
+LIB_PATH = os.path.join(_HERE, "libcs2d.so")
 
 F32, F16, BF16 = 0, 1, 2
 NOALLOC_SCRATCH_BYTES = 32 << 20  # CS2D_NOALLOC_SCRATCH_BYTES
@@ -82,8 +81,6 @@ def lib():
         L.cs2d_bwd_noalloc.restype = ctypes.c_int
         L.cs2d_bwd_noalloc.argtypes = [ctypes.POINTER(Problem), vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
         L.cs2d_last_error.restype = ctypes.c_char_p
-        L.cs2d_phase_cycles.restype = ctypes.c_int
-        L.cs2d_phase_cycles.argtypes = [ctypes.POINTER(ctypes.c_ulonglong)]
         L.cs2d_abi_version.restype = ctypes.c_int
         L.cs2d_launch_count.restype = ctypes.c_int64
         L.cs2d_device_status.restype = ctypes.c_int

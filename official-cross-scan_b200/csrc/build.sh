@@ -1,8 +1,7 @@
 #!/usr/bin/env bash
 # Builds the cs2d shared library in-tree for sm_100a.
 #   official-cross-scan_b200/csrc/build.sh [extra nvcc flags]
-# CS2D_OUT=<file> writes the library elsewhere, e.g. a profiling build with per-phase cycle
-# counters:  CS2D_OUT=/tmp/libcs2d_timers.so csrc/build.sh -DCS2D_PHASE_TIMERS
+# CS2D_OUT=<file> writes the library elsewhere.
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 out="${CS2D_OUT:-$here/../cs2d/libcs2d.so}"

@@ -1,7 +1,6 @@
 // extern "C" boundary of the cs2d library: validation, launch geometry, errors.
 // Mirrors the checks of the reference host binding
 // (src/cusoflex/selective_scan_oflex.cpp:188-245 and :298-391) on raw pointers.
-#include <cstdlib>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -95,8 +94,7 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, 
                         p->ncols, p->dstate);
         // The common geometry (8 state-pair slots, one channel group, one column tile) runs
         // warp-specialised when the second tile set fits: staging warps replace the bulk copies.
-        static const bool ws_off = [] { const char *e = getenv("CS2D_BWD_WS"); return e && e[0] == '0'; }();
-        if (!ws_off && NPp == 8 && CG == 1 &&
+        if (NPp == 8 && CG == 1 &&
             bwd_smem_bytes(L, CG, NPp, npass * CP, g->acc, W, es, eso, false, tiled, true) <= kMaxSmem) {
             g->ws = 1;
             g->bulk = 0;
@@ -108,8 +106,7 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, 
             return fail(CS2D_ERR_UNSUPPORTED, "ncols=%d with dstate=%d needs more shared memory than one SM has",
                         p->ncols, p->dstate);
         // warp-specialised like the backward, as long as two CTAs still share an SM
-        static const bool fws_off = [] { const char *e = getenv("CS2D_FWD_WS"); return e && e[0] == '0'; }();
-        if (!fws_off && NPp == 8 && CG == 1 &&
+        if (NPp == 8 && CG == 1 &&
             2 * (fwd_smem_bytes(L, CG, NPp, W, es, false, npass * CP, tiled, true) + kCtaReserve) <= kSmSmem) {
             g->ws = 1;
             g->bulk = 0;
@@ -199,9 +196,6 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
 }
 }  // namespace cs2d
 
-#ifdef CS2D_PHASE_TIMERS
-namespace cs2d { void phase_read_fwd(unsigned long long *); void phase_read_bwd(unsigned long long *); }
-#endif
 using namespace cs2d;
 
 extern "C" {
@@ -659,17 +653,5 @@ int cs2d_device_status(void) {
 const char *cs2d_last_error(void) { return g_err; }
 int cs2d_abi_version(void) { return CS2D_ABI_VERSION; }
 int64_t cs2d_launch_count(void) { return g_launches.load(); }
-
-int cs2d_phase_cycles(unsigned long long *out16) {
-#ifdef CS2D_PHASE_TIMERS
-    if (!out16) return fail(CS2D_ERR_INVALID, "out16 is NULL");
-    phase_read_fwd(out16);
-    phase_read_bwd(out16 + 8);
-    return CS2D_OK;
-#else
-    (void)out16;
-    return fail(CS2D_ERR_UNSUPPORTED, "this library was built without -DCS2D_PHASE_TIMERS");
-#endif
-}
 
 }  // extern "C"

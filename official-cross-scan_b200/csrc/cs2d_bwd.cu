@@ -29,15 +29,6 @@ namespace cs2d {
 
 static_assert(RB == STREAM_RB, "the tile backward reads the streaming forward's checkpoints at its own row-block cadence");
 
-#ifdef CS2D_PHASE_TIMERS
-__device__ unsigned long long g_phase_bwd[8];
-void phase_read_bwd(unsigned long long *o) {
-    unsigned long long z[8] = {};
-    cudaMemcpyFromSymbol(o, g_phase_bwd, sizeof(z));
-    cudaMemcpyToSymbol(g_phase_bwd, z, sizeof(z));
-}
-#endif
-
 template <int L>
 struct BwdSmem {
     static constexpr int Wp = L * STRIP, CW = 32 / L;
@@ -271,7 +262,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
             asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WS_REGS_STAGE));
             for (int k = 0; k < steps; ++k) {
                 const int set = k & 1;
-                if (k >= 2 && !mbar_wait_bounded(freeb + set, ((k >> 1) - 1) & 1)) {
+                if (k >= 2 && !mbar_wait_bounded_lazy(freeb + set, ((k >> 1) - 1) & 1)) {
                     atomicOr(P.status, ERR_STAGE_TIMEOUT);  // the compute warps give up on `full` in turn
                     return;
                 }
@@ -285,7 +276,6 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     auto cta_sync = [&]() {
         if constexpr (WS) group_sync(1, WS_COMPUTE); else __syncthreads();
     };
-    PT_DECL
     for (int step = 0; step <= steps; ++step) {
         const int blk = nblk - 1 - step / npass, pass = step % npass;  // bottom-up
         const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
@@ -326,7 +316,6 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
             }
             }
         }
-        PT_MARK(PT_PREFETCH)
         // ---- phase A: write out the previous step, stage this one -------------------
         if (!WS && bulk) {
             if (warp == 0 && step + 1 < steps) issue(step + 1);   // lands while this step computes
@@ -337,7 +326,6 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                 return;
             }
         }
-        PT_MARK(PT_BULK_WAIT)
         {
             // tiles of the previous step (being written out) and of this one
             float *prev = WS && (pstep & 1) ? set1 : smem, *cur = WS && (step & 1) ? set1 : smem;
@@ -394,7 +382,6 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                     q[1] += dbp;
                 }
             }
-            PT_MARK(PT_WRITE_OUT)
             if constexpr (WS) {
                 // the previous step's tile set may be refilled by the staging warps from here on
                 if (step > 0) mbar_arrive(freeb + (pstep & 1));
@@ -402,7 +389,6 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                 // every thread replaces the tile entries it has just read (same item mapping)
                 stage_step(step, smem, raw + (size_t)(step & 1) * stage_bytes, tid, nthr);
             }
-            PT_MARK(PT_STAGE)
             // a row block is complete when its last pass has been written out
             if (acc_on && pnr > 0 && ppass == npass - 1) {
                 const int itemsB = NPp * RB * Wp;  // one float2 (two states) per item
@@ -467,7 +453,6 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                 }
             }
         }
-        PT_MARK(PT_FLUSH_BC)
         if constexpr (WS) {  // this step's tiles have to be complete
             const bool ok = nr == 0 || mbar_wait_bounded(full + (step & 1), (step >> 1) & 1);
             if (group_or(2, WS_COMPUTE, !ok)) {  // the staging warps stopped (they flagged why): leave together
@@ -476,7 +461,6 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
             }
         }
         cta_sync();
-        PT_MARK(PT_TILES_WAIT)
         if (nr == 0) break;
 
         // ---- compute ---------------------------------------------------------------------
@@ -534,7 +518,6 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                     }
                 }
             }
-            PT_MARK(PT_RECOMPUTE)
             // -- adjoint row below the block --
             float2 m_dn[STRIP], a_dn[STRIP];
             float2 *adj = P.adj + (((int64_t)b * P.dim + d) * NPp + pp) * Wp + j * STRIP;
@@ -693,11 +676,11 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                         duv[i] = dl[i] * S1;
                         ddv[i] = fmaf(uu[i], S1, t2.x + t2.y);
                         dAacc = fma2(bc(dl[i]), G, dAacc);
-                        if (want_decay) ddecay_acc = add2(ddecay_acc, Gh);
+                        ddecay_acc = add2(ddecay_acc, Gh);   // only read when dA_decay is wanted; an add is cheaper than a branch
                         const float2 dBv = mul2(bc(dl[i] * uu[i] * wv), eps);
                         const float2 yt = fma2(p[i], bc(0.25f), sub2(hrow[i], s[i]));
                         const float2 dCv = mul2(bc(gg[i] * wv), yt);
-                        if (P.mw) dwacc = fma2(gC[i], yt, dwacc);   // dy * (C*(h - s + p/4)): this pair's share of dy*y
+                        dwacc = fma2(gC[i], yt, dwacc);   // dy * (C*(h - s + p/4)): this pair's share of dy*y (read when merging)
                         if constexpr (CW == 1) {
                             if (acc_on) {
                                 float2 *qb = accB + pos2<L>(j * STRIP + i), *qc = accC + pos2<L>(j * STRIP + i);
@@ -769,9 +752,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
             }
         }
         cta_sync();
-        PT_MARK(PT_SWEEP)
     }
-    PT_FLUSH(g_phase_bwd)
 
     // ---- per-channel parameter gradients ---------------------------------------
     if (want_decay) {

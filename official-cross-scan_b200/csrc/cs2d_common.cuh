@@ -113,22 +113,6 @@ enum { VEC_U = 1, VEC_DELTA = 2, VEC_B = 4, VEC_C = 8, VEC_OUT = 16, VEC_DU = 32
 // through cs2d_device_status().
 enum { ERR_BULK_COPY_TIMEOUT = 1, ERR_STAGE_TIMEOUT = 2 };
 
-// ---- per-phase cycle counters (only in builds with -DCS2D_PHASE_TIMERS) ------------------
-// Warp 0 of every CTA adds the cycles it spends in each phase of a step to eight global
-// counters, read by cs2d_phase_cycles().  PT_MARK(k) charges the time since the previous
-// mark to phase k.  Compiled out of the normal build.
-#ifdef CS2D_PHASE_TIMERS
-#define PT_DECL long long pt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long pt_t = clock64();
-#define PT_MARK(k) { const long long pt_now = clock64(); pt_acc[k] += pt_now - pt_t; pt_t = pt_now; }
-#define PT_FLUSH(sym) \
-    if (threadIdx.x == 0) for (int pt_k = 0; pt_k < 8; ++pt_k) atomicAdd(&sym[pt_k], (unsigned long long)pt_acc[pt_k]);
-#else
-#define PT_DECL
-#define PT_MARK(k)
-#define PT_FLUSH(sym)
-#endif
-enum { PT_PREFETCH = 0, PT_BULK_WAIT, PT_WRITE_OUT, PT_STAGE, PT_FLUSH_BC, PT_TILES_WAIT, PT_RECOMPUTE, PT_SWEEP };
-
 // ---- packed fp32x2 helpers -------------------------------------------------
 __device__ __forceinline__ float2 f2(float x, float y) { return make_float2(x, y); }
 __device__ __forceinline__ float2 bc(float x) { return make_float2(x, x); }
@@ -262,6 +246,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
     for (int i = 0; i < (1 << 22); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i > 64) __nanosleep(64);
+    }
+    return false;
+}
+// The same for a warp that runs well ahead of the one it waits for (the staging warps): it backs
+// off at once and for longer, so that its polling does not take issue slots from the warps that
+// share its scheduler.  Still bounded: 2^21 polls of >= 256 ns.
+__device__ __forceinline__ bool mbar_wait_bounded_lazy(uint64_t *bar, uint32_t parity) {
+    for (int i = 0; i < (1 << 21); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(256);
     }
     return false;
 }

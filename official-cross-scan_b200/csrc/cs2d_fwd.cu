@@ -15,15 +15,6 @@
 
 namespace cs2d {
 
-#ifdef CS2D_PHASE_TIMERS
-__device__ unsigned long long g_phase_fwd[8];
-void phase_read_fwd(unsigned long long *o) {
-    unsigned long long z[8] = {};
-    cudaMemcpyFromSymbol(o, g_phase_fwd, sizeof(z));
-    cudaMemcpyToSymbol(g_phase_fwd, z, sizeof(z));
-}
-#endif
-
 template <int L>
 struct FwdSmem {
     static constexpr int Wp = L * STRIP, CW = 32 / L;
@@ -222,7 +213,7 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
             asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FWS_REGS_STAGE));
             for (int k = 0; k < steps; ++k) {
                 const int set = k & 1;
-                if (k >= 2 && !mbar_wait_bounded(freeb + set, ((k >> 1) - 1) & 1)) {
+                if (k >= 2 && !mbar_wait_bounded_lazy(freeb + set, ((k >> 1) - 1) & 1)) {
                     atomicOr(P.status, ERR_STAGE_TIMEOUT);  // the compute warps give up on `full` in turn
                     return;
                 }
@@ -236,7 +227,6 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
     auto cta_sync = [&]() {
         if constexpr (WS) group_sync(1, FWS_COMPUTE); else __syncthreads();
     };
-    PT_DECL
     for (int step = 0; step <= steps; ++step) {
         const int blk = step / P.npass, pass = step % P.npass;
         const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
@@ -255,7 +245,6 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
 #pragma unroll
             for (int k = 0; k < STRIP / 2; ++k) ck_pre[k] = ok ? pk[k] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        PT_MARK(PT_PREFETCH)
         // ---- phase A: write out the previous step, stage this one -------------------
         if (!WS && bulk) {
             if (warp == 0 && step + 1 < steps) issue(step + 1);   // lands while this step computes
@@ -266,7 +255,6 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
                 return;
             }
         }
-        PT_MARK(PT_BULK_WAIT)
         {
             const int pstep = step - 1;
             const int pblk = pstep / P.npass, ppass = pstep % P.npass;
@@ -305,7 +293,6 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
                     }
                 }
             }
-            PT_MARK(PT_WRITE_OUT)
             if constexpr (WS) {
                 // the previous step's tile set may be refilled by the staging warps from here on
                 if (step > 0) mbar_arrive(freeb + (pstep & 1));
@@ -313,7 +300,6 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
                 // every thread replaces the tile entries it has just read (same item mapping)
                 stage_step(step, smem, raw + (size_t)(step & 1) * stage_bytes, tid, nthr);
             }
-            PT_MARK(PT_STAGE)
             if (nr > 0) {
                 if (pass == 0) stage_BC<L>(P, b, g, r0, nr, sB, sC, fh, fw, tid, nthr);
                 if (has_left) {  // column left of this tile: h, s written by the tile to the left; delta
@@ -340,7 +326,6 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
                 }
             }
         }
-        PT_MARK(PT_FLUSH_BC)
         if constexpr (WS) {  // this step's tiles have to be complete
             const bool ok = nr == 0 || mbar_wait_bounded(full + (step & 1), (step >> 1) & 1);
             if (group_or(2, FWS_COMPUTE, !ok)) {  // the staging warps stopped (they flagged why): leave together
@@ -349,7 +334,6 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
             }
         }
         cta_sync();
-        PT_MARK(PT_TILES_WAIT)
         if (nr == 0) break;
 
         // ---- compute: RB rows of CP channels ----------------------------------------
@@ -414,9 +398,7 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
             }
         }
         cta_sync();
-        PT_MARK(PT_SWEEP)
     }
-    PT_FLUSH(g_phase_fwd)
 }
 
 template <int L>

@@ -191,16 +191,17 @@ __device__ __forceinline__ void cvt8(const Raw8<DT> &r, float (&v)[STRIP]) {
 // 8 results of one strip to a tensor of runtime type dt; modes as ld_raw8
 template <int M>
 __device__ __forceinline__ void st_row8(void *base, int64_t off, int dt, int nv, bool on, const float (&v)[STRIP]) {
-    constexpr int mode = M;
-    if (mode && dt == CS2D_F32) {
+    if constexpr (M == 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (on && k < nv) st_elem(base, off + k, dt, v[k]);
+    } else if (dt == CS2D_F32) {
         float *p = reinterpret_cast<float *>(base) + off;
         stg16_if(p, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3])),
                  on && nv >= 4);
         stg16_if(p + 4, make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7])),
                  on && nv >= 8);
-        return;
-    }
-    if (mode) {
+    } else {
         uint4 raw;
         if (dt == CS2D_BF16) {
             *reinterpret_cast<__nv_bfloat162 *>(&raw.x) = __floats2bfloat162_rn(v[0], v[1]);
@@ -214,17 +215,13 @@ __device__ __forceinline__ void st_row8(void *base, int64_t off, int dt, int nv,
             *reinterpret_cast<__half2 *>(&raw.w) = __floats2half2_rn(v[6], v[7]);
         }
         uint16_t *p = reinterpret_cast<uint16_t *>(base) + off;
-        if (mode == 2) {
+        if constexpr (M == 2) {
             stg16_if(p, raw, on && nv >= 8);
         } else {
             stg8_if(p, make_uint2(raw.x, raw.y), on && nv >= 4);
             stg8_if(p + 4, make_uint2(raw.z, raw.w), on && nv >= 8);
         }
-        return;
     }
-#pragma unroll
-    for (int k = 0; k < 8; ++k)
-        if (on && k < nv) st_elem(base, off + k, dt, v[k]);
 }
 
 __device__ __forceinline__ float lg2(float x) {
