@@ -6,8 +6,13 @@ elements per second (B*K*D*H*W*N per pass) and the fraction of the HBM roofline.
 
 One process per GPU (torchrun for N > 1).  A step is one forward plus one
 backward of the operator over one synthetic batch; with N > 1 every rank owns
-its own batch shard (weak scaling) and the step ends with the single
-all-reduce of the per-channel parameter gradients.  Rank 0 prints one JSON line.
+its own batch of the configured size (weak scaling, the headline `value`) and
+the step ends with the single all-reduce of the per-channel parameter
+gradients.  The same line carries, as sub-records, the split the benchmark
+configuration itself names - the configured batch sharded over the N ranks
+("strong") with a check that the all-reduced parameter gradients of the shards
+equal the single-GPU result - and the four-corner operator on the
+segmentation-scale configuration ("cross").  Rank 0 prints one JSON line.
 """
 import argparse
 import ctypes
@@ -117,45 +122,59 @@ def cpu_sample_size(shape, budget_s):
     return int(max(1, min(shape[0], budget_s * rate / per_sample)))
 
 
-def run_reference(args, shape, name):
+def config_dict(name, shape, dtype, world):
+    return {"workload": name, "shape_BKDNHW": list(shape), "io_dtype": str(dtype)[6:], "per_gpu_batch": shape[0],
+            "l2": "inputs larger than L2 (no flush needed)",
+            "sharding": "batch per rank, one all-reduce of the parameter gradients" if world > 1 else "none"}
+
+
+def run_reference(args, shape, name, dtype):
     """The reference ships no CPU implementation of this operator (its only
     implementation is the CUDA extension), so the reference arm times the CPU
-    restatement of its algorithm on the host cores, as a bounded sample."""
+    restatement of its algorithm on the host cores: one rank's whole batch per
+    step when that takes a few seconds, else a bounded sample of it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    from cs2d.synthetic import elements
     B, K, D, N, H, W = shape
+    rate = cpu_port(shape, 1, 1)[0]
     for _ in range(args.warmup):
         cpu_port(shape, 1, 1)
-    sample = cpu_sample_size(shape, budget_s=20.0 / max(1, args.steps))
+    full_s = elements(*shape) / rate
+    sample = B if full_s <= 8.0 else int(max(1, min(B, 8.0 * rate / elements(1, *shape[1:]))))
     val, cores, sec = cpu_port(shape, sample, max(1, args.steps))
     what = f"{sample} of {B} samples of {name} per step, float32, OpenMP"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "shape_BKDNHW": list(shape), "sample": what},
+        "config": config_dict(name, shape, dtype, args.gpus),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": what},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
 
 
-def run_cross(args, shape, dtype, host, dev, world, rank, timed, real_stdout):
+def measure_cross(name, steps, warmup, dev, world, rank, timed, batch=0):
     """The four-corner operator (directions, shared u / dy and the weighted merge inside the kernels),
-    forward + backward on resident inputs.  Algorithmic bytes of this operator: u, y, dy, du once per
-    channel, delta and ddelta per direction and channel, B, C, dB, dC per direction and state."""
+    forward + backward on resident inputs, with the all-reduce of the parameter gradients in the
+    timed region.  Algorithmic bytes of this operator: u, y, dy, du once per channel, delta and ddelta
+    per direction and channel, B, C, dB, dC per direction and state."""
     import torch
-    import torch.distributed as dist
     import cs2d
     from cs2d import cross, parallel
-    B, K, D, N, H, W = shape
+    from cs2d.synthetic import CONFIGS, make_inputs
+    B, K, D, N, H, W, dtype = CONFIGS[name]
+    B = batch or B
     s = 4 if dtype == torch.float32 else 2
+    host = make_inputs(B, K, D, N, H, W, dtype=dtype, seed=rank)
     gen = torch.Generator().manual_seed(100 + rank)
     u0 = host["u"][:, :D].to(dev)                      # direction 0 of the synthetic input is the image itself
     dy = torch.randn(B, D, H, W, generator=gen).to(dtype).to(dev)
     w = torch.full((K, D), 1.0 / K, device=dev)
-    t = {k: (v.to(dev) if v is not None else None) for k, v in host.items()}
+    t = {k: (v.to(dev) if v is not None else None) for k, v in host.items() if k not in ("u", "dout")}
+    del host
 
     def step():
         y, saved = cross._dir_forward(u0, t["delta"], t["A"], t["B"], t["C"], w, t["D"], t["delta_bias"], True)
@@ -165,33 +184,25 @@ def run_cross(args, shape, dtype, host, dev, world, rank, timed, real_stdout):
             parallel.allreduce_param_grads(flat)
         return y, g
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
     n0 = cs2d.launch_count()
-    with ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else dev.index) as clk:
-        ms = timed(step, args.steps)
+    ms = timed(step, steps) / steps
     launches = cs2d.launch_count() - n0
+    assert cs2d.device_status() == 0, "a kernel gave up on a bounded wait"
     el = B * K * D * N * H * W * world
     nbytes = B * H * W * s * (5 * D + 3 * K * D + 6 * K * N)
     peak, peak_kind = load_peaks()
-    achieved = nbytes / (ms / args.steps * 1e-3) / 1e9
-    sys.stdout.flush()
-    os.dup2(real_stdout, 1)
-    if rank == 0:
-        print(json.dumps({
-            "metric": METRIC, "value": el / (ms / args.steps * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.config, "op": "four-corner operator with fusion weights",
-                       "shape_BKDNHW": list(shape), "io_dtype": str(dtype)[6:], "per_gpu_batch": B,
-                       "l2": "inputs larger than L2 (no flush needed)"},
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    return {"value": el / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "steps": steps, "scaling": "weak",
+            "config": {"workload": name, "op": "four-corner operator with fusion weights, all-reduce of the parameter "
+                                               "gradients in the timed region" if world > 1 else
+                                               "four-corner operator with fusion weights",
+                       "shape_BKDNHW": [B, K, D, N, H, W], "io_dtype": str(dtype)[6:], "per_gpu_batch": B},
             "roofline": {"bound": "hbm", "kernel": "fwd_kernel + bwd_kernel", "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                          "algorithmic_bytes": nbytes},
-            "cpu_baseline": None, "e2e": None, "gpu_launches": launches, "clocks": clk.summary(),
-        }))
-    if world > 1:
-        dist.destroy_process_group()
+            "gpu_launches": launches}
 
 
 def main():
@@ -202,12 +213,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default=DEFAULT_CONFIG)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cross", action="store_true", help="skip the four-corner operator sub-record")
     ap.add_argument("--e2e-chunks", type=int, default=0,
                     help="batch chunks of the host-buffer pipeline (0: chosen by the library, about 32 MB each)")
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch (profiling captures only)")
     ap.add_argument("--op", choices=("scan", "cross"), default="scan",
                     help="scan: the drop-in fwd/bwd operator (the headline); cross: the four-corner operator with "
-                         "fusion weights, timed on resident inputs only")
+                         "fusion weights alone, timed on resident inputs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference" or int(os.environ.get("WORLD_SIZE", "1")) == 1:
@@ -221,12 +233,12 @@ def main():
         B = args.batch
     shape = (B, K, D, N, H, W)
     if args.impl == "reference":
-        return run_reference(args, shape, args.config)
+        return run_reference(args, shape, args.config, dtype)
 
     import torch
     import torch.distributed as dist
     import cs2d
-    from cs2d import _lib, ops, parallel
+    from cs2d import parallel
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     # Libraries (NCCL prints its version banner at communicator creation) must not write into
@@ -241,19 +253,6 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
     s = 4 if dtype == torch.float32 else 2
-
-    # ---- inputs: generated on the host, pinned, then made resident -----------------
-    host = make_inputs(B, K, D, N, H, W, dtype=dtype, seed=rank)
-    host = {k: (v.pin_memory() if v is not None else None) for k, v in host.items()}
-    d = {k: (v.to(dev, non_blocking=True) if v is not None else None) for k, v in host.items()}
-    torch.cuda.synchronize()
-    fwd_args = lambda t: (t["u"], t["delta"], t["A"], t["B"], t["C"], t["D"], t["delta_bias"], True, False, None)
-
-    def step(t):
-        out, x, xv, xsd = cs2d.fwd(*fwd_args(t))
-        g = parallel.bwd_data_parallel(t["u"], t["delta"], t["A"], t["B"], t["C"], t["D"], t["delta_bias"], t["dout"],
-                                       x, xv, True, None, xsd)
-        return out, g
 
     def timed(fn, n):
         if world > 1:
@@ -271,60 +270,117 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms)
 
-    if args.op == "cross":
-        return run_cross(args, shape, dtype, host, dev, world, rank, timed, real_stdout)
+    def emit(line):
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        if rank == 0:
+            print(json.dumps(line))
+        if world > 1:
+            dist.destroy_process_group()
 
-    # ---- value: inputs resident in HBM ------------------------------------------------
+    gpu_index = torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local
+    if args.op == "cross":
+        with ClockSampler(gpu_index) as clk:
+            rec = measure_cross(args.config, args.steps, args.warmup, dev, world, rank, timed, args.batch)
+        rec.update({"metric": METRIC, "n_gpus": world, "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None,
+                    "dtype": "f32", "data": "synthetic", "cpu_baseline": None, "e2e": None, "clocks": clk.summary()})
+        return emit(rec)
+
+    # ---- inputs: generated on the host, pinned, then made resident -----------------
+    host = make_inputs(B, K, D, N, H, W, dtype=dtype, seed=rank)
+    host = {k: (v.pin_memory() if v is not None else None) for k, v in host.items()}
+    d = {k: (v.to(dev, non_blocking=True) if v is not None else None) for k, v in host.items()}
+    torch.cuda.synchronize()
+
+    # ---- value: inputs resident in HBM, every rank its own batch of B (weak scaling) ------------
+    # forward, backward, the zero fills, the all-reduce and the dB/dC cast, on preallocated buffers
+    rs = parallel.ResidentStep(d, True)
     for _ in range(args.warmup):
-        step(d)
+        rs.run(d)
     n0 = cs2d.launch_count()
-    with ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local) as clk:
-        ms = timed(lambda: step(d), args.steps)
+    with ClockSampler(gpu_index) as clk:
+        ms = timed(lambda: rs.run(d), args.steps)
     launches = cs2d.launch_count() - n0
+    assert cs2d.device_status() == 0, "a kernel gave up on a bounded wait"
     el_step = elements(B, K, D, N, H, W) * world
     value = el_step / (ms / args.steps * 1e-3)
 
     # ---- roofline of the dominant kernel (backward), timed alone on its stream ---------
-    out, x, xv, xsd = cs2d.fwd(*fwd_args(d))
-    L = _lib.lib()
-    p = ops._problem(d["u"], d["delta"], d["A"], d["B"], d["C"], d["D"], d["delta_bias"], None, True, dtype,
-                     "bench")
-    du, dd = torch.empty_like(d["u"]), torch.empty_like(d["u"])
-    dA = torch.zeros(K * D, N, device=dev)
-    dB, dC = torch.zeros_like(d["B"], dtype=torch.float32), torch.zeros_like(d["C"], dtype=torch.float32)
-    dD, dbias = torch.zeros(K * D, device=dev), torch.zeros(K * D, device=dev)
-    scratch = torch.empty(L.cs2d_bwd_scratch_bytes(ctypes.byref(p)) // 4, device=dev)
-    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    L = cs2d._lib.lib()
+    vp = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = rs.p
 
     def bwd_kernel():
+        p.out_dtype = cs2d.ops._DT[d["dout"].dtype]
         rc = L.cs2d_bwd(ctypes.byref(p), vp(d["dout"]), d["dout"].stride(0), d["dout"].stride(1), d["dout"].stride(2),
-                        vp(xv), vp(scratch), vp(du), vp(dd), vp(dA), vp(dB), vp(dC), vp(dD), vp(dbias), None, stream)
-        assert rc == 0, _lib.last_error()
+                        vp(rs.saved), vp(rs.scratch), vp(rs.du), vp(rs.ddelta), vp(rs._part("dA")), vp(rs.dB32), vp(rs.dC32),
+                        vp(rs._part("dD")), vp(rs._part("ddelta_bias")), None, stream)
+        assert rc == 0, cs2d._lib.last_error()
 
     def fwd_kernel():
-        rc = L.cs2d_fwd(ctypes.byref(p), vp(out), out.stride(0), out.stride(1), out.stride(2), vp(xv), stream)
-        assert rc == 0, _lib.last_error()
+        p.out_dtype = cs2d.ops._DT[rs.out.dtype]
+        rc = L.cs2d_fwd(ctypes.byref(p), vp(rs.out), rs.out.stride(0), rs.out.stride(1), rs.out.stride(2), vp(rs.saved),
+                        stream)
+        assert rc == 0, cs2d._lib.last_error()
 
     for _ in range(3):
-        bwd_kernel(); fwd_kernel()
-    bwd_ms = timed(bwd_kernel, args.steps) / args.steps
+        fwd_kernel(); bwd_kernel()
     fwd_ms = timed(fwd_kernel, args.steps) / args.steps
+    bwd_ms = timed(bwd_kernel, args.steps) / args.steps
     peak, peak_kind = load_peaks()
     bwd_bytes = algorithmic_bytes(B, K, D, N, H, W, s, fwd=False, bwd=True)
     fwd_bytes = algorithmic_bytes(B, K, D, N, H, W, s, fwd=True, bwd=False)
     achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "bwd_kernel", "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
+    roofline = {"bound": "hbm", "kernel": "backward kernel", "achieved": achieved, "peak": peak, "peak_kind": peak_kind,
                 "unit": "GB/s", "frac": achieved / peak, "traffic": load_traffic(args.config),
                 "algorithmic_bytes": bwd_bytes, "launch_ms": bwd_ms,
                 "fwd_kernel": {"launch_ms": fwd_ms, "achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
                                "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak},
                 "fwd_plus_bwd_frac": (fwd_bytes + bwd_bytes) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak}
-    del du, dd, dB, dC, scratch
+
+    # ---- the split the configuration names: its batch sharded over the ranks (strong scaling) ------
+    # every rank generates the same global batch (seed 0) and keeps its shard; before timing, the
+    # all-reduced parameter gradients of the shards are compared with one rank's full-batch result
+    strong = {"value": value, "unit": UNIT, "ms_per_step": ms / args.steps, "per_gpu_batch": B, "global_batch": B,
+              "note": "one GPU: the same run as the headline"}
+    if world > 1 and B >= world:
+        del rs
+        glob = make_inputs(B, K, D, N, H, W, dtype=dtype, seed=0)
+        lo, hi = parallel.shard_bounds(B, rank, world)
+        big = ("u", "delta", "B", "C", "dout")
+        sh = {k: (v[lo:hi].contiguous().to(dev) if k in big else (v.to(dev) if v is not None else None))
+              for k, v in glob.items()}
+        rss = parallel.ResidentStep(sh, True)
+        rss.run(sh)
+        torch.cuda.synchronize()
+        check = None
+        if rank == 0:   # the whole batch on one GPU, no collective
+            full = {k: (v.to(dev) if v is not None else None) for k, v in glob.items()}
+            ref = parallel.ResidentStep(full, True).run(full, allreduce=False).flat.double()
+            got = rss.flat.double()
+            rtol, atol = 1e-4, 1e-5
+            ratio = float(((got - ref).abs() / (atol + rtol * ref.abs())).max())
+            # two fp32 summation orders of ~1e5 terms each: the reduced-sum tolerance is ten times the element one
+            check = {"tensors": "dA | dD | ddelta_bias, all-reduced over the shards vs the full batch on one GPU",
+                     "worst_ratio": ratio, "rtol": rtol, "atol": atol, "allowed_ratio": 10.0, "passed": ratio <= 10.0}
+            assert check["passed"], f"all-reduced parameter gradients differ from the single-GPU result: {check}"
+            del full, ref
+        del glob
+        for _ in range(args.warmup):
+            rss.run(sh)
+        sms = timed(lambda: rss.run(sh), args.steps) / args.steps
+        assert cs2d.device_status() == 0, "a kernel gave up on a bounded wait"
+        strong = {"value": elements(B, K, D, N, H, W) / (sms * 1e-3), "unit": UNIT, "ms_per_step": sms,
+                  "per_gpu_batch": hi - lo, "global_batch": B, "scaling": "strong", "cross_rank_check": check}
+        del rss, sh
+        rs = None
 
     # ---- end to end: host buffers in, host buffers out, copies inside the timed region ----
     # cs2d.fwd_bwd_from_host is the call a user with host-resident tensors makes: it pipelines
     # batch chunks over copy-in / kernel / copy-out streams.
+    del rs
+    torch.cuda.empty_cache()
     big = ("u", "delta", "B", "C", "dout")
     h2d = sum(host[k].numel() * host[k].element_size() for k in big)
     hout = cs2d.alloc_host_outputs(host["u"], host["B"], d["A"], True, True)
@@ -339,8 +395,17 @@ def main():
     torch.cuda.synchronize()
     e2e_steps = max(2, min(args.steps, 5))
     e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    assert cs2d.device_status() == 0, "a kernel gave up on a bounded wait"
     e2e = {"value": el_step / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "ms_per_step": e2e_ms, "chunks": args.e2e_chunks or "auto (about 32 MB of input each)"}
+    del hout, host, d, params
+    cs2d.host._cache.clear()
+    torch.cuda.empty_cache()
+
+    # ---- the four-corner operator on the segmentation-scale configuration (sub-record) -----------
+    cross_rec = None
+    if not args.no_cross and args.config == DEFAULT_CONFIG and args.batch == 0:
+        cross_rec = measure_cross("c5_segmentation", max(2, min(args.steps, 5)), 3, dev, world, rank, timed)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -349,20 +414,14 @@ def main():
         cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
                "sample": f"{sample} of {B} samples of {args.config}, float32, OpenMP, {sec:.1f} s"}
 
-    sys.stdout.flush()
-    os.dup2(real_stdout, 1)
-    if rank == 0:
-        print(json.dumps({
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.config, "shape_BKDNHW": list(shape), "io_dtype": str(dtype)[6:],
-                       "per_gpu_batch": B, "l2": "inputs larger than L2 (no flush needed)",
-                       "sharding": "batch per rank, one all-reduce of the parameter gradients" if world > 1 else "none"},
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clk.summary(),
-        }))
-    if world > 1:
-        dist.destroy_process_group()
+    emit({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(args.config, shape, dtype, world),
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clk.summary(),
+        "strong": strong, "cross": cross_rec,
+    })
 
 
 if __name__ == "__main__":
