@@ -66,3 +66,27 @@ def test_evaluation_path_keeps_no_state_and_matches(shape):
     # the directions add onto the image with fp32 atomics: the order, hence the last bit, may differ
     torch.testing.assert_close(y_train.detach(), y_eval, rtol=1e-5, atol=1e-5)
     assert cs2d.device_status() == 0
+
+
+def test_ss2d_block_training_step_matches_float64_block():
+    """One training step of the SS2D block (forward, loss, gradients of every parameter and of the input)
+    against the same block in float64 with the scan replaced by the oracle's restatement."""
+    import copy
+    from cs2d.nn import SS2D
+    torch.manual_seed(3)
+    m = SS2D(d_model=8, d_state=4, expand=2, directions=4).cuda()
+    ref = copy.deepcopy(m).double().cpu()
+    ref._scan = lambda u, delta, A, B, C, w, D, bias: O.cross_fwd_torch(u, delta, A.double(), B, C, w, D, bias, True)
+    x = torch.randn(2, 6, 10, 8)
+    xg, xr = x.cuda().requires_grad_(True), x.double().requires_grad_(True)
+    tgt = torch.randn(2, 6, 10, 8)
+    (m(xg) - tgt.cuda()).square().mean().backward()
+    (ref(xr) - tgt.double()).square().mean().backward()
+    # fp32 end to end through projections, convolution and LayerNorm: a block-level tolerance
+    check_close("dx", xg.grad.cpu().numpy(), xr.grad.numpy(), 1e-3, 1e-5)
+    got, want = dict(m.named_parameters()), dict(ref.named_parameters())
+    assert set(got) == set(want)
+    for name in got:
+        assert got[name].grad is not None, name
+        check_close("d" + name, got[name].grad.cpu().numpy(), want[name].grad.numpy(), 1e-3, 1e-5)
+    assert cs2d.device_status() == 0
