@@ -43,12 +43,12 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
-def _dir_forward(u, delta, A, B, C, w, D, delta_bias, delta_softplus, keep_state=True):
+def _dir_forward(u, delta, A, B, C, w, D, delta_bias, delta_softplus, keep_state=True, A_decay=None):
     """One launch for all directions, merged in the kernel: returns y (b, d, h, w) fp32 and the saved state
     (``None`` when ``keep_state`` is false: the forward then only holds one rolling row of state)."""
     L = _lib.lib()
     K, dim = B.size(1), A.size(0)
-    p = ops._problem(u, delta, A, B, C, D, delta_bias, None, delta_softplus, torch.float32, "cross_scan_fwd",
+    p = ops._problem(u, delta, A, B, C, D, delta_bias, A_decay, delta_softplus, torch.float32, "cross_scan_fwd",
                      shared_u_dim=dim)
     rows, cols = _masks(K)
     wf = w.detach().float().contiguous()
@@ -66,12 +66,12 @@ def _dir_forward(u, delta, A, B, C, w, D, delta_bias, delta_softplus, keep_state
     return out, (saved if keep_state else None)
 
 
-def _dir_backward(u, delta, A, B, C, w, D, delta_bias, dy, saved, delta_softplus):
+def _dir_backward(u, delta, A, B, C, w, D, delta_bias, dy, saved, delta_softplus, A_decay=None):
     """dy: gradient of the merged image (b, d, h, w), input dtype or fp32, shared by the directions."""
     L = _lib.lib()
     K, dim, n = B.size(1), A.size(0), A.size(1)
     dev = u.device
-    p = ops._problem(u, delta, A, B, C, D, delta_bias, None, delta_softplus, dy.dtype, "cross_scan_bwd",
+    p = ops._problem(u, delta, A, B, C, D, delta_bias, A_decay, delta_softplus, dy.dtype, "cross_scan_bwd",
                      shared_u_dim=dim)
     rows, cols = _masks(K)
     wf = w.detach().float().contiguous()
@@ -79,7 +79,7 @@ def _dir_backward(u, delta, A, B, C, w, D, delta_bias, dy, saved, delta_softplus
         du = torch.zeros(tuple(u.shape), dtype=torch.float32, device=dev)          # sum over the directions
         dw = torch.zeros(dim, dtype=torch.float32, device=dev)
         ddelta = torch.empty(tuple(delta.shape), dtype=u.dtype, device=dev)
-        total, parts = ops.param_grad_layout(dim, n, D is not None, delta_bias is not None, False)
+        total, parts = ops.param_grad_layout(dim, n, D is not None, delta_bias is not None, A_decay is not None)
         flat = torch.zeros(total, dtype=torch.float32, device=dev)
         part = lambda name: flat[parts[name][0]:parts[name][0] + parts[name][1]] if name in parts else None
         dB = torch.zeros(tuple(B.shape), dtype=torch.float32, device=dev)
@@ -88,31 +88,31 @@ def _dir_backward(u, delta, A, B, C, w, D, delta_bias, dy, saved, delta_softplus
         dirs = _lib.Dirs(rows, cols, 3, 0, wf.data_ptr(), dw.data_ptr())  # u and dy shared by the directions
         rc = L.cs2d_bwd_dir(ctypes.byref(p), ctypes.byref(dirs), _ptr(dy), dy.stride(0), dy.stride(1), dy.stride(2),
                             _ptr(saved), _ptr(scratch), _ptr(du), _ptr(ddelta), _ptr(part("dA")), _ptr(dB), _ptr(dC),
-                            _ptr(part("dD")), _ptr(part("ddelta_bias")), None,
+                            _ptr(part("dD")), _ptr(part("ddelta_bias")), _ptr(part("dA_decay")),
                             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     ops._raise_on(rc, "backward")
     return (du.to(u.dtype), ddelta, part("dA").view(dim, n), dB.to(B.dtype), dC.to(C.dtype), dw.view(K, dim // K),
-            part("dD"), part("ddelta_bias"))
+            part("dD"), part("ddelta_bias"), part("dA_decay"))
 
 
 class CrossScan2D(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplus=True):
+    def forward(ctx, u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplus=True, A_decay=None):
         _check_shapes(u, delta, A, B, w)
         ctx.delta_softplus = delta_softplus
-        u, delta, B, C = u.contiguous(), delta.contiguous(), B.contiguous(), C.contiguous()
-        y, saved = _dir_forward(u, delta, A, B, C, w, D, delta_bias, delta_softplus)
-        ctx.save_for_backward(u, delta, A, B, C, D, delta_bias, w, saved)
+        u, delta = u.contiguous(), delta.contiguous()   # B, C may be strided views (innermost stride 1)
+        y, saved = _dir_forward(u, delta, A, B, C, w, D, delta_bias, delta_softplus, A_decay=A_decay)
+        ctx.save_for_backward(u, delta, A, B, C, D, delta_bias, w, saved, A_decay)
         return y.to(u.dtype)
 
     @staticmethod
     def backward(ctx, dy):
-        u, delta, A, B, C, D, delta_bias, w, saved = ctx.saved_tensors
+        u, delta, A, B, C, D, delta_bias, w, saved, A_decay = ctx.saved_tensors
         if dy.stride(-1) != 1:
             dy = dy.contiguous()
-        du, ddelta, dA, dB, dC, dw, dD, dbias = _dir_backward(u, delta, A, B, C, w, D, delta_bias, dy, saved,
-                                                              ctx.delta_softplus)
-        return du, ddelta, dA, dB, dC, dw.to(w.dtype), dD, dbias, None
+        du, ddelta, dA, dB, dC, dw, dD, dbias, ddecay = _dir_backward(u, delta, A, B, C, w, D, delta_bias, dy, saved,
+                                                                      ctx.delta_softplus, A_decay)
+        return du, ddelta, dA, dB, dC, dw.to(w.dtype), dD, dbias, None, ddecay
 
 
 def _check_shapes(u, delta, A, B, w):
@@ -121,13 +121,15 @@ def _check_shapes(u, delta, A, B, w):
         raise RuntimeError("expected delta (b, K*D, h, w), A (K*D, n), w (K, D)")
 
 
-def cross_scan_2d(u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplus=True):
-    """Differentiable four-corner CrossScan; see the module docstring for shapes."""
+def cross_scan_2d(u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplus=True, A_decay=None):
+    """Differentiable four-corner CrossScan; see the module docstring for shapes.  ``A_decay`` (a positive
+    float32 tensor of one element) scales every state transition, as in the plain operator; its gradient
+    follows the reference's formula (the row-scan term is left out there)."""
     needs_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad
-                                                 for t in (u, delta, A, B, C, w, D, delta_bias))
+                                                 for t in (u, delta, A, B, C, w, D, delta_bias, A_decay))
     if not needs_grad:  # evaluation: no saved state
         _check_shapes(u, delta, A, B, w)
-        y, _ = _dir_forward(u.contiguous(), delta.contiguous(), A, B.contiguous(), C.contiguous(), w, D, delta_bias,
-                            delta_softplus, keep_state=False)
+        y, _ = _dir_forward(u.contiguous(), delta.contiguous(), A, B, C, w, D, delta_bias, delta_softplus,
+                            keep_state=False, A_decay=A_decay)
         return y.to(u.dtype)
-    return CrossScan2D.apply(u, delta, A, B, C, w, D, delta_bias, delta_softplus)
+    return CrossScan2D.apply(u, delta, A, B, C, w, D, delta_bias, delta_softplus, A_decay)

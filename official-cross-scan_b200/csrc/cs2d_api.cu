@@ -279,7 +279,6 @@ static void tile_flip(Dev &d, int ncols, int c0, int tw, int nt) {
 }
 
 static int check_dirs(const cs2d_problem *p, const cs2d_dirs *o) {
-    if (o && o->merge_w && p->A_decay) return fail(CS2D_ERR_UNSUPPORTED, "A_decay is not combined with the direction merge");
     if (!o || (!o->flip_rows_mask && !o->flip_cols_mask && !o->shared_input && !o->merge_w)) return CS2D_OK;
     if (p->n_groups > 32) return fail(CS2D_ERR_INVALID, "direction masks cover at most 32 groups");
     return CS2D_OK;

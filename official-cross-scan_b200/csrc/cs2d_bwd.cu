@@ -676,7 +676,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                         duv[i] = dl[i] * S1;
                         ddv[i] = fmaf(uu[i], S1, t2.x + t2.y);
                         dAacc = fma2(bc(dl[i]), G, dAacc);
-                        ddecay_acc = add2(ddecay_acc, Gh);   // only read when dA_decay is wanted; an add is cheaper than a branch
+                        ddecay_acc = fma2(bc(wv), Gh, ddecay_acc);   // only read when dA_decay is wanted (wv: merge weight or 1)
                         const float2 dBv = mul2(bc(dl[i] * uu[i] * wv), eps);
                         const float2 yt = fma2(p[i], bc(0.25f), sub2(hrow[i], s[i]));
                         const float2 dCv = mul2(bc(gg[i] * wv), yt);

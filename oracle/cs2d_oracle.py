@@ -190,7 +190,7 @@ def fwd_torch(u, delta, A, B, C, D=None, delta_bias=None, delta_softplus=False, 
     return y
 
 
-def cross_fwd_torch(u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplus=True):
+def cross_fwd_torch(u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplus=True, A_decay=None):
     """Differentiable float64 restatement of the four-corner CrossScan with fusion weights.
 
     The reference has no code for the merge; the definition is: flip the inputs of
@@ -208,6 +208,7 @@ def cross_fwd_torch(u, delta, A, B, C, w, D=None, delta_bias=None, delta_softplu
     for k in range(K):
         sl = slice(k * d, (k + 1) * d)
         yk = fwd_torch(fl(u, k), fl(delta[:, sl], k), A[sl], fl(B[:, k:k + 1], k), fl(C[:, k:k + 1], k),
-                       None if D is None else D[sl], None if delta_bias is None else delta_bias[sl], delta_softplus)
+                       None if D is None else D[sl], None if delta_bias is None else delta_bias[sl], delta_softplus,
+                       A_decay)
         y = y + w[k][None, :, None, None] * fl(yk, k)
     return y

@@ -90,3 +90,39 @@ def test_ss2d_block_training_step_matches_float64_block():
         assert got[name].grad is not None, name
         check_close("d" + name, got[name].grad.cpu().numpy(), want[name].grad.numpy(), 1e-3, 1e-5)
     assert cs2d.device_status() == 0
+
+
+def test_cross_scan_with_state_decay():
+    """A_decay together with the direction merge: y and every gradient against the float64 restatement;
+    dA_decay against the reference's own formula (which leaves the row-scan term out), evaluated per
+    direction on the flipped inputs with the direction's share w*dy of the gradient."""
+    b, K, d, n, h, w_ = 2, 4, 3, 4, 6, 9
+    inp = make_inputs(b, K, d, n, h, w_, seed=2, a_decay=0.9)
+    gen = torch.Generator().manual_seed(9)
+    u0 = torch.randn(b, d, h, w_, generator=gen)
+    wt = torch.rand(K, d, generator=gen) + 0.1
+    dy = torch.randn(b, d, h, w_, generator=gen)
+    names = ("u", "delta", "A", "B", "C", "w", "D", "delta_bias")
+    host = dict(u=u0, delta=inp["delta"], A=inp["A"], B=inp["B"], C=inp["C"], w=wt, D=inp["D"],
+                delta_bias=inp["delta_bias"])
+    dev = {k: v.cuda().requires_grad_(True) for k, v in host.items()}
+    decay = inp["A_decay"].cuda().requires_grad_(True)
+    y = cs2d.cross_scan_2d(*[dev[k] for k in names], True, decay)
+    y.backward(dy.cuda())
+    ref = {k: v.double().requires_grad_(True) for k, v in host.items()}
+    yo = O.cross_fwd_torch(*[ref[k] for k in names], True, inp["A_decay"].double())
+    yo.backward(dy.double())
+    check_close("y", y.detach().cpu().numpy(), yo.detach().numpy(), 1e-4, 1e-5)
+    for k in names:
+        check_close("d" + k, dev[k].grad.cpu().numpy(), ref[k].grad.numpy(), 1e-4, 1e-5)
+    flips = ((), (-1,), (-2,), (-2, -1))
+    fl = lambda t, k: torch.flip(t, flips[k]) if flips[k] else t
+    want = 0.0
+    for k in range(K):
+        sl = slice(k * d, (k + 1) * d)
+        g = O.bwd(fl(u0, k), fl(inp["delta"][:, sl], k), inp["A"][sl], fl(inp["B"][:, k:k + 1], k),
+                  fl(inp["C"][:, k:k + 1], k), inp["D"][sl], inp["delta_bias"][sl],
+                  fl(dy * wt[k][None, :, None, None], k), True, inp["A_decay"])
+        want = want + g["dA_decay_ref"]
+    check_close("dA_decay", decay.grad.cpu().numpy(), want, 1e-4, 1e-5)
+    assert cs2d.device_status() == 0
