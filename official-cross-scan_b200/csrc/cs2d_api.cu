@@ -147,6 +147,15 @@ static bool vec_ok(const void *ptr, int esize, int ncols, std::initializer_list<
     return true;
 }
 static int esize(int dt) { return dt == CS2D_F32 ? 4 : 2; }
+// the same for aligned 4-byte words: every fp32 element, or pairs of 16-bit elements of even-width rows
+static bool word_ok(const void *ptr, int esize, int ncols, std::initializer_list<int64_t> strides) {
+    const int ew = 4 / esize;   // elements per word
+    if (ncols % ew) return false;
+    if (reinterpret_cast<uintptr_t>(ptr) % 4) return false;
+    for (int64_t s : strides)
+        if (s % ew) return false;
+    return true;
+}
 // the same for 8 elements at a time (the streaming kernels' one-word strips of 16-bit types)
 static bool vec8_ok(const void *ptr, int esize, int ncols, std::initializer_list<int64_t> strides) {
     if (ncols % 8) return false;
@@ -177,7 +186,7 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     d.B_bs = p->B_bs; d.B_gs = p->B_gs; d.B_ns = p->B_ns; d.B_hs = p->B_hs;
     d.C_bs = p->C_bs; d.C_gs = p->C_gs; d.C_ns = p->C_ns; d.C_hs = p->C_hs;
     const int es = esize(p->io_dtype);
-    d.vec = 0; d.vec8 = 0;
+    d.vec = 0; d.vec8 = 0; d.vec2 = 0;
     if (vec_ok(p->u, es, p->ncols, {p->u_bs, p->u_ds, p->u_hs})) d.vec |= VEC_U;
     if (vec_ok(p->delta, es, p->ncols, {p->delta_bs, p->delta_ds, p->delta_hs})) d.vec |= VEC_DELTA;
     if (vec_ok(p->B, es, p->ncols, {p->B_bs, p->B_gs, p->B_ns, p->B_hs})) d.vec |= VEC_B;
@@ -314,9 +323,13 @@ static void stream_fill(Dev &d, const cs2d_problem *p, int *L, int *grid) {
     fill(d, p, g);
     const int es = esize(p->io_dtype);
     if (vec8_ok(p->u, es, p->ncols, {p->u_bs, p->u_ds, p->u_hs})) d.vec8 |= VEC_U;
+    if (word_ok(p->u, es, p->ncols, {p->u_bs, p->u_ds, p->u_hs})) d.vec2 |= VEC_U;
     if (vec8_ok(p->delta, es, p->ncols, {p->delta_bs, p->delta_ds, p->delta_hs})) d.vec8 |= VEC_DELTA;
+    if (word_ok(p->delta, es, p->ncols, {p->delta_bs, p->delta_ds, p->delta_hs})) d.vec2 |= VEC_DELTA;
     if (vec8_ok(p->B, es, p->ncols, {p->B_bs, p->B_gs, p->B_ns, p->B_hs})) d.vec8 |= VEC_B;
+    if (word_ok(p->B, es, p->ncols, {p->B_bs, p->B_gs, p->B_ns, p->B_hs})) d.vec2 |= VEC_B;
     if (vec8_ok(p->C, es, p->ncols, {p->C_bs, p->C_gs, p->C_ns, p->C_hs})) d.vec8 |= VEC_C;
+    if (word_ok(p->C, es, p->ncols, {p->C_bs, p->C_gs, p->C_ns, p->C_hs})) d.vec2 |= VEC_C;
     *L = g.L; *grid = g.grid;
 }
 
@@ -339,6 +352,7 @@ static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_
         d.out = out; d.o_bs = out_bs; d.o_ds = out_ds; d.o_hs = out_hs;
         if (vec_ok(out, esize(p->out_dtype), p->ncols, {out_bs, out_ds, out_hs})) d.vec |= VEC_OUT;
         if (vec8_ok(out, esize(p->out_dtype), p->ncols, {out_bs, out_ds, out_hs})) d.vec8 |= VEC_OUT;
+        if (word_ok(out, esize(p->out_dtype), p->ncols, {out_bs, out_ds, out_hs})) d.vec2 |= VEC_OUT;
         d.saved = reinterpret_cast<float2 *>(saved);
         d.ck_roll = rolling;
         d.status = status;
@@ -470,6 +484,7 @@ static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout,
         d.out = const_cast<void *>(dout); d.o_bs = dout_bs; d.o_ds = dout_ds; d.o_hs = dout_hs;
         if (vec_ok(dout, esize(p->out_dtype), p->ncols, {dout_bs, dout_ds, dout_hs})) d.vec |= VEC_OUT;
         if (vec8_ok(dout, esize(p->out_dtype), p->ncols, {dout_bs, dout_ds, dout_hs})) d.vec8 |= VEC_OUT;
+        if (word_ok(dout, esize(p->out_dtype), p->ncols, {dout_bs, dout_ds, dout_hs})) d.vec2 |= VEC_OUT;
         d.du = du; d.ddelta = ddelta;
         if (vec_ok(du, esize(p->io_dtype), p->ncols, {(int64_t)p->ncols}) &&
             vec_ok(ddelta, esize(p->io_dtype), p->ncols, {(int64_t)p->ncols}))
@@ -477,6 +492,9 @@ static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout,
         if (vec8_ok(du, esize(p->io_dtype), p->ncols, {(int64_t)p->ncols}) &&
             vec8_ok(ddelta, esize(p->io_dtype), p->ncols, {(int64_t)p->ncols}))
             d.vec8 |= VEC_DU;
+        if (word_ok(du, esize(p->io_dtype), p->ncols, {(int64_t)p->ncols}) &&
+            word_ok(ddelta, esize(p->io_dtype), p->ncols, {(int64_t)p->ncols}))
+            d.vec2 |= VEC_DU;
         d.saved = reinterpret_cast<float2 *>(const_cast<void *>(saved));
         d.dA = dA; d.dB = dB; d.dC = dC; d.dD = dD; d.dbias = ddelta_bias;
         d.status = status;

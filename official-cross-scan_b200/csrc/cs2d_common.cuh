@@ -62,6 +62,7 @@ struct Dev {
     int u_shared;
     int vec;    // bit i set: tensor i may be accessed 4 elements at a time
     int vec8;   // bit i set: ... 8 elements at a time (streaming kernels, 16-bit types: one 16-byte word per strip)
+    int vec2;   // bit i set: ... in aligned 4-byte words (streaming kernels: fp32 elements, pairs of 16-bit ones)
     int ws;     // backward: 1 = warp-specialised kernel (8 compute warps + 4 staging warps)
     int bulk;   // 1: row blocks of u, delta (and dout) are fetched with bulk asynchronous copies
                 //    (rows are 16-byte multiples, planes contiguous and aligned); 0: plain loads

@@ -62,6 +62,10 @@ __device__ __forceinline__ void stg8_if(void *p, uint2 v, bool on) {
                  "r"(v.y), "r"((int)on)
                  : "memory");
 }
+__device__ __forceinline__ void stg4_if(void *p, uint32_t v, bool on) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p st.global.b32 [%0], %1;\n\t}" ::"l"(p), "r"(v), "r"((int)on)
+                 : "memory");
+}
 __device__ __forceinline__ void red16_if(float *p, float a, float b, float c, float d, bool on) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t@p red.global.add.v4.f32 [%0], {%1,%2,%3,%4};\n\t}" ::"l"(p),
                  "f"(a), "f"(b), "f"(c), "f"(d), "r"((int)on)
@@ -134,6 +138,9 @@ __device__ __forceinline__ void cp16(uint32_t dst, const void *src, bool on) {
 __device__ __forceinline__ void cp8(uint32_t dst, const void *src, bool on) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(on ? 8 : 0) : "memory");
 }
+__device__ __forceinline__ void cp4(uint32_t dst, const void *src, bool on) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(on ? 4 : 0) : "memory");
+}
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -144,7 +151,7 @@ __host__ __device__ constexpr int slot_words() { return DT == CS2D_F32 ? 2 : 1; 
 template <int DT, int M>
 __device__ __forceinline__ void cp_raw8(uint4 *slot, const char *row, int nv, bool on = true) {
     const uint32_t dst = smem_addr(slot);
-    if constexpr (DT == CS2D_F32 && M >= 1) {
+    if constexpr (DT == CS2D_F32 && (M == 1 || M == 2)) {   // 16-byte words (mode 3 is handled below)
         cp16(dst, row, on && nv >= 4);
         cp16(dst + STHREADS * 16, row + 16, on && nv >= 8);
     } else if constexpr (DT != CS2D_F32 && M == 2) {
@@ -152,6 +159,11 @@ __device__ __forceinline__ void cp_raw8(uint4 *slot, const char *row, int nv, bo
     } else if constexpr (DT != CS2D_F32 && M == 1) {
         cp8(dst, row, on && nv >= 4);
         cp8(dst + 8, row + 8, on && nv >= 8);
+    } else if constexpr (M == 3) {   // 4-byte words: single fp32 elements, pairs of 16-bit ones (even row width)
+        constexpr int EW = DT == CS2D_F32 ? 1 : 2;   // elements per word
+#pragma unroll
+        for (int k = 0; k < 8 / EW; ++k)
+            cp4(dst + (k / 4) * STHREADS * 16 + (k % 4) * 4, row + 4 * k, on && nv >= EW * (k + 1));
     } else {
         Raw8<DT> r;   // element by element: loaded now, parked in the slot
         ld_raw8<DT>(r, row, 0, nv, on);
@@ -191,7 +203,22 @@ __device__ __forceinline__ void cvt8(const Raw8<DT> &r, float (&v)[STRIP]) {
 // 8 results of one strip to a tensor of runtime type dt; modes as ld_raw8
 template <int M>
 __device__ __forceinline__ void st_row8(void *base, int64_t off, int dt, int nv, bool on, const float (&v)[STRIP]) {
-    if constexpr (M == 0) {
+    if constexpr (M == 3) {
+        if (dt == CS2D_F32) {
+            float *p = reinterpret_cast<float *>(base) + off;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) stg4_if(p + k, __float_as_uint(v[k]), on && k < nv);
+        } else {
+            uint16_t *p = reinterpret_cast<uint16_t *>(base) + off;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                uint32_t raw;
+                if (dt == CS2D_BF16) *reinterpret_cast<__nv_bfloat162 *>(&raw) = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+                else *reinterpret_cast<__half2 *>(&raw) = __floats2half2_rn(v[2 * k], v[2 * k + 1]);
+                stg4_if(p + 2 * k, raw, on && nv >= 2 * k + 2);
+            }
+        }
+    } else if constexpr (M == 0) {
 #pragma unroll
         for (int k = 0; k < 8; ++k)
             if (on && k < nv) st_elem(base, off + k, dt, v[k]);
@@ -301,8 +328,11 @@ __device__ __forceinline__ void srow_fwd(int j, const float2 (&a)[STRIP], const 
     }
 }
 
-// access mode of the launch (see ld_raw8): every tensor allows 8-element words -> 2, 4-element words -> 1, else 0
-__device__ __forceinline__ int vmode(const Dev &P, int all) { return (P.vec8 & all) == all ? 2 : (P.vec & all) == all ? 1 : 0; }
+// access mode of the launch (see ld_raw8 / cp_raw8): every tensor allows 8-element words -> 2, 4-element words -> 1,
+// 4-byte words -> 3, else 0 (element by element)
+__device__ __forceinline__ int vmode(const Dev &P, int all) {
+    return (P.vec8 & all) == all ? 2 : (P.vec & all) == all ? 1 : (P.vec2 & all) == all ? 3 : 0;
+}
 
 // Which channels, rows and columns a thread owns; shared by both kernels.
 template <int L>

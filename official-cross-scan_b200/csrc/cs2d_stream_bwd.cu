@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 1 : 2) sbwd_kernel(
     };
     auto issue_next = [&]() {
         if (pb >= 0) {   // one (uniform) branch on the access mode per item, not one per strip
-            if (vm == 2) issue_item(Int<2>()); else if (vm == 1) issue_item(Int<1>()); else issue_item(Int<0>());
+            if (vm == 2) issue_item(Int<2>()); else if (vm == 1) issue_item(Int<1>()); else if (vm == 3) issue_item(Int<3>()); else issue_item(Int<0>());
         }
         cp_commit();   // an empty group once everything has been asked for: the wait below counts groups
         ps = ps + 1 == BW_DEPTH ? 0 : ps + 1;
@@ -386,7 +386,7 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 1 : 2) sbwd_kernel(
                 st_row8<M>(P.du, q1 + (int64_t)r * W, DT, nv, w.on1, du1);
                 st_row8<M>(P.ddelta, q1 + (int64_t)r * W, DT, nv, w.on1, dd1);
             };
-            if (vm == 2) store(Int<2>()); else if (vm == 1) store(Int<1>()); else store(Int<0>());
+            if (vm == 2) store(Int<2>()); else if (vm == 1) store(Int<1>()); else if (vm == 3) store(Int<3>()); else store(Int<0>());
             add_dbc_rows<L>(v, dBp + (int64_t)r * W, dCp + (int64_t)r * W, w.c0, W, vBC, lane);
         }
     }

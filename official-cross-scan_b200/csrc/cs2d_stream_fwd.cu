@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 2 : 4) sfwd_kernel(
         cp_commit();
     };
     auto issue = [&](int r) {   // one (uniform) branch per row instead of one per strip
-        if (vm == 2) issue_m(r, Int<2>()); else if (vm == 1) issue_m(r, Int<1>()); else issue_m(r, Int<0>());
+        if (vm == 2) issue_m(r, Int<2>()); else if (vm == 1) issue_m(r, Int<1>()); else if (vm == 3) issue_m(r, Int<3>()); else issue_m(r, Int<0>());
     };
 #pragma unroll
     for (int k = 0; k < FW_DEPTH - 1; ++k) issue(k);
@@ -97,6 +97,8 @@ __global__ void __launch_bounds__(STHREADS, DT == CS2D_F32 ? 2 : 4) sfwd_kernel(
             st_row8<2>(P.out, o0 + r * so, out_dt, nv, w.on0, y0); st_row8<2>(P.out, o1 + r * so, out_dt, nv, w.on1, y1);
         } else if (vm == 1) {
             st_row8<1>(P.out, o0 + r * so, out_dt, nv, w.on0, y0); st_row8<1>(P.out, o1 + r * so, out_dt, nv, w.on1, y1);
+        } else if (vm == 3) {
+            st_row8<3>(P.out, o0 + r * so, out_dt, nv, w.on0, y0); st_row8<3>(P.out, o1 + r * so, out_dt, nv, w.on1, y1);
         } else {
             st_row8<0>(P.out, o0 + r * so, out_dt, nv, w.on0, y0); st_row8<0>(P.out, o1 + r * so, out_dt, nv, w.on1, y1);
         }
