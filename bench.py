@@ -128,6 +128,22 @@ def config_dict(name, shape, dtype, world):
             "sharding": "batch per rank, one all-reduce of the parameter gradients" if world > 1 else "none"}
 
 
+def reference_cuda_side_record(name):
+    """A labelled side record, outside every timed region: the reference's own CUDA extension (the
+    kernels this library replaces) timed on the same configuration with the state dimension capped
+    at 12, in a subprocess of its own.  Absent build or GPU -> a one-line reason instead."""
+    script = os.path.join(ROOT, "oracle", "ref_cuda_timing.py")
+    if not os.path.exists(os.path.join(ROOT, "oracle", "_ref", "selective_nd_scan_cuda_oflex.so")):
+        return {"unavailable": "the reference extension is not built (make -C oracle ref)"}
+    try:
+        out = subprocess.run([sys.executable, script, name], capture_output=True, text=True, timeout=300)
+        if out.returncode != 0:
+            return {"unavailable": (out.stderr.strip().splitlines() or ["failed"])[-1][:200]}
+        return json.loads(out.stdout.strip().splitlines()[-1])
+    except Exception as e:  # no GPU, time-out, ...
+        return {"unavailable": str(e)[:200]}
+
+
 def run_reference(args, shape, name, dtype):
     """The reference ships no CPU implementation of this operator (its only
     implementation is the CUDA extension), so the reference arm times the CPU
@@ -146,6 +162,7 @@ def run_reference(args, shape, name, dtype):
     val, cores, sec = cpu_port(shape, sample, max(1, args.steps))
     what = f"{sample} of {B} samples of {name} per step, float32, OpenMP"
     print(json.dumps({
+        "reference_cuda_extension": reference_cuda_side_record(name),
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
