@@ -129,16 +129,22 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
  *
  * Direction merge (merge_w != NULL): the weighted sum over the directions happens
  * inside the kernels.  merge_w holds one fp32 weight per channel (dim values:
- * direction-major, w[g][d]).
- *   forward:  `out` is an fp32 image (batch, dim/n_groups, nrows, ncols) that the
- *             caller zero-fills (p->out_dtype = CS2D_F32); the kernel ADDS
- *             sum_g w[g][d] * y_g[d] onto it - no per-direction outputs exist.
+ * direction-major, w[g][d]).  One CTA owns a channel tile for ALL directions and walks them
+ * one after the other, so the merged images have a single writer per element: no atomics,
+ * the same bits on every run.
+ *   forward:  `out` is an fp32 image (batch, dim/n_groups, nrows, ncols)
+ *             (p->out_dtype = CS2D_F32) that receives sum_g w[g][d] * y_g[d] - no
+ *             per-direction outputs exist.  For ncols <= 256 the image is WRITTEN (it need
+ *             not be initialised); wider rows run as column tiles in several launches,
+ *             which ADD onto it: zero-fill it first.
  *   backward: `dout` is the gradient of that image (dim/n_groups channels, set
  *             shared_input bit 1); `du` is an fp32 image (batch, dim/n_groups, nrows,
- *             ncols), zero-filled, onto which sum_g w*du_g is ADDED; ddelta, dA, dB, dC,
- *             dD, ddelta_bias come out scaled by w as the chain rule asks; merge_dw
+ *             ncols) that receives sum_g w*du_g under the same rule (written for
+ *             ncols <= 256, added onto a zero-filled image otherwise); ddelta, dA, dB, dC,
+ *             dD, ddelta_bias, dA_decay come out scaled by w as the chain rule asks; merge_dw
  *             (dim fp32 values, zero-filled, may be NULL) receives dw[g][d] = sum dy*y_g[d].
- * A_decay and the deterministic backward are not combined with the merge.
+ * The deterministic backward is not combined with the merge (dB, dC and the parameter
+ * gradients still sum over channel tiles with atomics).
  */
 typedef struct {
     uint32_t flip_rows_mask, flip_cols_mask;

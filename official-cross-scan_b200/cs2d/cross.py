@@ -19,10 +19,14 @@ All four directions run in ONE kernel launch each way.  The kernels apply the
 flips as index maps while they stage tiles and write results, the K directions
 read the same ``u`` (and, in the backward, the same ``dy``), and the weighted sum
 over the directions happens inside the kernels as well (``cs2d_dirs.merge_w``):
-the forward adds ``w*y_k`` onto one fp32 image, the backward adds ``w*du_k`` onto
-one fp32 image, scales the other gradients by ``w`` and accumulates ``dw``.
+a CTA owns its channel tile for all K directions and walks them one after the
+other, so it alone writes its part of the merged ``y`` (forward) and ``du``
+(backward) images - stored by the first direction, read-modify-written by the
+others in a fixed order: no atomics, no zero fills, bit-identical results from run
+to run; the other gradients are scaled by ``w`` and ``dw`` is accumulated.
 Nothing is flipped, replicated or kept per direction in memory; rows wider than
-256 columns run as column tiles like the plain operator.
+256 columns run as column tiles like the plain operator (the tiles then add onto
+zero-filled images).
 """
 from __future__ import annotations
 
@@ -57,7 +61,8 @@ def _dir_forward(u, delta, A, B, C, w, D, delta_bias, delta_softplus, keep_state
     if nbytes == 0:
         raise RuntimeError(f"cs2d forward: {_lib.last_error()}")
     with torch.cuda.device(u.device):
-        out = torch.zeros(tuple(u.shape), dtype=torch.float32, device=u.device)   # the directions add onto it
+        # rows of at most 256 columns: the kernel writes the merged image; wider rows (column tiles) add onto it
+        out = (torch.zeros if u.size(-1) > 256 else torch.empty)(tuple(u.shape), dtype=torch.float32, device=u.device)
         saved = torch.empty(nbytes // 4, dtype=torch.float32, device=u.device)
         rc = (L.cs2d_fwd_dir if keep_state else L.cs2d_fwd_only)(
             ctypes.byref(p), ctypes.byref(dirs), _ptr(out), out.stride(0), out.stride(1), out.stride(2), _ptr(saved),
@@ -76,7 +81,7 @@ def _dir_backward(u, delta, A, B, C, w, D, delta_bias, dy, saved, delta_softplus
     rows, cols = _masks(K)
     wf = w.detach().float().contiguous()
     with torch.cuda.device(dev):
-        du = torch.zeros(tuple(u.shape), dtype=torch.float32, device=dev)          # sum over the directions
+        du = (torch.zeros if u.size(-1) > 256 else torch.empty)(tuple(u.shape), dtype=torch.float32, device=dev)
         dw = torch.zeros(dim, dtype=torch.float32, device=dev)
         ddelta = torch.empty(tuple(delta.shape), dtype=u.dtype, device=dev)
         total, parts = ops.param_grad_layout(dim, n, D is not None, delta_bias is not None, A_decay is not None)

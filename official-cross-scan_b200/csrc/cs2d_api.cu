@@ -47,7 +47,9 @@ static const size_t kCtaReserve = 1024;
 static const int kSMs = 148;
 
 // Lanes per row, state-pair slots, channels per pass and per CTA, and the grid.
-static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, Geometry *g) {
+// serial: the CTAs walk all groups of their channel tile one after the other (direction merge), so the
+// grid has no group dimension.
+static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, Geometry *g, bool serial = false) {
     const int W = p->ncols, es = p->io_dtype == CS2D_F32 ? 4 : 2, eso = p->out_dtype == CS2D_F32 ? 4 : 2;
     const int strips = (p->ncols + STRIP - 1) / STRIP;
     int L = 1;
@@ -76,7 +78,7 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, 
     const double stage = 1.0 / (32 / L);
     for (int np = 1; np <= (pmax < 8 ? pmax : 8); ++np) {
         const int64_t chunks = (dpg + np * CP - 1) / (np * CP);
-        const int64_t grid = (int64_t)p->batch * p->n_groups * chunks;
+        const int64_t grid = (int64_t)p->batch * (serial ? 1 : p->n_groups) * chunks;
         const int64_t waves = (grid + slots - 1) / slots;
         const double cost = (double)waves * (stage + np);
         if (cost < best - 1e-9) { best = cost; npass = np; }
@@ -114,7 +116,7 @@ static int plan(const cs2d_problem *p, bool backward, bool bulk_ok, bool tiled, 
     }
     g->L = L; g->NPp = NPp; g->CG = CG; g->CP = CP; g->npass = npass; g->CT = npass * CP;
     g->ntiles = (dpg + g->CT - 1) / g->CT;
-    g->grid = p->batch * p->n_groups * g->ntiles;
+    g->grid = p->batch * (serial ? 1 : p->n_groups) * g->ntiles;
     g->nck = (p->nrows + RB - 1) / RB;
     return CS2D_OK;
 }
@@ -197,6 +199,7 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     d.cshift = 0;
     d.ck_roll = 0;
     d.ck_pairs = 0;
+    d.dir_serial = 0; d.merge_store = 0;
     d.status = nullptr;
     d.tile_left = d.tile_right = 0; d.Wout = p->ncols;
     d.flip_h = d.flip_w = 0; d.u_shared = 0;
@@ -235,7 +238,7 @@ static const char *at(const void *p, int64_t elems, int es) {
 }
 
 // Fills `tv` for tile t and returns the bytes of the per-tile buffers; edge buffers follow them.
-static int tile_view(const cs2d_problem *p, int t, bool backward, bool bulk_ok, TileView *tv) {
+static int tile_view(const cs2d_problem *p, int t, bool backward, bool bulk_ok, TileView *tv, bool serial = false) {
     const int es = esize(p->io_dtype);
     const int tc = tile_cols(p->ncols);
     tv->c0 = t * tc;
@@ -245,7 +248,7 @@ static int tile_view(const cs2d_problem *p, int t, bool backward, bool bulk_ok, 
     tv->q.delta = at(p->delta, tv->c0, es);
     tv->q.B = at(p->B, tv->c0, es);
     tv->q.C = at(p->C, tv->c0, es);
-    int rc = plan(&tv->q, backward, bulk_ok, n_tiles(p->ncols) > 1, &tv->g);
+    int rc = plan(&tv->q, backward, bulk_ok, n_tiles(p->ncols) > 1, &tv->g, serial);
     if (rc) return rc;
     const size_t per = (size_t)p->batch * p->dim * tv->g.NPp * (tv->g.L * STRIP) * sizeof(float2);
     tv->saved_bytes = per * tv->g.nck;
@@ -374,9 +377,11 @@ static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_
         TileView tv;
         const bool bulk = nt == 1 && !dirs && bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
                           bulk_ok1(p->delta, es, p->ncols, p->delta_bs, p->delta_ds, p->delta_hs);
-        if ((rc = tile_view(p, t, false, bulk, &tv))) return rc;
+        const bool serial = o && o->merge_w;   // the direction merge: a CTA walks all directions of its channel tile
+        if ((rc = tile_view(p, t, false, bulk, &tv, serial))) return rc;
         Dev d;
         fill(d, &tv.q, tv.g);
+        d.dir_serial = serial; d.merge_store = serial && nt == 1;
         d.out = const_cast<char *>(at(out, tv.c0, eso)); d.o_bs = out_bs; d.o_ds = out_ds; d.o_hs = out_hs;
         if (vec_ok(d.out, eso, tv.q.ncols, {out_bs, out_ds, out_hs})) d.vec |= VEC_OUT;
         d.saved = reinterpret_cast<float2 *>(reinterpret_cast<char *>(saved) + ck_off);
@@ -519,15 +524,18 @@ static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout,
         const bool bulk = nt == 1 && !dirs && bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
                           bulk_ok1(p->delta, es, p->ncols, p->delta_bs, p->delta_ds, p->delta_hs) &&
                           bulk_ok1(dout, eso, p->ncols, dout_bs, dout_ds, dout_hs);
-        if ((rc = tile_view(p, t, true, bulk, &tv))) return rc;
+        const bool serial = o && o->merge_w;   // the direction merge: a CTA walks all directions of its channel tile
+        if ((rc = tile_view(p, t, true, bulk, &tv, serial))) return rc;
         Dev d;
         fill(d, &tv.q, tv.g);
+        d.dir_serial = serial; d.merge_store = serial && nt == 1;
         d.out = const_cast<char *>(at(dout, tv.c0, eso)); d.o_bs = dout_bs; d.o_ds = dout_ds; d.o_hs = dout_hs;
         if (vec_ok(d.out, eso, tv.q.ncols, {dout_bs, dout_ds, dout_hs})) d.vec |= VEC_OUT;
         d.du = const_cast<char *>(at(du, tv.c0, o && o->merge_w ? 4 : es));   // the merged du image is fp32
         d.ddelta = const_cast<char *>(at(ddelta, tv.c0, es));
         if (vec_ok(d.du, es, tv.q.ncols, {(int64_t)p->ncols}) && vec_ok(d.ddelta, es, tv.q.ncols, {(int64_t)p->ncols}))
             d.vec |= VEC_DU;
+        if (serial && vec_ok(d.du, 4, tv.q.ncols, {(int64_t)p->ncols})) d.vec |= VEC_MDU;   // the merged du image is fp32
         d.saved = reinterpret_cast<float2 *>(const_cast<char *>(reinterpret_cast<const char *>(saved)) + ck_offs[t]);
         d.adj = reinterpret_cast<float2 *>(reinterpret_cast<char *>(scratch) + adj_offs[t]);
         d.dA = dA; d.dB = dB + tv.c0; d.dC = dC + tv.c0; d.dD = dD; d.dbias = ddelta_bias; d.ddecay = dA_decay;

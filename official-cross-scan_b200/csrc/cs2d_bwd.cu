@@ -110,9 +110,26 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     const int pp = warp % NPp, cg = warp / NPp;
     const int cp = cg * CW + cl;
     const int tile = blockIdx.x % P.ntiles, bg = blockIdx.x / P.ntiles;
-    const int g_ = bg % P.G, b = bg / P.G;
-    const int dbase = g_ * P.dpg + tile * CT;
-    const int nch = min(CT, (g_ + 1) * P.dpg - dbase);
+    // Normally a CTA serves one group (scan direction).  With Dev::dir_serial (the direction merge) it
+    // owns its channel tile for ALL groups and walks them one after the other, so that the merged du
+    // image is written by this CTA alone: stored by the first direction, read-modify-written by the
+    // others in a fixed order, no atomics; the barriers between the directions order those accesses.
+    const int ng = P.dir_serial ? P.G : 1;
+    const int b = P.dir_serial ? bg : bg / P.G;
+    int g_ = 0, dbase = 0, nch = 0, ush = 0, gsh = 0, gi = 0;
+    bool fh = false, fw = false;
+    int64_t cs = 0;
+    auto set_dir = [&](int i) {
+        gi = i;
+        g_ = P.dir_serial ? i : bg % P.G;
+        dbase = g_ * P.dpg + tile * CT;
+        nch = min(CT, (g_ + 1) * P.dpg - dbase);
+        fh = (P.flip_h >> g_) & 1u; fw = (P.flip_w >> g_) & 1u;   // scan direction of this group
+        ush = (P.u_shared & 1) ? g_ * P.dpg : 0;                    // u indexed by channel - ush
+        gsh = (P.u_shared & 2) ? g_ * P.dpg : 0;                    // dout indexed by channel - gsh
+        cs = fw ? P.cshift : 0;                                     // see Dev::cshift
+    };
+    set_dir(0);
     const int H = P.H, W = P.W, N = P.N;
     const int n0 = 2 * pp, n1 = n0 + 1;
     const bool pair_on = n0 < N;
@@ -120,20 +137,24 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     const float2 lgd = bc(P.decay ? log2f(decay) : 0.f);
     const bool want_decay = P.ddecay != nullptr;
 
-    for (int i = tid; i < nw * CW * CS4; i += nthr) { spdu[i] = 0.f; spdd[i] = 0.f; }
-    if (acc_on)
-        for (int i = tid; i < nw * RB * Wp; i += nthr) { saB[i] = bc(0.f); saC[i] = bc(0.f); }
-    for (int i = tid; i < CT * 2 * NPp + CT * S::NSEG * 2 + nw; i += nthr) sdA[i] = 0.f;
-    // D, delta_bias and merge weight of this CTA's channels; slots past the last valid channel
-    // are read too (their staged values are zero, so the weight has to be finite)
-    for (int i = tid; i < CT; i += nthr) {
-        const bool on = i < nch;
-        spar[2 * i] = on && P.D ? __ldg(P.D + dbase + i) : 0.f;
-        spar[2 * i + 1] = on && P.bias ? __ldg(P.bias + (dbase + i) / P.drep) : 0.f;
-        smw[i] = on && P.mw ? __ldg(P.mw + dbase + i) : 1.f;
-    }
-    for (int i = tid; i < CT * NPp; i += nthr) sdw[i] = 0.f;
     float2 ddecay_acc = bc(0.f);
+    auto init_dir = [&]() {   // accumulators and parameter copies of the current direction
+        for (int i = tid; i < nw * CW * CS4; i += nthr) { spdu[i] = 0.f; spdd[i] = 0.f; }
+        if (acc_on)
+            for (int i = tid; i < nw * RB * Wp; i += nthr) { saB[i] = bc(0.f); saC[i] = bc(0.f); }
+        for (int i = tid; i < CT * 2 * NPp + CT * S::NSEG * 2 + nw; i += nthr) sdA[i] = 0.f;
+        // D, delta_bias and merge weight of this CTA's channels; slots past the last valid channel
+        // are read too (their staged values are zero, so the weight has to be finite)
+        for (int i = tid; i < CT; i += nthr) {
+            const bool on = i < nch;
+            spar[2 * i] = on && P.D ? __ldg(P.D + dbase + i) : 0.f;
+            spar[2 * i + 1] = on && P.bias ? __ldg(P.bias + (dbase + i) / P.drep) : 0.f;
+            smw[i] = on && P.mw ? __ldg(P.mw + dbase + i) : 1.f;
+        }
+        for (int i = tid; i < CT * NPp; i += nthr) sdw[i] = 0.f;
+        ddecay_acc = bc(0.f);
+    };
+    init_dir();
 
     const int nblk = P.nck, npass = P.npass;
     const int steps = nblk * npass;
@@ -153,10 +174,6 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     float *sedl_l = reinterpret_cast<float *>(sadj + (TILED ? CP * NPp * (RB + 1) : 0));   // [CP][RB]
     float *sedl_r = sedl_l + (TILED ? CP * 4 : 0);                                          // [CP][RB+1] (pitch 8)
     const bool has_left = TILED && P.tile_left != 0, has_right = TILED && P.tile_right != 0;
-    const bool fh = (P.flip_h >> g_) & 1u, fw = (P.flip_w >> g_) & 1u;  // scan direction of this group
-    const int ush = (P.u_shared & 1) ? g_ * P.dpg : 0;                    // u indexed by channel - ush
-    const int gsh = (P.u_shared & 2) ? g_ * P.dpg : 0;                    // dout indexed by channel - gsh
-    const int64_t cs = fw ? P.cshift : 0;                                 // see Dev::cshift
     uint64_t *bars = reinterpret_cast<uint64_t *>(sedl_r + (TILED ? CP * 8 : 0));
     unsigned char *raw = reinterpret_cast<unsigned char *>(bars + 2);
     const int stage_bytes = CP * W * (RB * es + RB * eso + (RB + 2) * es);
@@ -260,14 +277,18 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     if constexpr (WS) {
         if (warp >= WS_COMPUTE / 32) {  // ---- staging warps ----
             asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WS_REGS_STAGE));
-            for (int k = 0; k < steps; ++k) {
-                const int set = k & 1;
-                if (k >= 2 && !mbar_wait_bounded_lazy(freeb + set, ((k >> 1) - 1) & 1)) {
-                    atomicOr(P.status, ERR_STAGE_TIMEOUT);  // the compute warps give up on `full` in turn
-                    return;
+            for (int d = 0; d < ng; ++d) {
+                if (d > 0) { set_dir(d); __syncthreads(); }   // the compute warps have refilled the parameter copies
+                for (int k = 0; k < steps; ++k) {
+                    const int gk = d * steps + k, set = gk & 1;   // tile sets and barrier phases run on across directions
+                    if (gk >= 2 && !mbar_wait_bounded_lazy(freeb + set, ((gk >> 1) - 1) & 1)) {
+                        atomicOr(P.status, ERR_STAGE_TIMEOUT);  // the compute warps give up on `full` in turn
+                        return;
+                    }
+                    stage_step(k, set ? set1 : smem, nullptr, tid - WS_COMPUTE, WS_STAGE);
+                    mbar_arrive(full + set);  // release: the tile writes above are visible to the waiters
                 }
-                stage_step(k, set ? set1 : smem, nullptr, tid - WS_COMPUTE, WS_STAGE);
-                mbar_arrive(full + set);  // release: the tile writes above are visible to the waiters
+                if (d + 1 < ng) __syncthreads();   // end of a direction
             }
             return;
         }
@@ -276,7 +297,15 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     auto cta_sync = [&]() {
         if constexpr (WS) group_sync(1, WS_COMPUTE); else __syncthreads();
     };
+    for (int dir = 0; dir < ng; ++dir) {
+    if (dir > 0) {   // next direction of a merged launch: fresh accumulators and parameter copies
+        set_dir(dir);
+        init_dir();
+        __syncthreads();
+    }
+    const int sbase = dir * steps;   // tile sets and barrier phases run on across directions
     for (int step = 0; step <= steps; ++step) {
+        const int gs = sbase + step;
         const int blk = nblk - 1 - step / npass, pass = step % npass;  // bottom-up
         const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
         const int ch0 = pass * CP;
@@ -328,7 +357,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
         }
         {
             // tiles of the previous step (being written out) and of this one
-            float *prev = WS && (pstep & 1) ? set1 : smem, *cur = WS && (step & 1) ? set1 : smem;
+            float *prev = WS && ((gs - 1) & 1) ? set1 : smem, *cur = WS && (gs & 1) ? set1 : smem;
             const float *psu = prev + S::u(CP), *psg = prev + S::g(CP), *pssig = prev + S::sig(CP);
             su = cur + S::u(CP); sg = cur + S::g(CP); ssig = cur + S::sig(CP); sdl = cur + S::dl(CP);
             const int items = pnr > 0 ? CP * RB * T4 : 0;
@@ -359,8 +388,8 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                         const float wv = smw[pch0 + sc];
                         a1.x *= wv; a1.y *= wv; a1.z *= wv; a1.w *= wv;
                         a2.x *= wv; a2.y *= wv; a2.z *= wv; a2.w *= wv;
-                        red4d(reinterpret_cast<float *>(P.du), ((int64_t)b * P.dpg + sd - g_ * P.dpg) * H * P.Wout + cs, P.Wout,
-                              pr0 + rr, c, H, W, fh, fw, a1);
+                        acc4d(reinterpret_cast<float *>(P.du), ((int64_t)b * P.dpg + sd - g_ * P.dpg) * H * P.Wout + cs, P.Wout,
+                              pr0 + rr, c, H, W, fh, fw, P.vec & VEC_MDU, P.merge_store && gi == 0, a1);
                     } else {
                         st4d(P.du, o, P.Wout, pr0 + rr, c, H, W, fh, fw, P.io_dt, P.vec & VEC_DU, a1);
                     }
@@ -384,7 +413,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
             }
             if constexpr (WS) {
                 // the previous step's tile set may be refilled by the staging warps from here on
-                if (step > 0) mbar_arrive(freeb + (pstep & 1));
+                if (step > 0) mbar_arrive(freeb + ((gs - 1) & 1));
             } else {
                 // every thread replaces the tile entries it has just read (same item mapping)
                 stage_step(step, smem, raw + (size_t)(step & 1) * stage_bytes, tid, nthr);
@@ -454,7 +483,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
             }
         }
         if constexpr (WS) {  // this step's tiles have to be complete
-            const bool ok = nr == 0 || mbar_wait_bounded(full + (step & 1), (step >> 1) & 1);
+            const bool ok = nr == 0 || mbar_wait_bounded(full + (gs & 1), (gs >> 1) & 1);
             if (group_or(2, WS_COMPUTE, !ok)) {  // the staging warps stopped (they flagged why): leave together
                 if (tid == 0) atomicOr(P.status, ERR_STAGE_TIMEOUT);
                 return;
@@ -793,6 +822,8 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
         float v = 0.f;
         for (int w = 0; w < nw; ++w) v += sdecay[w];
         if (P.det) P.ddecay[blockIdx.x] = v / decay; else atomicAdd(P.ddecay, v / decay);
+    }
+    if (dir + 1 < ng) __syncthreads();   // end of a direction: its share of the merged du image is written
     }
 }
 

@@ -102,12 +102,17 @@ struct Dev {
     // by w[d] and accumulates dw[d] = sum dy*y_d.
     const float *mw;
     float *dw;
+    // dir_serial: a CTA walks all G groups of its channel tile one after the other (the grid has no
+    // group dimension) and owns the merged images; merge_store: the first direction stores them (the
+    // launch covers the whole row width), otherwise every direction adds onto zero-filled images.
+    int dir_serial, merge_store;
     // Column tiles of a group that walks the columns right-to-left: the launch's scan columns
     // c0..c0+W-1 are image columns Wfull-c0-W..Wfull-c0-1, so every tensor access of such a group
     // adds cshift = Wfull - 2*c0 - W elements to the (c0-shifted) pointers.  0 without tiles.
     int64_t cshift;
 };
-enum { VEC_U = 1, VEC_DELTA = 2, VEC_B = 4, VEC_C = 8, VEC_OUT = 16, VEC_DU = 32 };
+enum { VEC_U = 1, VEC_DELTA = 2, VEC_B = 4, VEC_C = 8, VEC_OUT = 16, VEC_DU = 32,
+       VEC_MDU = 64 };   // VEC_MDU: the merged fp32 du image of a direction merge
 
 // Device-side status word of the library (0 = fine).  A kernel that gives up on a
 // bounded wait records why here instead of spinning; the host reads and clears it
@@ -281,16 +286,32 @@ __device__ __forceinline__ float lds1(const unsigned char *raw, int idx, int dt)
     return __half2float(reinterpret_cast<const __half *>(raw)[idx]);
 }
 
-// out[...] += v for 4 consecutive SCAN columns c..c+3 of scan row r of an fp32 image plane
-// (several CTAs add onto the same image, one per scan direction)
-__device__ __forceinline__ void red4d(float *p, int64_t plane, int64_t hs, int r, int c, int H, int W, bool fh, bool fw,
-                                      float4 v) {
+// w*y (or w*du) of 4 consecutive SCAN columns c..c+3 of scan row r goes onto an fp32 image plane shared by
+// the scan directions.  The CTA owns the image (Dev::dir_serial): plain stores by the first direction
+// (`store`), read-modify-write by the following ones.  The reads bypass L1: the earlier
+// direction's stores were made by other threads of this CTA, behind a CTA barrier.
+__device__ __forceinline__ void acc4d(float *p, int64_t plane, int64_t hs, int r, int c, int H, int W, bool fh, bool fw,
+                                      bool vec, bool store, float4 v) {
     float *row = p + plane + (int64_t)(fh ? H - 1 - r : r) * hs;
     const int nv = W - c;
+    if (nv <= 0) return;
+    if (vec && nv >= 4) {
+        float4 *q = reinterpret_cast<float4 *>(row + (fw ? W - 4 - c : c));
+        float4 t = fw ? make_float4(v.w, v.z, v.y, v.x) : v;
+        if (!store) {
+            const float4 o = __ldcg(q);
+            t.x += o.x; t.y += o.y; t.z += o.z; t.w += o.w;
+        }
+        *q = t;
+        return;
+    }
     const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-        if (k < nv) atomicAdd(row + (fw ? W - 1 - (c + k) : c + k), e[k]);
+        if (k < nv) {
+            float *q = row + (fw ? W - 1 - (c + k) : c + k);
+            *q = store ? e[k] : __ldcg(q) + e[k];
+        }
 }
 
 // Direction-aware access to 4 consecutive SCAN columns c..c+3 of scan row r of an image plane

@@ -83,12 +83,25 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
     const int pp = warp % NPp, cg = warp / NPp;
     const int cp = cg * CW + cl;  // channel slot inside a pass
     const int tile = blockIdx.x % P.ntiles, bg = blockIdx.x / P.ntiles;
-    const int g = bg % P.G, b = bg / P.G;
-    const bool fh = (P.flip_h >> g) & 1u, fw = (P.flip_w >> g) & 1u;  // scan direction of this group
-    const int ush = (P.u_shared & 1) ? g * P.dpg : 0;                        // u is indexed by channel - ush
-    const int64_t cs = fw ? P.cshift : 0;                                    // see Dev::cshift
-    const int dbase = g * P.dpg + tile * P.CT;
-    const int nch = min(P.CT, (g + 1) * P.dpg - dbase);  // valid channels of this CTA
+    // Normally a CTA serves one group (scan direction).  With Dev::dir_serial (the direction merge) it
+    // owns its channel tile for ALL groups and walks them one after the other: the merged image is then
+    // written by this CTA alone - stored by the first direction, read-modify-written by the others in a
+    // fixed order, no atomics - and the barriers between the directions order those accesses.
+    const int ng = P.dir_serial ? P.G : 1;
+    const int b = P.dir_serial ? bg : bg / P.G;
+    int g = 0, ush = 0, dbase = 0, nch = 0, gi = 0;
+    bool fh = false, fw = false;
+    int64_t cs = 0;
+    auto set_dir = [&](int i) {
+        gi = i;
+        g = P.dir_serial ? i : bg % P.G;
+        fh = (P.flip_h >> g) & 1u; fw = (P.flip_w >> g) & 1u;   // scan direction of this group
+        ush = (P.u_shared & 1) ? g * P.dpg : 0;                    // u is indexed by channel - ush
+        cs = fw ? P.cshift : 0;                                    // see Dev::cshift
+        dbase = g * P.dpg + tile * P.CT;
+        nch = min(P.CT, (g + 1) * P.dpg - dbase);                  // valid channels of this CTA
+    };
+    set_dir(0);
     const int H = P.H, W = P.W, N = P.N;
     const int n0 = 2 * pp, n1 = n0 + 1;
     const bool pair_on = n0 < N;  // warp-uniform
@@ -97,11 +110,14 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
 
     // the partial tiles of idle pair slots are summed too: keep them zero
     for (int i = tid; i < nw * CW * CS4; i += nthr) sy[i] = 0.f;
-    for (int i = tid; i < nch; i += nthr) {  // D and delta_bias of this CTA's channels
-        spar[2 * i] = P.D ? __ldg(P.D + dbase + i) : 0.f;
-        spar[2 * i + 1] = P.bias ? __ldg(P.bias + (dbase + i) / P.drep) : 0.f;
-        spar[2 * P.CT + i] = P.mw ? __ldg(P.mw + dbase + i) : 1.f;
-    }
+    auto fill_par = [&]() {  // D, delta_bias and merge weight of this CTA's channels in the current direction
+        for (int i = tid; i < nch; i += nthr) {
+            spar[2 * i] = P.D ? __ldg(P.D + dbase + i) : 0.f;
+            spar[2 * i + 1] = P.bias ? __ldg(P.bias + (dbase + i) / P.drep) : 0.f;
+            spar[2 * P.CT + i] = P.mw ? __ldg(P.mw + dbase + i) : 1.f;
+        }
+    };
+    fill_par();
 
     const int nblk = P.nck;
     const int steps = nblk * P.npass;
@@ -211,14 +227,18 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
     if constexpr (WS) {
         if (warp >= FWS_COMPUTE / 32) {  // ---- staging warps ----
             asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FWS_REGS_STAGE));
-            for (int k = 0; k < steps; ++k) {
-                const int set = k & 1;
-                if (k >= 2 && !mbar_wait_bounded_lazy(freeb + set, ((k >> 1) - 1) & 1)) {
-                    atomicOr(P.status, ERR_STAGE_TIMEOUT);  // the compute warps give up on `full` in turn
-                    return;
+            for (int d = 0; d < ng; ++d) {
+                if (d > 0) { set_dir(d); __syncthreads(); }   // the compute warps have refilled the parameter copies
+                for (int k = 0; k < steps; ++k) {
+                    const int gk = d * steps + k, set = gk & 1;   // tile sets and barrier phases run on across directions
+                    if (gk >= 2 && !mbar_wait_bounded_lazy(freeb + set, ((gk >> 1) - 1) & 1)) {
+                        atomicOr(P.status, ERR_STAGE_TIMEOUT);  // the compute warps give up on `full` in turn
+                        return;
+                    }
+                    stage_step(k, set ? set1 : smem, nullptr, tid - FWS_COMPUTE, FWS_STAGE);
+                    mbar_arrive(full + set);  // release: the tile writes above are visible to the waiters
                 }
-                stage_step(k, set ? set1 : smem, nullptr, tid - FWS_COMPUTE, FWS_STAGE);
-                mbar_arrive(full + set);  // release: the tile writes above are visible to the waiters
+                if (d + 1 < ng) __syncthreads();   // end of a direction
             }
             return;
         }
@@ -227,7 +247,15 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
     auto cta_sync = [&]() {
         if constexpr (WS) group_sync(1, FWS_COMPUTE); else __syncthreads();
     };
+    for (int dir = 0; dir < ng; ++dir) {
+    if (dir > 0) {   // next direction of a merged launch: new parameter copies, then everybody goes on
+        set_dir(dir);
+        fill_par();
+        __syncthreads();
+    }
+    const int sbase = dir * steps;   // tile sets and barrier phases run on across directions
     for (int step = 0; step <= steps; ++step) {
+        const int gs = sbase + step;
         const int blk = step / P.npass, pass = step % P.npass;
         const int r0 = blk * RB, nr = step < steps ? min(RB, H - r0) : 0;
         const int ch0 = pass * CP;
@@ -260,7 +288,7 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
             const int pblk = pstep / P.npass, ppass = pstep % P.npass;
             const int pr0 = pblk * RB, pnr = step > 0 ? min(RB, H - pr0) : 0, pch0 = ppass * CP;
             // tiles of the previous step (its u is needed for D*u) and of this one
-            float *prev = WS && (pstep & 1) ? set1 : smem, *cur = WS && (step & 1) ? set1 : smem;
+            float *prev = WS && ((gs - 1) & 1) ? set1 : smem, *cur = WS && (gs & 1) ? set1 : smem;
             const float *psu = prev + S::u(CP);
             su = cur + S::u(CP); sdl = cur + S::dl(CP);
             const int items = pnr > 0 ? CP * RB * T4 : 0;
@@ -282,11 +310,11 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
                         acc.x = fmaf(Dv, uv.x, acc.x); acc.y = fmaf(Dv, uv.y, acc.y);
                         acc.z = fmaf(Dv, uv.z, acc.z); acc.w = fmaf(Dv, uv.w, acc.w);
                     }
-                    if (P.mw) {  // direction merge: add w*y onto the image shared by the directions
+                    if (P.mw) {  // direction merge: w*y goes onto the image shared by the directions
                         const float wv = spar[2 * P.CT + pch0 + sc];
                         acc.x *= wv; acc.y *= wv; acc.z *= wv; acc.w *= wv;
-                        red4d(reinterpret_cast<float *>(P.out), (int64_t)b * P.o_bs + (int64_t)(sd - g * P.dpg) * P.o_ds + cs,
-                              P.o_hs, pr0 + rr, c, H, W, fh, fw, acc);
+                        acc4d(reinterpret_cast<float *>(P.out), (int64_t)b * P.o_bs + (int64_t)(sd - g * P.dpg) * P.o_ds + cs,
+                              P.o_hs, pr0 + rr, c, H, W, fh, fw, P.vec & VEC_OUT, P.merge_store && gi == 0, acc);
                     } else {
                         st4d(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + cs, P.o_hs, pr0 + rr, c, H, W, fh, fw, P.out_dt,
                              P.vec & VEC_OUT, acc);
@@ -295,7 +323,7 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
             }
             if constexpr (WS) {
                 // the previous step's tile set may be refilled by the staging warps from here on
-                if (step > 0) mbar_arrive(freeb + (pstep & 1));
+                if (step > 0) mbar_arrive(freeb + ((gs - 1) & 1));
             } else {
                 // every thread replaces the tile entries it has just read (same item mapping)
                 stage_step(step, smem, raw + (size_t)(step & 1) * stage_bytes, tid, nthr);
@@ -327,7 +355,7 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
             }
         }
         if constexpr (WS) {  // this step's tiles have to be complete
-            const bool ok = nr == 0 || mbar_wait_bounded(full + (step & 1), (step >> 1) & 1);
+            const bool ok = nr == 0 || mbar_wait_bounded(full + (gs & 1), (gs >> 1) & 1);
             if (group_or(2, FWS_COMPUTE, !ok)) {  // the staging warps stopped (they flagged why): leave together
                 if (tid == 0) atomicOr(P.status, ERR_STAGE_TIMEOUT);
                 return;
@@ -398,6 +426,8 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
             }
         }
         cta_sync();
+    }
+    if (dir + 1 < ng) __syncthreads();   // end of a direction: its part of the merged image is written
     }
 }
 
