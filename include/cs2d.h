@@ -129,27 +129,36 @@ int cs2d_bwd(const cs2d_problem *p, const void *dout, int64_t dout_bs, int64_t d
  *
  * Direction merge (merge_w != NULL): the weighted sum over the directions happens
  * inside the kernels.  merge_w holds one fp32 weight per channel (dim values:
- * direction-major, w[g][d]).  One CTA owns a channel tile for ALL directions and walks them
- * one after the other, so the merged images have a single writer per element: no atomics,
- * the same bits on every run.
+ * direction-major, w[g][d]).
  *   forward:  `out` is an fp32 image (batch, dim/n_groups, nrows, ncols)
  *             (p->out_dtype = CS2D_F32) that receives sum_g w[g][d] * y_g[d] - no
- *             per-direction outputs exist.  For ncols <= 256 the image is WRITTEN (it need
- *             not be initialised); wider rows run as column tiles in several launches,
- *             which ADD onto it: zero-fill it first.
+ *             per-direction outputs exist.
  *   backward: `dout` is the gradient of that image (dim/n_groups channels, set
  *             shared_input bit 1); `du` is an fp32 image (batch, dim/n_groups, nrows,
- *             ncols) that receives sum_g w*du_g under the same rule (written for
- *             ncols <= 256, added onto a zero-filled image otherwise); ddelta, dA, dB, dC,
- *             dD, ddelta_bias, dA_decay come out scaled by w as the chain rule asks; merge_dw
- *             (dim fp32 values, zero-filled, may be NULL) receives dw[g][d] = sum dy*y_g[d].
- * The deterministic backward is not combined with the merge (dB, dC and the parameter
- * gradients still sum over channel tiles with atomics).
+ *             ncols) that receives sum_g w*du_g; ddelta, dA, dB, dC, dD, ddelta_bias,
+ *             dA_decay come out scaled by w as the chain rule asks; merge_dw (dim fp32
+ *             values, zero-filled, may be NULL) receives dw[g][d] = sum dy*y_g[d].
+ * Two forms, chosen by `flags`:
+ *   0                 the directions run as separate CTAs and ADD onto the merged images with
+ *                     fp32 atomics: zero-fill `out` / `du` first; the last bit of the sums
+ *                     depends on the order in which the CTAs arrive.
+ *   CS2D_DIRS_SERIAL  one CTA owns a channel tile for ALL directions and walks them one
+ *                     after the other, so every element of the merged images has a single
+ *                     writer: no atomics, the same bits on every run.  For ncols <= 256 the
+ *                     images are WRITTEN (they need not be initialised); wider rows run as
+ *                     column tiles in several launches, which add onto them: zero-fill them
+ *                     first.  Slower (measured +17 % to +24 % on the stage-1 and
+ *                     segmentation-scale maps, far more when batch x channel tiles leave
+ *                     most SMs idle): a quarter of the CTAs, and the read-modify-write of
+ *                     the merged image sits in the write-out path.
+ * The deterministic backward (cs2d_bwd_det) is not combined with the merge (dB, dC and the
+ * parameter gradients still sum over channel tiles with atomics).
  */
+#define CS2D_DIRS_SERIAL 1
 typedef struct {
     uint32_t flip_rows_mask, flip_cols_mask;
     int32_t shared_input;
-    int32_t reserved;        /* zero */
+    int32_t flags;           /* 0 or CS2D_DIRS_SERIAL (merge only) */
     const float *merge_w;    /* NULL: no merge */
     float *merge_dw;
 } cs2d_dirs;

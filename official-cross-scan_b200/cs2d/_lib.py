@@ -9,6 +9,7 @@ LIB_PATH = os.path.join(_HERE, "libcs2d.so")
 
 F32, F16, BF16 = 0, 1, 2
 NOALLOC_SCRATCH_BYTES = 32 << 20  # CS2D_NOALLOC_SCRATCH_BYTES
+DIRS_SERIAL = 1                   # CS2D_DIRS_SERIAL
 
 
 _i32, _i64, _p = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p
@@ -17,7 +18,7 @@ _i32, _i64, _p = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p
 class Dirs(ctypes.Structure):
     """Mirror of ``cs2d_dirs``."""
     _fields_ = [("flip_rows_mask", ctypes.c_uint32), ("flip_cols_mask", ctypes.c_uint32),
-                ("shared_input", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("shared_input", ctypes.c_int32), ("flags", ctypes.c_int32),
                 ("merge_w", ctypes.c_void_p), ("merge_dw", ctypes.c_void_p)]
 
 

@@ -11,6 +11,8 @@
 namespace cs2d {
 cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st);
 cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st);
+cudaError_t launch_fwd_serial(const Dev &P, int L, int grid, cudaStream_t st);   // one CTA walks all groups of its tile
+cudaError_t launch_bwd_serial(const Dev &P, int L, int grid, cudaStream_t st);
 cudaError_t launch_stream_fwd(const Dev &P, int L, int grid, cudaStream_t st);
 cudaError_t launch_stream_bwd(const Dev &P, int L, int grid, cudaStream_t st);
 int stream_pairs_per_cta(int L);
@@ -377,7 +379,7 @@ static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_
         TileView tv;
         const bool bulk = nt == 1 && !dirs && bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
                           bulk_ok1(p->delta, es, p->ncols, p->delta_bs, p->delta_ds, p->delta_hs);
-        const bool serial = o && o->merge_w;   // the direction merge: a CTA walks all directions of its channel tile
+        const bool serial = o && o->merge_w && (o->flags & CS2D_DIRS_SERIAL);   // a CTA walks all directions of its channel tile
         if ((rc = tile_view(p, t, false, bulk, &tv, serial))) return rc;
         Dev d;
         fill(d, &tv.q, tv.g);
@@ -397,7 +399,7 @@ static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_
             d.flip_h = o->flip_rows_mask; d.flip_w = o->flip_cols_mask; d.u_shared = o->shared_input; d.mw = o->merge_w;
             tile_flip(d, p->ncols, tv.c0, tv.q.ncols, nt);
         }
-        cudaError_t e = launch_fwd(d, tv.g.L, tv.g.grid, reinterpret_cast<cudaStream_t>(stream));
+        cudaError_t e = (serial ? launch_fwd_serial : launch_fwd)(d, tv.g.L, tv.g.grid, reinterpret_cast<cudaStream_t>(stream));
         if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
         g_launches.fetch_add(1);
     }
@@ -524,7 +526,7 @@ static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout,
         const bool bulk = nt == 1 && !dirs && bulk_ok1(p->u, es, p->ncols, p->u_bs, p->u_ds, p->u_hs) &&
                           bulk_ok1(p->delta, es, p->ncols, p->delta_bs, p->delta_ds, p->delta_hs) &&
                           bulk_ok1(dout, eso, p->ncols, dout_bs, dout_ds, dout_hs);
-        const bool serial = o && o->merge_w;   // the direction merge: a CTA walks all directions of its channel tile
+        const bool serial = o && o->merge_w && (o->flags & CS2D_DIRS_SERIAL);   // a CTA walks all directions of its channel tile
         if ((rc = tile_view(p, t, true, bulk, &tv, serial))) return rc;
         Dev d;
         fill(d, &tv.q, tv.g);
@@ -562,7 +564,7 @@ static int bwd_impl(const cs2d_problem *p, const cs2d_dirs *o, const void *dout,
             d.dD = dD ? det + dl.dD : nullptr; d.dbias = ddelta_bias ? det + dl.dbias : nullptr;
             d.ddecay = dA_decay ? det + dl.ddecay : nullptr;
         }
-        cudaError_t e = launch_bwd(d, tv.g.L, tv.g.grid, reinterpret_cast<cudaStream_t>(stream));
+        cudaError_t e = (serial ? launch_bwd_serial : launch_bwd)(d, tv.g.L, tv.g.grid, reinterpret_cast<cudaStream_t>(stream));
         if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
         g_launches.fetch_add(1);
     }

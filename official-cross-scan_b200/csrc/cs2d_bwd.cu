@@ -25,7 +25,16 @@
 // memory once per block and CTA.
 #include "cs2d_common.cuh"
 
+// This file is compiled twice: as it is (every group of a launch is served by CTAs of its own), and
+// from cs2d_bwd_serial.cu with CS2D_SERIAL_DIRS = 1 (the reproducible direction merge: one CTA walks all
+// groups of its channel tile).  The choice is a compile-time constant so that the common form carries
+// no trace of the loop over directions.
+#ifndef CS2D_SERIAL_DIRS
+#define CS2D_SERIAL_DIRS 0
+#endif
+
 namespace cs2d {
+constexpr bool SERIAL = CS2D_SERIAL_DIRS != 0;
 
 static_assert(RB == STREAM_RB, "the tile backward reads the streaming forward's checkpoints at its own row-block cadence");
 
@@ -81,7 +90,8 @@ __device__ __forceinline__ void add_dbc(const Dev &P, int tile, int64_t og, bool
 // meet on mbarriers (tile set full / tile set free), every wait bounded.  The staging warps
 // give most of their registers to the compute warps (setmaxnreg).
 constexpr int WS_COMPUTE = 256, WS_STAGE = 128, WS_REGS_COMPUTE = 232, WS_REGS_STAGE = 40;
-template <int L, int NPC, bool TILED, bool WS>
+// SER = SERIAL: part of the kernel's name, so that the two compilations of this file define distinct kernels
+template <int L, int NPC, bool TILED, bool WS, bool SER>
 __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) bwd_kernel(const Dev P) {
     static_assert(!WS || NPC == 8, "the warp-specialised form covers the common geometry only");
     using S = BwdSmem<L>;
@@ -110,18 +120,18 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     const int pp = warp % NPp, cg = warp / NPp;
     const int cp = cg * CW + cl;
     const int tile = blockIdx.x % P.ntiles, bg = blockIdx.x / P.ntiles;
-    // Normally a CTA serves one group (scan direction).  With Dev::dir_serial (the direction merge) it
-    // owns its channel tile for ALL groups and walks them one after the other, so that the merged du
+    // Normally a CTA serves one group (scan direction).  With Dev::dir_serial (the reproducible direction
+    // merge) it owns its channel tile for ALL groups and walks them one after the other, so that the merged du
     // image is written by this CTA alone: stored by the first direction, read-modify-written by the
     // others in a fixed order, no atomics; the barriers between the directions order those accesses.
-    const int ng = P.dir_serial ? P.G : 1;
-    const int b = P.dir_serial ? bg : bg / P.G;
+    const int ng = SERIAL ? P.G : 1;
+    const int b = SERIAL ? bg : bg / P.G;
     int g_ = 0, dbase = 0, nch = 0, ush = 0, gsh = 0, gi = 0;
     bool fh = false, fw = false;
     int64_t cs = 0;
     auto set_dir = [&](int i) {
         gi = i;
-        g_ = P.dir_serial ? i : bg % P.G;
+        g_ = SERIAL ? i : bg % P.G;
         dbase = g_ * P.dpg + tile * CT;
         nch = min(CT, (g_ + 1) * P.dpg - dbase);
         fh = (P.flip_h >> g_) & 1u; fw = (P.flip_w >> g_) & 1u;   // scan direction of this group
@@ -388,8 +398,12 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
                         const float wv = smw[pch0 + sc];
                         a1.x *= wv; a1.y *= wv; a1.z *= wv; a1.w *= wv;
                         a2.x *= wv; a2.y *= wv; a2.z *= wv; a2.w *= wv;
-                        acc4d(reinterpret_cast<float *>(P.du), ((int64_t)b * P.dpg + sd - g_ * P.dpg) * H * P.Wout + cs, P.Wout,
-                              pr0 + rr, c, H, W, fh, fw, P.vec & VEC_MDU, P.merge_store && gi == 0, a1);
+                        const int64_t plane = ((int64_t)b * P.dpg + sd - g_ * P.dpg) * H * P.Wout + cs;
+                        if (SERIAL)
+                            acc4d(reinterpret_cast<float *>(P.du), plane, P.Wout, pr0 + rr, c, H, W, fh, fw, P.vec & VEC_MDU,
+                                  P.merge_store && gi == 0, a1);
+                        else
+                            red4d(reinterpret_cast<float *>(P.du), plane, P.Wout, pr0 + rr, c, H, W, fh, fw, a1);
                     } else {
                         st4d(P.du, o, P.Wout, pr0 + rr, c, H, W, fh, fw, P.io_dt, P.vec & VEC_DU, a1);
                     }
@@ -827,6 +841,7 @@ __global__ void __launch_bounds__(WS ? WS_COMPUTE + WS_STAGE : MAX_THREADS, 1) b
     }
 }
 
+#if !CS2D_SERIAL_DIRS
 template <int L>
 static size_t smem_floats(int CP, int NPp, int CT, int nw, bool acc, bool ws) {
     return (size_t)((BwdSmem<L>::total(CP, NPp, CT, nw, acc) + 3) & ~3) + (ws ? BwdSmem<L>::set_floats(CP) : 0);
@@ -849,17 +864,21 @@ size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, i
     }
 }
 
+#else
+size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk, bool tiled, bool ws);
+#endif
+
 template <int L, int NPC, bool TILED, bool WS>
 static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) {
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(bwd_kernel<L, NPC, TILED, WS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(bwd_kernel<L, NPC, TILED, WS, SERIAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    bwd_kernel<L, NPC, TILED, WS><<<grid, WS ? WS_COMPUTE + WS_STAGE : 32 * P.CG * P.NPp, smem, st>>>(P);
+    bwd_kernel<L, NPC, TILED, WS, SERIAL><<<grid, WS ? WS_COMPUTE + WS_STAGE : 32 * P.CG * P.NPp, smem, st>>>(P);
     return cudaGetLastError();
 }
 
@@ -871,7 +890,11 @@ static cudaError_t launch_L(const Dev &P, int grid, size_t smem, cudaStream_t st
                  : (spec ? launch<L, 8, false, false>(P, grid, smem, st) : launch<L, 0, false, false>(P, grid, smem, st));
 }
 
+#if CS2D_SERIAL_DIRS
+cudaError_t launch_bwd_serial(const Dev &P, int L, int grid, cudaStream_t st) {
+#else
 cudaError_t launch_bwd(const Dev &P, int L, int grid, cudaStream_t st) {
+#endif
     const bool tiled = P.tile_left || P.tile_right;
     if (P.ws && (P.NPp != 8 || P.CG != 1)) return cudaErrorInvalidValue;
     const size_t smem = bwd_smem_bytes(L, P.CG, P.NPp, P.CT, P.acc_dbc != 0, P.W, P.io_dt == CS2D_F32 ? 4 : 2,

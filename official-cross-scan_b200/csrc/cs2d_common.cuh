@@ -102,9 +102,11 @@ struct Dev {
     // by w[d] and accumulates dw[d] = sum dy*y_d.
     const float *mw;
     float *dw;
-    // dir_serial: a CTA walks all G groups of its channel tile one after the other (the grid has no
-    // group dimension) and owns the merged images; merge_store: the first direction stores them (the
-    // launch covers the whole row width), otherwise every direction adds onto zero-filled images.
+    // dir_serial (the reproducible form of the direction merge): a CTA walks all G groups of its channel
+    // tile one after the other (the grid has no group dimension) and owns the merged images; merge_store:
+    // the first direction stores them (the launch covers the whole row width), otherwise every direction
+    // adds onto zero-filled images.  Without dir_serial the directions are separate CTAs that add onto the
+    // zero-filled images with atomics (faster: four times the CTAs, no read-modify-write latency).
     int dir_serial, merge_store;
     // Column tiles of a group that walks the columns right-to-left: the launch's scan columns
     // c0..c0+W-1 are image columns Wfull-c0-W..Wfull-c0-1, so every tensor access of such a group
@@ -287,8 +289,19 @@ __device__ __forceinline__ float lds1(const unsigned char *raw, int idx, int dt)
 }
 
 // w*y (or w*du) of 4 consecutive SCAN columns c..c+3 of scan row r goes onto an fp32 image plane shared by
-// the scan directions.  The CTA owns the image (Dev::dir_serial): plain stores by the first direction
-// (`store`), read-modify-write by the following ones.  The reads bypass L1: the earlier
+// the scan directions.  red4d: the directions run as separate CTAs and add with atomics (the image starts
+// zero-filled).
+__device__ __forceinline__ void red4d(float *p, int64_t plane, int64_t hs, int r, int c, int H, int W, bool fh, bool fw,
+                                      float4 v) {
+    float *row = p + plane + (int64_t)(fh ? H - 1 - r : r) * hs;
+    const int nv = W - c;
+    const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        if (k < nv) atomicAdd(row + (fw ? W - 1 - (c + k) : c + k), e[k]);
+}
+// acc4d: one CTA owns the image and walks the directions itself (Dev::dir_serial): plain stores by the
+// first direction (`store`), read-modify-write by the following ones.  The reads bypass L1: the earlier
 // direction's stores were made by other threads of this CTA, behind a CTA barrier.
 __device__ __forceinline__ void acc4d(float *p, int64_t plane, int64_t hs, int r, int c, int H, int W, bool fh, bool fw,
                                       bool vec, bool store, float4 v) {

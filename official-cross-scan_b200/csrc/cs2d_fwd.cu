@@ -13,7 +13,16 @@
 // itself reloads when it comes back to the channel for the next row block.
 #include "cs2d_common.cuh"
 
+// This file is compiled twice: as it is (every group of a launch is served by CTAs of its own), and
+// from cs2d_fwd_serial.cu with CS2D_SERIAL_DIRS = 1 (the reproducible direction merge: one CTA walks all
+// groups of its channel tile).  The choice is a compile-time constant so that the common form carries
+// no trace of the loop over directions.
+#ifndef CS2D_SERIAL_DIRS
+#define CS2D_SERIAL_DIRS 0
+#endif
+
 namespace cs2d {
+constexpr bool SERIAL = CS2D_SERIAL_DIRS != 0;
 
 template <int L>
 struct FwdSmem {
@@ -60,7 +69,8 @@ struct FwdSmem {
 // bounded, and the staging warps give registers to the compute warps (setmaxnreg).  Two such
 // CTAs share an SM: 2 * (256 * 104 + 128 * 32) registers.
 constexpr int FWS_COMPUTE = 256, FWS_STAGE = 128, FWS_REGS_COMPUTE = 104, FWS_REGS_STAGE = 32;
-template <int L, int NPC, bool TILED, bool WS>
+// SER = SERIAL: part of the kernel's name, so that the two compilations of this file define distinct kernels
+template <int L, int NPC, bool TILED, bool WS, bool SER>
 __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2) fwd_kernel(const Dev P) {
     static_assert(!WS || NPC == 8, "the warp-specialised form covers the common geometry only");
     using S = FwdSmem<L>;
@@ -83,18 +93,18 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
     const int pp = warp % NPp, cg = warp / NPp;
     const int cp = cg * CW + cl;  // channel slot inside a pass
     const int tile = blockIdx.x % P.ntiles, bg = blockIdx.x / P.ntiles;
-    // Normally a CTA serves one group (scan direction).  With Dev::dir_serial (the direction merge) it
-    // owns its channel tile for ALL groups and walks them one after the other: the merged image is then
-    // written by this CTA alone - stored by the first direction, read-modify-written by the others in a
-    // fixed order, no atomics - and the barriers between the directions order those accesses.
-    const int ng = P.dir_serial ? P.G : 1;
-    const int b = P.dir_serial ? bg : bg / P.G;
+    // Normally a CTA serves one group (scan direction).  With Dev::dir_serial (the reproducible direction
+    // merge) it owns its channel tile for ALL groups and walks them one after the other: the merged image
+    // is then written by this CTA alone - stored by the first direction, read-modify-written by the others
+    // in a fixed order, no atomics - and the barriers between the directions order those accesses.
+    const int ng = SERIAL ? P.G : 1;
+    const int b = SERIAL ? bg : bg / P.G;
     int g = 0, ush = 0, dbase = 0, nch = 0, gi = 0;
     bool fh = false, fw = false;
     int64_t cs = 0;
     auto set_dir = [&](int i) {
         gi = i;
-        g = P.dir_serial ? i : bg % P.G;
+        g = SERIAL ? i : bg % P.G;
         fh = (P.flip_h >> g) & 1u; fw = (P.flip_w >> g) & 1u;   // scan direction of this group
         ush = (P.u_shared & 1) ? g * P.dpg : 0;                    // u is indexed by channel - ush
         cs = fw ? P.cshift : 0;                                    // see Dev::cshift
@@ -313,8 +323,12 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
                     if (P.mw) {  // direction merge: w*y goes onto the image shared by the directions
                         const float wv = spar[2 * P.CT + pch0 + sc];
                         acc.x *= wv; acc.y *= wv; acc.z *= wv; acc.w *= wv;
-                        acc4d(reinterpret_cast<float *>(P.out), (int64_t)b * P.o_bs + (int64_t)(sd - g * P.dpg) * P.o_ds + cs,
-                              P.o_hs, pr0 + rr, c, H, W, fh, fw, P.vec & VEC_OUT, P.merge_store && gi == 0, acc);
+                        const int64_t plane = (int64_t)b * P.o_bs + (int64_t)(sd - g * P.dpg) * P.o_ds + cs;
+                        if (SERIAL)
+                            acc4d(reinterpret_cast<float *>(P.out), plane, P.o_hs, pr0 + rr, c, H, W, fh, fw, P.vec & VEC_OUT,
+                                  P.merge_store && gi == 0, acc);
+                        else
+                            red4d(reinterpret_cast<float *>(P.out), plane, P.o_hs, pr0 + rr, c, H, W, fh, fw, acc);
                     } else {
                         st4d(P.out, (int64_t)b * P.o_bs + (int64_t)sd * P.o_ds + cs, P.o_hs, pr0 + rr, c, H, W, fh, fw, P.out_dt,
                              P.vec & VEC_OUT, acc);
@@ -431,6 +445,7 @@ __global__ void __launch_bounds__(WS ? FWS_COMPUTE + FWS_STAGE : MAX_THREADS, 2)
     }
 }
 
+#if !CS2D_SERIAL_DIRS
 template <int L>
 static size_t smem_floats(int CP, int NPp, int nw, bool ws) {
     return (size_t)FwdSmem<L>::total(CP, NPp, nw) + (ws ? FwdSmem<L>::set_floats(CP) : 0);
@@ -453,17 +468,21 @@ size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk, int CT, 
     }
 }
 
+#else
+size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk, int CT, bool tiled, bool ws);
+#endif
+
 template <int L, int NPC, bool TILED, bool WS>
 static cudaError_t launch(const Dev &P, int grid, size_t smem, cudaStream_t st) {
     static bool attr_done[64] = {};  // per template instance and device
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(fwd_kernel<L, NPC, TILED, WS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(fwd_kernel<L, NPC, TILED, WS, SERIAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    fwd_kernel<L, NPC, TILED, WS><<<grid, WS ? FWS_COMPUTE + FWS_STAGE : 32 * P.CG * P.NPp, smem, st>>>(P);
+    fwd_kernel<L, NPC, TILED, WS, SERIAL><<<grid, WS ? FWS_COMPUTE + FWS_STAGE : 32 * P.CG * P.NPp, smem, st>>>(P);
     return cudaGetLastError();
 }
 
@@ -475,7 +494,11 @@ static cudaError_t launch_L(const Dev &P, int grid, size_t smem, cudaStream_t st
                  : (spec ? launch<L, 8, false, false>(P, grid, smem, st) : launch<L, 0, false, false>(P, grid, smem, st));
 }
 
+#if CS2D_SERIAL_DIRS
+cudaError_t launch_fwd_serial(const Dev &P, int L, int grid, cudaStream_t st) {
+#else
 cudaError_t launch_fwd(const Dev &P, int L, int grid, cudaStream_t st) {
+#endif
     const bool tiled = P.tile_left || P.tile_right;
     if (P.ws && (P.NPp != 8 || P.CG != 1)) return cudaErrorInvalidValue;
     const size_t smem = fwd_smem_bytes(L, P.CG, P.NPp, P.W, P.io_dt == CS2D_F32 ? 4 : 2, P.bulk != 0, P.CT, tiled, P.ws != 0);
