@@ -37,6 +37,7 @@ def ratios(g, go):
 def main():
     sys.path.insert(0, os.path.join(ROOT, "oracle", "_ref"))
     import selective_nd_scan_cuda_oflex as ref
+    assert ref.__file__.endswith(".so"), "expected the compiled reference extension in oracle/_ref"
     import cs2d
     shape = (32, 1, 192, 12, 56, 56)
     inp = make_inputs(*shape, dtype=torch.float32, seed=0)
