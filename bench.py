@@ -51,29 +51,66 @@ def load_traffic(workload):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons while a region runs: NVML read calls from a thread every
+    20 ms (a timed region of a fraction of a second still gets samples, on every rank), and
+    nvidia-smi in a loop when the NVML binding is missing.  Reads only; nothing is set."""
     Q = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, uuid=None):
+        self.index, self.uuid, self.rows, self.proc, self.stop = index, uuid, [], None, threading.Event()
+        self.source = None
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        if self.uuid:
+            try:
+                return pynvml, pynvml.nvmlDeviceGetHandleByUUID(f"GPU-{self.uuid}")
+            except Exception:
+                pass
+        return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
 
     def __enter__(self):
         try:
+            self.nv, self.h = self._nvml_handle()
+            self.mx = self.nv.nvmlDeviceGetMaxClockInfo(self.h, self.nv.NVML_CLOCK_SM)
+            self.source = "nvml"
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            self.source = None
+        try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.source = "nvidia-smi"
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
             self.proc = None
         return self
 
+    def _poll(self):
+        while not self.stop.is_set():
+            try:
+                mhz = self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM)
+                bits = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.rows.append([self.index, mhz, self.mx] + ["Active" if bits & b else "Not Active" for _, b in self.BITS])
+            except Exception:
+                pass
+            self.stop.wait(0.02)
+
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([x.strip() for x in line.split(",")])
 
     def __exit__(self, *a):
-        if self.proc is not None:
+        if self.source == "nvml":
+            self.stop.set()
+            self.thread.join(timeout=2)
+        elif self.proc is not None:
             time.sleep(0.15)
             self.proc.terminate()
             self.thread.join(timeout=2)
@@ -86,11 +123,11 @@ class ClockSampler:
             except Exception:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
-                if v.lower().startswith("active"):
+                if str(v).lower().startswith("active"):
                     reasons.add(name)
         mhz.sort()
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
-                "samples": len(mhz)}
+                "samples": len(mhz), "source": self.source}
 
 
 def cpu_port(shape, sample_batch, steps=1):
@@ -296,8 +333,9 @@ def main():
             dist.destroy_process_group()
 
     gpu_index = torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local
+    gpu_uuid = str(torch.cuda.get_device_properties(local).uuid)
     if args.op == "cross":
-        with ClockSampler(gpu_index) as clk:
+        with ClockSampler(gpu_index, gpu_uuid) as clk:
             rec = measure_cross(args.config, args.steps, args.warmup, dev, world, rank, timed, args.batch)
         rec.update({"metric": METRIC, "n_gpus": world, "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None,
                     "dtype": "f32", "data": "synthetic", "cpu_baseline": None, "e2e": None, "clocks": clk.summary()})
@@ -315,7 +353,7 @@ def main():
     for _ in range(args.warmup):
         rs.run(d)
     n0 = cs2d.launch_count()
-    with ClockSampler(gpu_index) as clk:
+    with ClockSampler(gpu_index, gpu_uuid) as clk:
         ms = timed(lambda: rs.run(d), args.steps)
     launches = cs2d.launch_count() - n0
     assert cs2d.device_status() == 0, "a kernel gave up on a bounded wait"
