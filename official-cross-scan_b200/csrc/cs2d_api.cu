@@ -16,6 +16,10 @@ cudaError_t launch_bwd_serial(const Dev &P, int L, int grid, cudaStream_t st);
 cudaError_t launch_stream_fwd(const Dev &P, int L, int grid, cudaStream_t st);
 cudaError_t launch_stream_bwd(const Dev &P, int L, int grid, cudaStream_t st);
 int stream_pairs_per_cta(int L);
+cudaError_t launch_walk_fwd(const Dev &P, int grid, cudaStream_t st);
+void walk_geometry(int ncols, int *swd, int *lr);
+int walk_channels_per_cta(int lr);
+size_t walk_bc_bytes(int batch, int groups, int nrows, int ncols);
 size_t fwd_smem_bytes(int L, int CG, int NPp, int W, int es, bool bulk, int CT, bool tiled, bool ws);
 size_t bwd_smem_bytes(int L, int CG, int NPp, int CT, bool acc, int W, int es, int eso, bool bulk, bool tiled, bool ws);
 static __device__ int g_cs2d_status = 0;  // see ERR_* in cs2d_common.cuh
@@ -201,6 +205,8 @@ static void fill(Dev &d, const cs2d_problem *p, const Geometry &g) {
     d.cshift = 0;
     d.ck_roll = 0;
     d.ck_pairs = 0;
+    d.ck_wp = g.L * STRIP;
+    d.wbt = nullptr; d.wct = nullptr;
     d.dir_serial = 0; d.merge_store = 0;
     d.status = nullptr;
     d.tile_left = d.tile_right = 0; d.Wout = p->ncols;
@@ -258,6 +264,8 @@ static int tile_view(const cs2d_problem *p, int t, bool backward, bool bulk_ok, 
     return CS2D_OK;
 }
 
+static bool walk_shape(const cs2d_problem *p) { return p->dstate > 8 && p->ncols <= 8 * STRIP; }
+
 static size_t edge_bytes(const cs2d_problem *p, int NPp) {
     return (size_t)p->batch * p->dim * NPp * p->nrows * sizeof(float4);
 }
@@ -275,7 +283,11 @@ static size_t layout_bytes(const cs2d_problem *p, bool backward, bool rolling = 
         total += backward || rolling ? tv.adj_bytes : tv.saved_bytes;
         NPp = tv.g.NPp;
     }
-    return total + (size_t)(nt - 1) * edge_bytes(p, NPp);
+    total += (size_t)(nt - 1) * edge_bytes(p, NPp);
+    // the row-walk forward keeps B and C, regrouped, behind the checkpoints (whatever the scan directions
+    // turn out to be: the size depends on the problem alone)
+    if (!backward && walk_shape(p)) total += walk_bc_bytes(p->batch, p->n_groups, p->nrows, p->ncols);
+    return total;
 }
 
 size_t cs2d_saved_bytes(const cs2d_problem *p) { return layout_bytes(p, false); }
@@ -338,6 +350,12 @@ static void stream_fill(Dev &d, const cs2d_problem *p, int *L, int *grid) {
     *L = g.L; *grid = g.grid;
 }
 
+// ---- row-walk forward (cs2d_walk_fwd.cu) ---------------------------------------------------------
+// Rows of at most 64 columns with more than 8 states per channel and one scan orientation: the lanes
+// of a row work one image row apart, so the recurrence needs no scan.  It writes y and the checkpoints
+// exactly where the tile forward would, so the choice is invisible to the backward.
+static bool walk_fwd_ok(const cs2d_problem *p, const cs2d_dirs *o) { return walk_shape(p) && !has_dirs(o); }
+
 static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_t out_bs, int64_t out_ds,
                     int64_t out_hs, void *saved, void *stream, bool rolling = false) {
     int rc = validate(p);
@@ -364,6 +382,27 @@ static int fwd_impl(const cs2d_problem *p, const cs2d_dirs *o, void *out, int64_
         cudaError_t e = launch_stream_fwd(d, L, grid, reinterpret_cast<cudaStream_t>(stream));
         if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
         g_launches.fetch_add(1);
+        return CS2D_OK;
+    }
+    if (walk_fwd_ok(p, o)) {
+        TileView tv;
+        if ((rc = tile_view(p, 0, false, false, &tv))) return rc;   // the checkpoint layout is the tile kernels'
+        Dev d;
+        fill(d, &tv.q, tv.g);
+        int swd, lr;
+        walk_geometry(p->ncols, &swd, &lr);
+        const int ct = walk_channels_per_cta(lr), dpg = p->dim / p->n_groups;
+        d.ntiles = (dpg + ct - 1) / ct;
+        d.out = out; d.o_bs = out_bs; d.o_ds = out_ds; d.o_hs = out_hs;
+        d.saved = reinterpret_cast<float2 *>(saved);
+        d.ck_roll = rolling;
+        d.status = status;
+        char *bc = reinterpret_cast<char *>(saved) + (rolling ? tv.adj_bytes : tv.saved_bytes);
+        d.wbt = reinterpret_cast<float4 *>(bc);
+        d.wct = reinterpret_cast<float4 *>(bc + walk_bc_bytes(p->batch, p->n_groups, p->nrows, p->ncols) / 2);
+        cudaError_t e = launch_walk_fwd(d, p->batch * p->n_groups * d.ntiles, reinterpret_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return fail(CS2D_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
+        g_launches.fetch_add(2);   // the regrouping of B and C, then the scan
         return CS2D_OK;
     }
     const int es = esize(p->io_dtype), eso = esize(p->out_dtype), nt = n_tiles(p->ncols);

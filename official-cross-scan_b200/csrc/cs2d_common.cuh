@@ -76,6 +76,8 @@ struct Dev {
     int ck_roll;                           // forward without backward: one rolling row [batch][dim][1][NPp][L*8]
     int ck_pairs;                          // checkpoints were written by the streaming forward (dstate 1):
                                            // [batch][G][ceil(dpg/2)][nck][L*8] float2 = two CHANNELS per value
+    int ck_wp;                             // L*8: columns of a checkpoint row (the row-walk forward writes the same layout)
+    float4 *wbt, *wct;                     // row-walk kernels: B and C regrouped as [batch][G][H][4][W] entries of four states
     // Column tiling of rows wider than 256 columns: this launch covers one tile (all
     // tensor pointers are already moved to the tile's first column).  The values that
     // cross a tile boundary travel through global edge buffers [batch][dim][NPp][H] float4

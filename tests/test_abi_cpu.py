@@ -43,8 +43,11 @@ def _problem(**over):
 def test_sizes_without_gpu():
     L = _lib.lib()
     p = _problem()
-    # 14 row blocks x 8 pair slots x 64 padded columns x 8 bytes per (batch, channel)
-    assert L.cs2d_saved_bytes(ctypes.byref(p)) == 2 * 8 * 14 * 8 * 64 * 8
+    # 14 row blocks x 8 pair slots x 64 padded columns x 8 bytes per (batch, channel); rows of at most 64
+    # columns with more than 8 states also keep B and C regrouped in fp32 entries of four states
+    # (batch x groups x rows x 4 entries x columns x 16 bytes, twice) for the row-walk forward
+    bc = 2 * (2 * 4 * 56 * 4 * 56 * 16)
+    assert L.cs2d_saved_bytes(ctypes.byref(p)) == 2 * 8 * 14 * 8 * 64 * 8 + bc
     assert L.cs2d_bwd_scratch_bytes(ctypes.byref(p)) == 2 * 8 * 8 * 64 * 8
     p1 = _problem(dstate=1, nrows=7, ncols=7)
     assert L.cs2d_saved_bytes(ctypes.byref(p1)) == 2 * 8 * 2 * 1 * 8 * 8
@@ -60,7 +63,7 @@ def test_sizes_without_gpu():
     assert det > 0 and (det // 4 - slots) % (2 * nB) in range(0, 2 * 8 * 4 + 1)
     assert L.cs2d_bwd_det_scratch_bytes(ctypes.byref(pw)) == 0   # wider than one column tile
     # a forward that no backward follows keeps one rolling row instead of 14 checkpoints
-    assert L.cs2d_fwd_only_scratch_bytes(ctypes.byref(p)) == 2 * 8 * 8 * 64 * 8
+    assert L.cs2d_fwd_only_scratch_bytes(ctypes.byref(p)) == 2 * 8 * 8 * 64 * 8 + bc
     assert L.cs2d_fwd_only_scratch_bytes(ctypes.byref(pw)) == per * (5 * 64 + 16) + 5 * edge
 
 
