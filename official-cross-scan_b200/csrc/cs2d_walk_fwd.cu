@@ -62,11 +62,46 @@ __device__ __forceinline__ float wk_softplus(float x) {
     const float l = t < 0.03f ? t * fmaf(t, fmaf(t, 0.33333334f, -0.5f), 1.f) : y * 0.6931471805599453f;
     return fmaxf(l, x);
 }
+// One element, loaded only when `on` (else 0), as raw bits: the guard is a predicate on the load, so that
+// nothing depends on the loaded register until the value is used iterations later (a select on the
+// result would wait for the memory access on the spot).
 template <int DT>
-__device__ __forceinline__ float wk_ld(const void *p, int64_t i) {
-    if constexpr (DT == CS2D_F32) return __ldg(reinterpret_cast<const float *>(p) + i);
-    else if constexpr (DT == CS2D_BF16) return __uint_as_float((uint32_t)__ldg(reinterpret_cast<const uint16_t *>(p) + i) << 16);
-    else return __half2float(__ushort_as_half(__ldg(reinterpret_cast<const uint16_t *>(p) + i)));
+__device__ __forceinline__ uint32_t wk_ld_raw(const void *p, int64_t i, bool on) {
+    if constexpr (DT == CS2D_F32) {
+        uint32_t v;
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\tmov.b32 %0, 0;\n\t@p ld.global.nc.b32 %0, [%1];\n\t}"
+                     : "=r"(v) : "l"(reinterpret_cast<const float *>(p) + i), "r"((int)on));
+        return v;
+    } else {
+        unsigned short v;
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\tmov.b16 %0, 0;\n\t@p ld.global.nc.b16 %0, [%1];\n\t}"
+                     : "=h"(v) : "l"(reinterpret_cast<const uint16_t *>(p) + i), "r"((int)on));
+        return v;
+    }
+}
+// predicated stores: a guard that differs between the lanes of a warp costs a predicate, not a branch
+__device__ __forceinline__ void wk_st8_if(float2 *p, float2 v, bool on) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %3, 0;\n\t@p st.global.v2.f32 [%0], {%1,%2};\n\t}" ::"l"(p), "f"(v.x), "f"(v.y),
+                 "r"((int)on)
+                 : "memory");
+}
+__device__ __forceinline__ void wk_st4_if(void *p, uint32_t v, bool on) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p st.global.b32 [%0], %1;\n\t}" ::"l"(p), "r"(v), "r"((int)on) : "memory");
+}
+__device__ __forceinline__ void wk_st2_if(void *p, unsigned short v, bool on) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p st.global.b16 [%0], %1;\n\t}" ::"l"(p), "h"(v), "r"((int)on) : "memory");
+}
+// one result element of runtime type dt (the branch on dt is uniform)
+__device__ __forceinline__ void wk_st_elem_if(void *base, int64_t i, int dt, float v, bool on) {
+    if (dt == CS2D_F32) wk_st4_if(reinterpret_cast<float *>(base) + i, __float_as_uint(v), on);
+    else if (dt == CS2D_BF16) wk_st2_if(reinterpret_cast<uint16_t *>(base) + i, __bfloat16_as_ushort(__float2bfloat16(v)), on);
+    else wk_st2_if(reinterpret_cast<uint16_t *>(base) + i, __half_as_ushort(__float2half(v)), on);
+}
+template <int DT>
+__device__ __forceinline__ float wk_cvt(uint32_t raw) {
+    if constexpr (DT == CS2D_F32) return __uint_as_float(raw);
+    else if constexpr (DT == CS2D_BF16) return __uint_as_float(raw << 16);
+    else return __half2float(__ushort_as_half((unsigned short)raw));
 }
 __host__ __device__ constexpr int wk_pitch(int swd) { return swd | 1; }   // strip pitch in 16-byte entries: odd
 
@@ -213,29 +248,30 @@ __global__ void __launch_bounds__(WK_THREADS, 1) wfwd_kernel(const Dev P) {
     }
     const bool softplus = P.softplus != 0;
     // raw values travel for two iterations: two register sets, used in turn
-    float rx[2][NE], ru[2][NE];
-    auto stage_load = [&](int t2, float (&vx)[NE], float (&vu)[NE]) {   // raw delta and u of iteration t2 (calls come in order of t2)
+    uint32_t rx[2][NE], ru[2][NE];
+    auto stage_load = [&](int t2, uint32_t (&vx)[NE], uint32_t (&vu)[NE]) {   // raw delta and u of iteration t2 (calls come in order of t2)
 #pragma unroll
         for (int m = 0; m < NE; ++m) {
             const int R = t2 - e_jj[m];
             const bool on = e_on[m] && R >= 0 && R < H;
-            vx[m] = on ? wk_ld<DT>(P.delta, ox[m]) : 0.f;
-            vu[m] = on ? wk_ld<DT>(P.u, ou[m]) : 0.f;
+            vx[m] = wk_ld_raw<DT>(P.delta, ox[m], on);
+            vu[m] = wk_ld_raw<DT>(P.u, ou[m], on);
             ox[m] += dl_hs; ou[m] += u_hs;
         }
     };
-    auto stage_store = [&](int t2, const float (&vx)[NE], const float (&vu)[NE]) {  // ... transformed, into the warp's slot of iteration t2
+    auto stage_store = [&](int t2, const uint32_t (&vx)[NE], const uint32_t (&vu)[NE]) {  // ... transformed, into the warp's slot of iteration t2
 #pragma unroll
         for (int m = 0; m < NE; ++m) {
             const int e = lane + 32 * m, R = t2 - e_jj[m];
             const bool on = e_on[m] && R >= 0 && R < H;
-            float dl = vx[m] + e_bias[m];
+            const float uv = wk_cvt<DT>(vu[m]);
+            float dl = wk_cvt<DT>(vx[m]) + e_bias[m];
             // fp32 I/O: the same evaluation as the backward's recompute (h - s cancels, the two must agree to the last bit)
             if (softplus) dl = DT == CS2D_F32 ? softplus20(dl) : wk_softplus(dl);
             dl = on ? dl : 0.f;   // columns and rows outside the image: a = 1, p = 0
             if (e < EW) {
-                sDU[(t2 & 1) * EW + e] = make_float4(dl, dl, dl * vu[m], dl * vu[m]);
-                sDu[(t2 & 1) * EW + e] = e_D[m] * vu[m];
+                sDU[(t2 & 1) * EW + e] = make_float4(dl, dl, dl * uv, dl * uv);
+                sDu[(t2 & 1) * EW + e] = e_D[m] * uv;
             }
         }
     };
@@ -261,7 +297,9 @@ __global__ void __launch_bounds__(WK_THREADS, 1) wfwd_kernel(const Dev P) {
     for (int x = 0; x < CNT; ++x) y_on[x] = ch_ok && ybase + x < SWD && j * SWD + ybase + x < W;
     const int64_t o_hs = P.o_hs;
     int64_t yo = (int64_t)b * P.o_bs + (int64_t)d * P.o_ds + j * SWD + ybase - (int64_t)j * o_hs;   // row t - j of iteration t = 0
-    const int du_off = chw * TW + j * SP + ybase;
+    int du_idx[CNT];   // D*u of those columns; a column the lane does not store reads (and drops) the strip's last entry
+#pragma unroll
+    for (int x = 0; x < CNT; ++x) du_idx[x] = chw * TW + j * SP + min(ybase + x, SWD - 1);
     // checkpoint rows of the thread's two pairs (block 0), and the column past the strips this lane zeroes
     const int Wp = P.ck_wp, ck_step = P.NPp * Wp;
     float2 *ckrow[2];
@@ -343,22 +381,22 @@ __global__ void __launch_bounds__(WK_THREADS, 1) wfwd_kernel(const Dev P) {
                 yv[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2 * LR);
             }
         }
-        if (act) {
 #pragma unroll
-            for (int x = 0; x < CNT; ++x)
-                if (y_on[x]) st_elem(P.out, yo + x, out_dt, yv[x] + sDu[(t & 1) * EW + du_off + x]);
-            // the last row of a block of RB rows is the checkpoint of that block (none after the last block)
-            if (keep_ck && (R & (RB - 1)) == RB - 1 && R + 1 < H) {
-                const int64_t off = (int64_t)(R >> 2) * ck_step;
+        for (int x = 0; x < CNT; ++x)
+            wk_st_elem_if(P.out, yo + x, out_dt, yv[x] + sDu[(t & 1) * EW + du_idx[x]], act && y_on[x]);
+        // the last row of a block of RB rows is the checkpoint of that block (none after the last block).  The
+        // lanes of a row are at different image rows, so in every iteration some of them are at such a row.
+        {
+            const bool ck_on = act && keep_ck && (R & (RB - 1)) == RB - 1 && R + 1 < H;
+            const int64_t off = (int64_t)(R >> 2) * ck_step;
 #pragma unroll
-                for (int k = 0; k < 2; ++k)
-                    if (pair_on[k]) {
+            for (int k = 0; k < 2; ++k) {
+                float2 *row = ckrow[k] + off;
+                const bool on = ck_on && pair_on[k];
 #pragma unroll
-                        for (int i = 0; i < SWD; ++i)
-                            if (j * SWD + i < Wp) ckrow[k][off + j * SWD + i] = h_up[k][i];
-                        // columns no strip covers: finite values for the backward's padded strips
-                        if (zc < Wp) ckrow[k][off + zc] = bc(0.f);
-                    }
+                for (int i = 0; i < SWD; ++i) wk_st8_if(row + j * SWD + i, h_up[k][i], on);   // LR*SWD <= Wp
+                // columns no strip covers: finite values for the backward's padded strips
+                wk_st8_if(row + zc, bc(0.f), on && zc < Wp);
             }
         }
         yo += o_hs;
