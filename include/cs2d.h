@@ -65,7 +65,9 @@ typedef struct {
 
 /*
  * Bytes of the saved-state buffer the forward writes and the backward reads
- * (row checkpoints of the state h).  It takes the place of the reference's
+ * (row checkpoints of the state h; for rows of at most 64 columns with more
+ * than 8 states also the forward's regrouped fp32 copy of B and C, behind the
+ * checkpoints).  It takes the place of the reference's
  * three side tensors x, x_v, x_sd (selective_scan_oflex.cpp:251-258); unlike
  * them it is NOT modified by the backward, so backward may run twice on it.
  * Returns 0 for an invalid problem.
