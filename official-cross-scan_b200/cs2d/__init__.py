@@ -5,5 +5,6 @@ Drop-in for the ``fwd`` / ``bwd`` operators of the reference CUDA extension
 """
 from .ops import SelectiveScan2D, bwd, fwd, fwd_only, selective_scan_2d  # noqa: F401
 from .cross import CrossScan2D, cross_scan_2d  # noqa: F401
-from .host import HostPipeline, alloc_host_outputs, fwd_bwd_from_host  # noqa: F401
+from .host import (CrossHostPipeline, HostPipeline, alloc_cross_host_outputs, alloc_host_outputs,  # noqa: F401
+                   fwd_bwd_from_host)
 from ._lib import LIB_PATH, build, device_status, launch_count  # noqa: F401

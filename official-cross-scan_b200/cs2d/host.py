@@ -183,3 +183,136 @@ def fwd_bwd_from_host(host, params, out_host, delta_softplus=True, out_float=Fal
         pipe = HostPipeline(host, params, delta_softplus, out_float, chunk, device=device)
         _cache["pipe"] = pipe
     return pipe.run(host, out_host, allreduce)
+
+
+# ---- the four-corner operator on host-resident data ---------------------------------------------------
+# Through the drop-in operator a caller with K = 4 corner directions moves u, out, dout and du with K*D
+# channels although the four groups of u are flips of one image.  The four-corner operator takes the
+# image once: (2 + K)*D + 2*K*N values per pixel in, (2 + K)*D + 2*K*N out, instead of 3*K*D + 2*K*N
+# each way (53 % of the bytes at K4 D192 N16).
+_XBIG = ("u", "delta", "B", "C", "dy")
+
+
+def alloc_cross_host_outputs(u, delta, B, A, has_D, has_bias):
+    """Pinned host buffers for every output of one four-corner forward + backward step."""
+    dim, n = A.shape
+    total, _ = ops.param_grad_layout(dim, n, has_D, has_bias, False)
+    pin = lambda shape, dt: torch.empty(shape, dtype=dt, pin_memory=True)
+    return {"y": pin(tuple(u.shape), u.dtype), "du": pin(tuple(u.shape), u.dtype), "ddelta": pin(tuple(delta.shape), u.dtype),
+            "dB": pin(tuple(B.shape), B.dtype), "dC": pin(tuple(B.shape), B.dtype),
+            "param_grads": pin((total,), torch.float32), "dw": pin((B.size(1), dim // B.size(1)), torch.float32)}
+
+
+class CrossHostPipeline:
+    """``HostPipeline`` for ``cross_scan_2d``: u (b, D, h, w) and dy (b, D, h, w) cross the bus once for all K
+    directions; delta (b, K*D, h, w), B and C (b, K, n, h, w) as in the plain operator.  The merged images y and
+    du are formed on the device in fp32 (the directions' CTAs add onto them) and leave in the input type."""
+
+    def __init__(self, host, params, delta_softplus=True, chunk=None, depth=3, device=None):
+        from . import cross
+        self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.A, self.D, self.bias, self.w = params["A"], params.get("D"), params.get("delta_bias"), params["w"]
+        self.softplus = delta_softplus
+        u, delta, B = host["u"], host["delta"], host["B"]
+        cross._check_shapes(u, delta, self.A, B, self.w)
+        self.batch, self.K = u.size(0), B.size(1)
+        per_sample = sum(host[k][0].numel() * host[k].element_size() for k in _XBIG)
+        auto = -(-self.batch // min(64, max(1, round(self.batch * per_sample / 32e6))))   # about 32 MB of input per chunk
+        self.chunk = max(1, min(chunk or auto, self.batch))
+        dim, n = self.A.shape
+        self.total, self.parts = ops.param_grad_layout(dim, n, self.D is not None, self.bias is not None, False)
+        self.rows, self.cols = cross._masks(self.K)
+        c, dev = self.chunk, self.dev
+        with torch.cuda.device(dev):
+            self.flat = torch.zeros(self.total, dtype=torch.float32, device=dev)
+            self.dw = torch.zeros(dim, dtype=torch.float32, device=dev)
+            self.wf = self.w.detach().float().contiguous().view(-1)
+            self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+            mk = lambda ref, dt=None: torch.empty((c,) + tuple(ref.shape[1:]), dtype=dt or ref.dtype, device=dev)
+            self.slots = []
+            for _ in range(max(2, depth)):
+                s = {k: mk(host[k]) for k in _XBIG}
+                s.update(y32=mk(u, torch.float32), du32=mk(u, torch.float32), y=mk(u), du=mk(u), ddelta=mk(delta, u.dtype),
+                         dB32=mk(B, torch.float32), dC32=mk(B, torch.float32))
+                if B.dtype != torch.float32:
+                    s.update(dB=mk(B), dC=mk(B))
+                s["free"], s["loaded"], s["done"] = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+                self.slots.append(s)
+            s0 = self.slots[0]
+            p = ops._problem(s0["u"], s0["delta"], self.A, s0["B"], s0["C"], self.D, self.bias, None, delta_softplus,
+                             torch.float32, "host pipeline", shared_u_dim=dim)
+            L = _lib.lib()
+            nsaved, nscr = L.cs2d_saved_bytes(ctypes.byref(p)), L.cs2d_bwd_scratch_bytes(ctypes.byref(p))
+            if nsaved == 0 or nscr == 0:
+                raise RuntimeError(f"cs2d host pipeline: {_lib.last_error()}")
+            for s in self.slots:
+                s["saved"] = torch.empty(nsaved // 4, dtype=torch.float32, device=dev)
+                s["scratch"] = torch.empty(nscr // 4, dtype=torch.float32, device=dev)
+
+    def _part(self, name):
+        if name not in self.parts:
+            return None
+        off, n = self.parts[name]
+        return self.flat[off:off + n]
+
+    def run(self, host, out_host, allreduce=False):
+        """One forward + backward step; returns ``out_host`` with every copy queued behind the current stream."""
+        L = _lib.lib()
+        vp = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+        dim = self.A.size(0)
+        with torch.cuda.device(self.dev):
+            main = torch.cuda.current_stream()
+            stream = ctypes.c_void_p(main.cuda_stream)
+            self.flat.zero_()
+            self.dw.zero_()
+            self.s_in.wait_stream(main)
+            nslots = len(self.slots)
+            bounds = [(lo, min(lo + self.chunk, self.batch)) for lo in range(0, self.batch, self.chunk)]
+            for i, (lo, hi) in enumerate(bounds):
+                s, n = self.slots[i % nslots], hi - lo
+                with torch.cuda.stream(self.s_in):
+                    if i >= nslots:
+                        self.s_in.wait_event(s["free"])     # the slot's previous results have left the device
+                    for k in _XBIG:
+                        s[k][:n].copy_(host[k][lo:hi], non_blocking=True)
+                    s["loaded"].record(self.s_in)
+                main.wait_event(s["loaded"])
+                if i >= nslots:
+                    main.wait_event(s["free"])
+                t = {k: s[k][:n] for k in _XBIG + ("y32", "du32", "y", "du", "ddelta", "dB32", "dC32")}
+                for k in ("y32", "du32", "dB32", "dC32"):   # the directions add onto these
+                    t[k].zero_()
+                p = ops._problem(t["u"], t["delta"], self.A, t["B"], t["C"], self.D, self.bias, None, self.softplus,
+                                 torch.float32, "host pipeline", shared_u_dim=dim)
+                dirs = _lib.Dirs(self.rows, self.cols, 1, 0, self.wf.data_ptr(), None)
+                rc = L.cs2d_fwd_dir(ctypes.byref(p), ctypes.byref(dirs), vp(t["y32"]), t["y32"].stride(0), t["y32"].stride(1),
+                                    t["y32"].stride(2), vp(s["saved"]), stream)
+                ops._raise_on(rc, "forward")
+                p.out_dtype = ops._DT[t["dy"].dtype]
+                dirs = _lib.Dirs(self.rows, self.cols, 3, 0, self.wf.data_ptr(), self.dw.data_ptr())
+                rc = L.cs2d_bwd_dir(ctypes.byref(p), ctypes.byref(dirs), vp(t["dy"]), t["dy"].stride(0), t["dy"].stride(1),
+                                    t["dy"].stride(2), vp(s["saved"]), vp(s["scratch"]), vp(t["du32"]), vp(t["ddelta"]),
+                                    vp(self._part("dA")), vp(t["dB32"]), vp(t["dC32"]), vp(self._part("dD")),
+                                    vp(self._part("ddelta_bias")), None, stream)
+                ops._raise_on(rc, "backward")
+                t["y"].copy_(t["y32"])
+                t["du"].copy_(t["du32"])
+                dB, dC = t["dB32"], t["dC32"]
+                if "dB" in s:
+                    dB, dC = s["dB"][:n], s["dC"][:n]
+                    dB.copy_(t["dB32"])
+                    dC.copy_(t["dC32"])
+                s["done"].record(main)
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(s["done"])
+                    for name, src in (("y", t["y"]), ("du", t["du"]), ("ddelta", t["ddelta"]), ("dB", dB), ("dC", dC)):
+                        out_host[name][lo:hi].copy_(src, non_blocking=True)
+                    s["free"].record(self.s_out)
+            if allreduce:
+                from . import parallel
+                parallel.allreduce_param_grads(self.flat)
+                parallel.allreduce_param_grads(self.dw)
+            out_host["param_grads"].copy_(self.flat, non_blocking=True)
+            out_host["dw"].copy_(self.dw.view(self.K, dim // self.K), non_blocking=True)
+            main.wait_stream(self.s_out)
+        return out_host

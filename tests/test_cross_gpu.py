@@ -164,3 +164,43 @@ def test_cross_scan_with_state_decay():
         want = want + g["dA_decay_ref"]
     check_close("dA_decay", decay.grad.cpu().numpy(), want, 1e-4, 1e-5)
     assert cs2d.device_status() == 0
+
+
+@pytest.mark.parametrize("shape,dtype,chunk", [((5, 4, 3, 4, 6, 9), torch.float32, 2), ((3, 4, 4, 16, 8, 8), torch.bfloat16, 1)])
+def test_host_pipeline_of_the_four_corner_operator(shape, dtype, chunk):
+    """Host buffers in, host buffers out, in batch chunks (a ragged last chunk, slots reused): the same
+    values as the operator on device tensors."""
+    b, K, d, n, h, w = shape
+    inp = make_inputs(b, K, d, n, h, w, dtype=dtype, seed=3)
+    gen = torch.Generator().manual_seed(11)
+    u0 = torch.randn(b, d, h, w, generator=gen).to(dtype)
+    wt = (torch.rand(K, d, generator=gen) + 0.1)
+    dy = torch.randn(b, d, h, w, generator=gen).to(dtype)
+    names = ("u", "delta", "A", "B", "C", "w", "D", "delta_bias")
+    full = dict(u=u0, delta=inp["delta"], A=inp["A"], B=inp["B"], C=inp["C"], w=wt, D=inp["D"], delta_bias=inp["delta_bias"])
+    dev = {k: v.cuda().requires_grad_(True) for k, v in full.items()}
+    y = cs2d.cross_scan_2d(*[dev[k] for k in names], True)
+    y.backward(dy.cuda())
+
+    host = {"u": u0.pin_memory(), "delta": inp["delta"].pin_memory(), "B": inp["B"].pin_memory(), "C": inp["C"].pin_memory(),
+            "dy": dy.pin_memory()}
+    params = {"A": inp["A"].cuda(), "D": inp["D"].cuda(), "delta_bias": inp["delta_bias"].cuda(), "w": wt.cuda()}
+    out = cs2d.alloc_cross_host_outputs(host["u"], host["delta"], host["B"], params["A"], True, True)
+    pipe = cs2d.CrossHostPipeline(host, params, True, chunk=chunk, depth=2)
+    for _ in range(2):   # the second run reuses every slot and accumulator
+        pipe.run(host, out)
+        torch.cuda.synchronize()
+    rtol, atol = (1e-4, 1e-5) if dtype == torch.float32 else (2e-2, 1e-3)
+    f = lambda t: t.detach().float().cpu().numpy()
+    check_close("y", f(out["y"]), f(y), rtol, atol)
+    check_close("du", f(out["du"]), f(dev["u"].grad), rtol, atol)
+    check_close("ddelta", f(out["ddelta"]), f(dev["delta"].grad), rtol, atol)
+    check_close("dB", f(out["dB"]), f(dev["B"].grad), rtol, atol)
+    check_close("dC", f(out["dC"]), f(dev["C"].grad), rtol, atol)
+    check_close("dw", f(out["dw"]), f(dev["w"].grad), rtol, atol)
+    dim = K * d
+    pg = out["param_grads"]
+    check_close("dA", pg[:dim * n].view(dim, n).numpy(), f(dev["A"].grad), rtol, atol)
+    check_close("dD", pg[dim * n:dim * n + dim].numpy(), f(dev["D"].grad), rtol, atol)
+    check_close("ddelta_bias", pg[dim * n + dim:dim * n + 2 * dim].numpy(), f(dev["delta_bias"].grad), rtol, atol)
+    assert cs2d.device_status() == 0
