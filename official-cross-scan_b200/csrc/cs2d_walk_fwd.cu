@@ -91,6 +91,16 @@ __device__ __forceinline__ void wk_st4_if(void *p, uint32_t v, bool on) {
 __device__ __forceinline__ void wk_st2_if(void *p, unsigned short v, bool on) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p st.global.b16 [%0], %1;\n\t}" ::"l"(p), "h"(v), "r"((int)on) : "memory");
 }
+__device__ __forceinline__ void wk_sts8_if(float2 *p, float2 v, bool on) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %3, 0;\n\t@p st.shared.v2.f32 [%0], {%1,%2};\n\t}" ::"r"(smem_addr(p)), "f"(v.x),
+                 "f"(v.y), "r"((int)on)
+                 : "memory");
+}
+__device__ __forceinline__ void wk_st16_if(float4 *p, float4 v, bool on) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %5, 0;\n\t@p st.global.v4.f32 [%0], {%1,%2,%3,%4};\n\t}" ::"l"(p), "f"(v.x),
+                 "f"(v.y), "f"(v.z), "f"(v.w), "r"((int)on)
+                 : "memory");
+}
 // one result element of runtime type dt (the branch on dt is uniform)
 __device__ __forceinline__ void wk_st_elem_if(void *base, int64_t i, int dt, float v, bool on) {
     if (dt == CS2D_F32) wk_st4_if(reinterpret_cast<float *>(base) + i, __float_as_uint(v), on);
@@ -142,7 +152,11 @@ struct WalkSmem {
     static constexpr size_t C = B + (size_t)WK_NS * QC * TW * 16;
     static constexpr size_t DU = C + (size_t)WK_NS * QC * TW * 16;     // float4 [WK_NWC][2][EW]
     static constexpr size_t Du = DU + (size_t)WK_NWC * 2 * EW * 16;    // float  [WK_NWC][2][EW]
-    static constexpr size_t total = Du + (size_t)WK_NWC * 2 * EW * 4;
+    // checkpoint rows on their way out: per compute warp two slots of [CPW channels][2*QC pairs][8*LR columns]
+    // float2, rows padded by two entries (the lanes of one store then fall on distinct banks)
+    static constexpr int NPR = 2 * QC, WPC = 8 * LR, TP = WPC + 2, CKS = CPW * NPR * TP;
+    static constexpr size_t CK = (Du + (size_t)WK_NWC * 2 * EW * 4 + 15) & ~(size_t)15;
+    static constexpr size_t total = CK + (size_t)WK_NWC * 2 * CKS * 8;
 };
 
 template <int SWD, int LR, int QC, int DT>
@@ -300,13 +314,20 @@ __global__ void __launch_bounds__(WK_THREADS, 1) wfwd_kernel(const Dev P) {
     int du_idx[CNT];   // D*u of those columns; a column the lane does not store reads (and drops) the strip's last entry
 #pragma unroll
     for (int x = 0; x < CNT; ++x) du_idx[x] = chw * TW + j * SP + min(ybase + x, SWD - 1);
-    // checkpoint rows of the thread's two pairs (block 0), and the column past the strips this lane zeroes
-    const int Wp = P.ck_wp, ck_step = P.NPp * Wp;
-    float2 *ckrow[2];
-#pragma unroll
-    for (int k = 0; k < 2; ++k) ckrow[k] = P.saved + (((int64_t)b * P.dim + d) * P.nck * P.NPp + 2 * q + k) * Wp;
-    const bool keep_ck = !P.ck_roll && ch_ok;
-    const int zc = LR * SWD + j;
+    // Checkpoint rows: this lane's strips go to the warp's shared tile (two slots: the next checkpoint row
+    // begins before the last lane has finished this one), the warp writes the finished row.  The tile is
+    // zero-filled once: columns no strip covers and idle pairs stay finite for the backward's padded strips.
+    constexpr int NPR = S::NPR, WPC = S::WPC, TP = S::TP, CKS = S::CKS;
+    float2 *sCK = reinterpret_cast<float2 *>(wsm + S::CK) + warp * 2 * CKS;
+    for (int i = lane; i < 2 * CKS; i += 32) sCK[i] = bc(0.f);
+    float2 *ck_mine = sCK + (chw * NPR + 2 * q) * TP + j * SWD;   // pair k: + k*TP; slot: + CKS
+    const bool keep_ck = !P.ck_roll;
+    // flush: float4 number lane + 32*m of a slot (m < 8) belongs to channel m / LR of the warp, pair row
+    // lane / (4*LR) + (8/LR) * (m % LR), column pair lane % (4*LR)
+    const float4 *ck_src0 = reinterpret_cast<const float4 *>(sCK + (lane / (4 * LR)) * TP + 2 * (lane % (4 * LR)));
+    const int ck_lane4 = (lane / (4 * LR)) * (WPC / 2) + lane % (4 * LR);
+    float4 *saved4 = reinterpret_cast<float4 *>(P.saved);
+    const int ck_step4 = NPR * WPC / 2;   // float4 per checkpoint block of a channel
     const int out_dt = P.out_dt;
 
     const float4 *sB0 = sB + q * TW + j * SP, *sC0 = sC + q * TW + j * SP, *sDU0 = sDU + chw * TW + j * SP;
@@ -388,15 +409,26 @@ __global__ void __launch_bounds__(WK_THREADS, 1) wfwd_kernel(const Dev P) {
         // lanes of a row are at different image rows, so in every iteration some of them are at such a row.
         {
             const bool ck_on = act && keep_ck && (R & (RB - 1)) == RB - 1 && R + 1 < H;
-            const int64_t off = (int64_t)(R >> 2) * ck_step;
+            float2 *mine = ck_mine + ((R >> 2) & 1) * CKS;
 #pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                float2 *row = ckrow[k] + off;
-                const bool on = ck_on && pair_on[k];
+            for (int k = 0; k < 2; ++k)
 #pragma unroll
-                for (int i = 0; i < SWD; ++i) wk_st8_if(row + j * SWD + i, h_up[k][i], on);   // LR*SWD <= Wp
-                // columns no strip covers: finite values for the backward's padded strips
-                wk_st8_if(row + zc, bc(0.f), on && zc < Wp);
+                for (int i = 0; i < SWD; ++i) wk_sts8_if(mine + k * TP + i, h_up[k][i], ck_on);
+        }
+        {   // the row the last lane has just finished: complete, written by the whole warp
+            const int Rf = t - (LR - 1);
+            if (keep_ck && Rf >= 0 && (Rf & (RB - 1)) == RB - 1 && Rf + 1 < H) {   // uniform
+                __syncwarp();
+                const int so = ((Rf >> 2) & 1) * (CKS / 2);   // float4 units: CKS is even
+                const int64_t go = (int64_t)(Rf >> 2) * ck_step4;
+#pragma unroll
+                for (int m = 0; m < 8; ++m) {
+                    const int cw = m / LR, rowm = cw * NPR + (8 / LR) * (m % LR);   // compile-time
+                    const int che = warp * CPW + cw;
+                    const int64_t dm = (int64_t)b * P.dim + dbase + min(che, nch - 1);
+                    wk_st16_if(saved4 + dm * P.nck * ck_step4 + go + (8 / LR) * (m % LR) * (WPC / 2) + ck_lane4,
+                               ck_src0[so + rowm * (TP / 2)], che < nch);
+                }
             }
         }
         yo += o_hs;
@@ -460,6 +492,8 @@ size_t walk_bc_bytes(int batch, int groups, int nrows, int ncols) { return (size
 cudaError_t launch_walk_fwd(const Dev &P, int grid, cudaStream_t st) {
     int swd, lr;
     walk_geometry(P.W, &swd, &lr);
+    // the checkpoint layout the kernel writes: 8 pair slots (more than 8 states), 8*lr columns per row
+    if (P.NPp != 8 || P.ck_wp != 8 * lr) return cudaErrorInvalidValue;
     return swd == 7 ? launch_wf2<7>(P, lr, grid, st) : launch_wf2<8>(P, lr, grid, st);
 }
 
