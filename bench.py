@@ -249,30 +249,32 @@ def measure_cross(name, steps, warmup, dev, world, rank, timed, batch=0):
     peak, peak_kind = load_peaks()
     achieved = nbytes / (ms * 1e-3) / 1e9
 
-    # end to end: u, delta, B, C, dy from pinned host memory, every output back to it, inside the timed
-    # region (cs2d.CrossHostPipeline); u and dy cross the bus once for all K directions
-    hx = {"u": u0.cpu().pin_memory(), "delta": t["delta"].cpu().pin_memory(), "B": t["B"].cpu().pin_memory(),
-          "C": t["C"].cpu().pin_memory(), "dy": dy.cpu().pin_memory()}
-    params = {"A": t["A"], "D": t["D"], "delta_bias": t["delta_bias"], "w": w}
-    del u0, dy
-    for k in ("delta", "B", "C"):
-        t.pop(k)
-    torch.cuda.empty_cache()
-    hout = cs2d.alloc_cross_host_outputs(hx["u"], hx["delta"], hx["B"], params["A"], params["D"] is not None,
-                                         params["delta_bias"] is not None)
-    pipe = cs2d.CrossHostPipeline(hx, params, True)
-    for _ in range(2):
-        pipe.run(hx, hout, allreduce=world > 1)
-    torch.cuda.synchronize()
-    e2e_steps = max(2, min(steps, 3))
-    e2e_ms = timed(lambda: pipe.run(hx, hout, allreduce=world > 1), e2e_steps) / e2e_steps
-    assert cs2d.device_status() == 0, "a kernel gave up on a bounded wait"
-    h2d = sum(v.numel() * v.element_size() for v in hx.values())
-    d2h = sum(v.numel() * v.element_size() for v in hout.values())
-    e2e = {"value": el / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
-           "d2h_bytes_per_step": d2h, "chunk": pipe.chunk}
-    del pipe, hx, hout
-    torch.cuda.empty_cache()
+    e2e = None
+    if world == 1:   # one GPU only: with N ranks the host link is shared and the figure says nothing about the operator
+        # end to end: u, delta, B, C, dy from pinned host memory, every output back to it, inside the timed
+        # region (cs2d.CrossHostPipeline); u and dy cross the bus once for all K directions
+        hx = {"u": u0.cpu().pin_memory(), "delta": t["delta"].cpu().pin_memory(), "B": t["B"].cpu().pin_memory(),
+              "C": t["C"].cpu().pin_memory(), "dy": dy.cpu().pin_memory()}
+        params = {"A": t["A"], "D": t["D"], "delta_bias": t["delta_bias"], "w": w}
+        del u0, dy
+        for k in ("delta", "B", "C"):
+            t.pop(k)
+        torch.cuda.empty_cache()
+        hout = cs2d.alloc_cross_host_outputs(hx["u"], hx["delta"], hx["B"], params["A"], params["D"] is not None,
+                                             params["delta_bias"] is not None)
+        pipe = cs2d.CrossHostPipeline(hx, params, True)
+        for _ in range(2):
+            pipe.run(hx, hout, allreduce=world > 1)
+        torch.cuda.synchronize()
+        e2e_steps = max(2, min(steps, 3))
+        e2e_ms = timed(lambda: pipe.run(hx, hout, allreduce=world > 1), e2e_steps) / e2e_steps
+        assert cs2d.device_status() == 0, "a kernel gave up on a bounded wait"
+        h2d = sum(v.numel() * v.element_size() for v in hx.values())
+        d2h = sum(v.numel() * v.element_size() for v in hout.values())
+        e2e = {"value": el / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "chunk": pipe.chunk}
+        del pipe, hx, hout
+        torch.cuda.empty_cache()
     return {"value": el / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "steps": steps, "scaling": "weak", "e2e": e2e,
             "config": {"workload": name, "op": "four-corner operator with fusion weights, all-reduce of the parameter "
                                                "gradients in the timed region" if world > 1 else
